@@ -1,0 +1,579 @@
+/*
+ * br_oracle.c -- TEST INFRASTRUCTURE, not a product path.
+ *
+ * A plain-C (fp32, optional OpenMP) restatement of the operator semantics of the
+ * BlackRiver BLOOM decoder hot path.  It exists so that the CUDA kernels can be
+ * checked against an independent CPU implementation and so that the benchmark
+ * can time a CPU baseline.  Only the tests, the smoke check and the CPU-baseline
+ * leg of the benchmark may load this library; nothing the product ships calls it.
+ *
+ * Parity pin: the reference keeps no golden vectors for this path, so the oracle
+ * is pinned against outputs of the reference's own PyTorch model
+ * (bloomz-7b/model.py: BloomBlock forward/backward, bloom_gelu_forward/back,
+ * LayerNorm, CrossEntropyLoss on shifted logits) generated with seeded inputs and
+ * committed as fixtures beside the generating script (tests/golden).
+ *
+ * Every function names the reference file:line whose behaviour it restates.
+ * All tensors are row-major and contiguous.
+ *
+ * Deliberate deviations from the reference CUDA path (each one follows the
+ * reference's PyTorch model instead, which is the only executable oracle):
+ *   - LayerNorm backward uses rsqrt(var) where `var` already holds sigma^2+eps;
+ *     the reference kernel adds eps a second time (normalize_kernels.cu:166).
+ *   - the loss is returned as +mean NLL (CrossEntropyLoss); the reference returns
+ *     the mean log-probability, i.e. the same number with the opposite sign
+ *     (cuda_tensor.cpp:691).
+ *   - bloom-GELU backward is evaluated in fp32, the reference kernel promotes to
+ *     fp64 through its literals (gelu.cu:61-70).
+ */
+#include <math.h>
+#include <float.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORC_API __attribute__((visibility("default")))
+
+ORC_API int orc_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* ------------------------------------------------------------------------- */
+/* LayerNorm.  cuda_tensor.cpp:236-255 -> normalize_kernels.cu:40-85.          */
+/* y = (x-mu)*rsqrt(v)*gamma+beta, mean[row]=mu, var[row]=sigma^2+eps.          */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_layernorm(const float* x, const float* gamma, const float* beta,
+                           float* y, float* mean, float* var,
+                           int64_t rows, int64_t hidden, float eps) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; r++) {
+        const float* xr = x + r * hidden;
+        float* yr = y + r * hidden;
+        double s = 0.0;
+        for (int64_t i = 0; i < hidden; i++) s += xr[i];
+        float mu = (float)(s / (double)hidden);
+        double q = 0.0;
+        for (int64_t i = 0; i < hidden; i++) {
+            double d = (double)xr[i] - (double)mu;
+            q += d * d;
+        }
+        float v = (float)(q / (double)hidden) + eps;
+        float rstd = 1.0f / sqrtf(v);
+        for (int64_t i = 0; i < hidden; i++) {
+            yr[i] = (xr[i] - mu) * rstd * gamma[i] + beta[i];
+        }
+        if (mean) mean[r] = mu;
+        if (var) var[r] = v;
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* LayerNorm backward.  cuda_tensor.cpp:700-727 -> normalize_kernels.cu:134-383 */
+/* xhat is recovered from the LN *output* y (the op never sees x):              */
+/*   xhat = (y-beta)/gamma', gamma' = gamma pushed away from 0 by +-eps          */
+/*   g = dy*gamma ; dx = (g - mean(g) - xhat*mean(g*xhat)) * rsqrt(var)          */
+/*   dbeta = sum_rows dy ; dgamma = sum_rows xhat*dy   (both overwrite)          */
+/* ------------------------------------------------------------------------- */
+static inline float orc_guard_gamma(float g, float eps) {
+    /* normalize_kernels.cu:15-17: keep the sign, move |gamma| off zero */
+    return g >= 0.0f ? g + eps : g - eps;
+}
+
+ORC_API void orc_layernorm_backward(const float* dy, const float* gamma, const float* beta,
+                                    const float* var, const float* y,
+                                    float* dgamma, float* dbeta, float* dx,
+                                    int64_t rows, int64_t hidden, float eps) {
+    double* accg = (double*)calloc((size_t)hidden, sizeof(double));
+    double* accb = (double*)calloc((size_t)hidden, sizeof(double));
+    for (int64_t r = 0; r < rows; r++) {
+        const float* dyr = dy + r * hidden;
+        const float* yr = y + r * hidden;
+        for (int64_t i = 0; i < hidden; i++) {
+            float xhat = (yr[i] - beta[i]) / orc_guard_gamma(gamma[i], eps);
+            accg[i] += (double)xhat * (double)dyr[i];
+            accb[i] += (double)dyr[i];
+        }
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; r++) {
+        const float* dyr = dy + r * hidden;
+        const float* yr = y + r * hidden;
+        float* dxr = dx + r * hidden;
+        double sg = 0.0, sgx = 0.0;
+        for (int64_t i = 0; i < hidden; i++) {
+            float xhat = (yr[i] - beta[i]) / orc_guard_gamma(gamma[i], eps);
+            double g = (double)dyr[i] * (double)gamma[i];
+            sg += g;
+            sgx += g * (double)xhat;
+        }
+        float mg = (float)(sg / (double)hidden);
+        float mgx = (float)(sgx / (double)hidden);
+        float rstd = 1.0f / sqrtf(var[r]);
+        for (int64_t i = 0; i < hidden; i++) {
+            float xhat = (yr[i] - beta[i]) / orc_guard_gamma(gamma[i], eps);
+            float g = dyr[i] * gamma[i];
+            dxr[i] = (g - mg - xhat * mgx) * rstd;
+        }
+    }
+    for (int64_t i = 0; i < hidden; i++) {
+        dgamma[i] = (float)accg[i];
+        dbeta[i] = (float)accb[i];
+    }
+    free(accg);
+    free(accb);
+}
+
+/* ------------------------------------------------------------------------- */
+/* bloom GELU.  cuda_tensor.cpp:401-412,815-828 -> gelu.cu:37-44,61-70.         */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_gelu(const float* x, float* y, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; i++) {
+        float v = x[i];
+        float t = tanhf(0.79788456f * v * (1.0f + 0.044715f * v * v));
+        y[i] = v * 0.5f * (1.0f + t);
+    }
+}
+
+ORC_API void orc_gelu_backward(const float* dy, const float* x, float* dx, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; i++) {
+        float v = x[i];
+        float t = tanhf(0.79788456f * v * (1.0f + 0.044715f * v * v));
+        float ff = 0.5f * v * ((1.0f - t * t) * (0.79788456f + 0.1070322243f * v * v)) + 0.5f * (1.0f + t);
+        dx[i] = ff * dy[i];
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Linear.  cuda_tensor.cpp:147-193.  y[n,o] = sum_i x[n,i] W[o,i] + b[o].      */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_linear(const float* x, const float* w, const float* b, float* y,
+                        int64_t n, int64_t in, int64_t out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < n; r++) {
+        const float* xr = x + r * in;
+        for (int64_t o = 0; o < out; o++) {
+            const float* wr = w + o * in;
+            float acc = 0.0f;
+            for (int64_t i = 0; i < in; i++) acc += xr[i] * wr[i];
+            y[r * out + o] = acc + (b ? b[o] : 0.0f);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Linear backward.  cuda_tensor.cpp:731-812.  Order: b_g, W_g, then x_g, all   */
+/* overwrite; x_g may alias x (train.words:198), so W_g is finished first.      */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_linear_backward(const float* dy, const float* x, const float* w,
+                                 float* x_g, float* w_g, float* b_g,
+                                 int64_t n, int64_t in, int64_t out) {
+    if (b_g) {
+        for (int64_t o = 0; o < out; o++) {
+            double s = 0.0;
+            for (int64_t r = 0; r < n; r++) s += dy[r * out + o];
+            b_g[o] = (float)s;
+        }
+    }
+    if (w_g) {
+#pragma omp parallel for schedule(static)
+        for (int64_t o = 0; o < out; o++) {
+            float* row = w_g + o * in;
+            for (int64_t i = 0; i < in; i++) row[i] = 0.0f;
+            for (int64_t r = 0; r < n; r++) {
+                float g = dy[r * out + o];
+                const float* xr = x + r * in;
+                for (int64_t i = 0; i < in; i++) row[i] += g * xr[i];
+            }
+        }
+    }
+    if (x_g) {
+        float* tmp = (float*)malloc((size_t)(n * in) * sizeof(float));
+#pragma omp parallel for schedule(static)
+        for (int64_t r = 0; r < n; r++) {
+            float* row = tmp + r * in;
+            for (int64_t i = 0; i < in; i++) row[i] = 0.0f;
+            for (int64_t o = 0; o < out; o++) {
+                float g = dy[r * out + o];
+                const float* wr = w + o * in;
+                for (int64_t i = 0; i < in; i++) row[i] += g * wr[i];
+            }
+        }
+        memcpy(x_g, tmp, (size_t)(n * in) * sizeof(float));
+        free(tmp);
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* [a,b,c,d] -> [a,c,b,d].  cuda_tensor.cpp:258-275, transform_kernels.cu:40-65 */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_transpose_0213(const float* x, float* y, int64_t a, int64_t b, int64_t c, int64_t d) {
+    for (int64_t ia = 0; ia < a; ia++)
+        for (int64_t ib = 0; ib < b; ib++)
+            for (int64_t ic = 0; ic < c; ic++)
+                memcpy(y + ((ia * c + ic) * b + ib) * d, x + ((ia * b + ib) * c + ic) * d,
+                       (size_t)d * sizeof(float));
+}
+
+/* ------------------------------------------------------------------------- */
+/* S = Q K^T / sqrt(d).  cuda_tensor.cpp:278-330.  q,k [B,h,T,d] -> [B,h,T,T].  */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_qk(const float* q, const float* k, float* s, int64_t bh, int64_t t, int64_t d) {
+    float scale = (float)(1.0 / sqrt((double)d));
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < bh; g++) {
+        for (int64_t i = 0; i < t; i++)
+            for (int64_t j = 0; j < t; j++) {
+                float acc = 0.0f;
+                for (int64_t e = 0; e < d; e++) acc += q[(g * t + i) * d + e] * k[(g * t + j) * d + e];
+                s[(g * t + i) * t + j] = acc * scale;
+            }
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* c = a + b with size-1 dims of b broadcast (4-D).  cuda_tensor.cpp:207-232.   */
+/* c may alias a.                                                              */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_add_bcast(const float* a, const float* b, float* c,
+                           const int64_t adim[4], const int64_t bdim[4]) {
+    int64_t bs[4];
+    int64_t st = 1;
+    for (int i = 3; i >= 0; i--) {
+        bs[i] = (bdim[i] == 1) ? 0 : st;
+        st *= bdim[i];
+    }
+    for (int64_t i0 = 0; i0 < adim[0]; i0++)
+        for (int64_t i1 = 0; i1 < adim[1]; i1++)
+            for (int64_t i2 = 0; i2 < adim[2]; i2++)
+                for (int64_t i3 = 0; i3 < adim[3]; i3++) {
+                    int64_t ai = ((i0 * adim[1] + i1) * adim[2] + i2) * adim[3] + i3;
+                    int64_t bi = i0 * bs[0] + i1 * bs[1] + i2 * bs[2] + i3 * bs[3];
+                    c[ai] = a[ai] + b[bi];
+                }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Row softmax, max-subtracted.  cuda_tensor.cpp:333-356 (cuDNN ACCURATE).      */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_softmax(const float* x, float* y, int64_t rows, int64_t cols) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; r++) {
+        const float* xr = x + r * cols;
+        float* yr = y + r * cols;
+        float m = -INFINITY;
+        for (int64_t j = 0; j < cols; j++) m = xr[j] > m ? xr[j] : m;
+        double s = 0.0;
+        for (int64_t j = 0; j < cols; j++) {
+            float e = expf(xr[j] - m);
+            yr[j] = e;
+            s += e;
+        }
+        float inv = (float)(1.0 / s);
+        for (int64_t j = 0; j < cols; j++) yr[j] *= inv;
+    }
+}
+
+/* dS = P o (dP - sum_j P o dP).  cuda_tensor.cpp:891-918. dx may alias dy/out. */
+ORC_API void orc_softmax_backward(const float* dy, const float* out, float* dx, int64_t rows, int64_t cols) {
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; r++) {
+        const float* g = dy + r * cols;
+        const float* p = out + r * cols;
+        float* d = dx + r * cols;
+        double dot = 0.0;
+        for (int64_t j = 0; j < cols; j++) dot += (double)g[j] * (double)p[j];
+        float fd = (float)dot;
+        for (int64_t j = 0; j < cols; j++) d[j] = p[j] * (g[j] - fd);
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* O = P V.  cuda_tensor.cpp:359-398.  P [B,h,T,T], v [B,h,T,d] -> [B,h,T,d].   */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_attn(const float* p, const float* v, float* o, int64_t bh, int64_t t, int64_t d) {
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < bh; g++) {
+        for (int64_t i = 0; i < t; i++) {
+            float* orow = o + (g * t + i) * d;
+            for (int64_t e = 0; e < d; e++) orow[e] = 0.0f;
+            for (int64_t j = 0; j < t; j++) {
+                float w = p[(g * t + i) * t + j];
+                const float* vr = v + (g * t + j) * d;
+                for (int64_t e = 0; e < d; e++) orow[e] += w * vr[e];
+            }
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* dV = P^T dO ; dP = dO V^T.  cuda_tensor.cpp:831-888 (unfused half).          */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_attn_backward(const float* dout, const float* p, const float* v,
+                               float* dp, float* dv, int64_t bh, int64_t t, int64_t d) {
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < bh; g++) {
+        for (int64_t j = 0; j < t; j++) {
+            float* dvr = dv + (g * t + j) * d;
+            for (int64_t e = 0; e < d; e++) dvr[e] = 0.0f;
+        }
+        for (int64_t i = 0; i < t; i++) {
+            const float* dor = dout + (g * t + i) * d;
+            for (int64_t j = 0; j < t; j++) {
+                float w = p[(g * t + i) * t + j];
+                float* dvr = dv + (g * t + j) * d;
+                const float* vr = v + (g * t + j) * d;
+                float acc = 0.0f;
+                for (int64_t e = 0; e < d; e++) {
+                    dvr[e] += w * dor[e];
+                    acc += dor[e] * vr[e];
+                }
+                dp[(g * t + i) * t + j] = acc;
+            }
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Fused form used by train.words:217.  cuda_tensor.cpp:921-1002.               */
+/* dV = P^T dO ; dS = softmax_bwd(P, dO V^T) ; dS may be written over P.        */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_softmax_attn_backward(const float* dout, const float* p, const float* v,
+                                       float* ds, float* dv, int64_t bh, int64_t t, int64_t d) {
+    float* dp = (float*)malloc((size_t)(bh * t * t) * sizeof(float));
+    orc_attn_backward(dout, p, v, dp, dv, bh, t, d);
+    orc_softmax_backward(dp, p, ds, bh * t, t);
+    free(dp);
+}
+
+/* ------------------------------------------------------------------------- */
+/* dQ = dS K / sqrt(d) ; dK = dS^T Q / sqrt(d).  cuda_tensor.cpp:1005-1063.     */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_qk_backward(const float* ds, const float* q, const float* k,
+                             float* dq, float* dk, int64_t bh, int64_t t, int64_t d) {
+    float scale = (float)(1.0 / sqrt((double)d));
+#pragma omp parallel for schedule(static)
+    for (int64_t g = 0; g < bh; g++) {
+        for (int64_t i = 0; i < t * d; i++) {
+            dq[g * t * d + i] = 0.0f;
+            dk[g * t * d + i] = 0.0f;
+        }
+        for (int64_t i = 0; i < t; i++)
+            for (int64_t j = 0; j < t; j++) {
+                float w = ds[(g * t + i) * t + j] * scale;
+                for (int64_t e = 0; e < d; e++) {
+                    dq[(g * t + i) * d + e] += w * k[(g * t + j) * d + e];
+                    dk[(g * t + j) * d + e] += w * q[(g * t + i) * d + e];
+                }
+            }
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Host-side input construction, bit-exact.  train_bloom.cpp:50-90.             */
+/* ------------------------------------------------------------------------- */
+/* slope_j = base^(j+1), base = 2^(-2^(3-log2 heads)), in double (:61-66).      */
+ORC_API void orc_alibi_slopes(int heads, double* slopes) {
+    double base = 3.0 - log2((double)heads * 1.0);
+    base = -1.0 * pow(2.0, base);
+    base = pow(2.0, base);
+    for (int j = 0; j < heads; j++) slopes[j] = pow(base, (double)(j + 1) * 1.0);
+}
+
+/* alibi[j,k] = (float)(k*slope_j)  (:65-70) */
+ORC_API void orc_alibi(int heads, int tokens, float* out) {
+    double* sl = (double*)malloc(sizeof(double) * (size_t)heads);
+    orc_alibi_slopes(heads, sl);
+    for (int j = 0; j < heads; j++)
+        for (int k = 0; k < tokens; k++) out[(int64_t)j * tokens + k] = (float)((double)k * 1.0 * sl[j]);
+    free(sl);
+}
+
+/* xmask[b,m,n] = 0 for n<=m while mask[b,n]!=0, stopping at the first 0 key;   */
+/* everything else -FLT_MAX (:73-90).                                           */
+ORC_API void orc_build_xmask(const int32_t* mask, int batch, int tokens, float* xmask) {
+    int64_t tt = (int64_t)tokens * tokens;
+    for (int64_t i = 0; i < batch * tt; i++) xmask[i] = -1.0f * FLT_MAX;
+    for (int b = 0; b < batch; b++) {
+        const int32_t* ms = mask + (int64_t)b * tokens;
+        float* m2d = xmask + b * tt;
+        for (int m = 0; m < tokens; m++)
+            for (int n = 0; n <= m; n++) {
+                if (ms[n] != 0) m2d[(int64_t)m * tokens + n] = 0.0f;
+                else break;
+            }
+    }
+}
+
+/* x[i,:] = table[ids[i],:]  (:50-56) */
+ORC_API void orc_embedding_gather(const float* table, const int32_t* ids, float* out, int64_t n, int64_t hidden) {
+    for (int64_t i = 0; i < n; i++)
+        memcpy(out + i * hidden, table + (int64_t)ids[i] * hidden, (size_t)hidden * sizeof(float));
+}
+
+/* ------------------------------------------------------------------------- */
+/* Loss target indexing, bit-exact.  cuda_tensor.cpp:555-568, 597-625.          */
+/* target[b,t] = ids[b,t+1] if t<T-1 and mask[b,t]!=0 and mask[b,t+1]!=0,       */
+/* otherwise -100.  Returns the number of counted positions.                   */
+/* ------------------------------------------------------------------------- */
+ORC_API int orc_loss_targets(const int32_t* ids, const int32_t* mask, int batch, int tokens, int32_t* target) {
+    int items = 0;
+    for (int b = 0; b < batch; b++) {
+        const int32_t* m = mask + (int64_t)b * tokens;
+        const int32_t* id = ids + (int64_t)b * tokens;
+        int32_t* tg = target + (int64_t)b * tokens;
+        for (int t = 0; t < tokens; t++) {
+            if (t < tokens - 1 && m[t] != 0 && m[t + 1] != 0) {
+                tg[t] = id[t + 1];
+                items++;
+            } else {
+                tg[t] = -100;
+            }
+        }
+    }
+    return items;
+}
+
+/* ------------------------------------------------------------------------- */
+/* Row-wise log-softmax + NLL on materialised logits.                          */
+/* Restates cudnnSoftmaxForward(LOG) + nll_loss.cu:10-43 + cudnnSoftmaxBackward */
+/* (cuda_tensor.cpp:642-671).  target outside [0,V) is skipped (nll_loss.cu:31) */
+/* row_loss[r] = -(logit[target]-logsumexp) or 0; dlogits = (softmax-onehot)*   */
+/* grad_scale for counted rows, 0 for skipped rows (dlogits may be NULL).       */
+/* Returns the sum of row losses in double.                                     */
+/* ------------------------------------------------------------------------- */
+ORC_API double orc_logsoftmax_nll(const float* logits, const int32_t* target, float* row_loss,
+                                  float* dlogits, int64_t rows, int64_t vocab, float grad_scale) {
+    double total = 0.0;
+#pragma omp parallel for schedule(static) reduction(+ : total)
+    for (int64_t r = 0; r < rows; r++) {
+        const float* z = logits + r * vocab;
+        int32_t tg = target[r];
+        int counted = (tg >= 0 && tg < vocab);
+        if (!counted) {
+            if (row_loss) row_loss[r] = 0.0f;
+            if (dlogits) memset(dlogits + r * vocab, 0, (size_t)vocab * sizeof(float));
+            continue;
+        }
+        float m = -INFINITY;
+        for (int64_t j = 0; j < vocab; j++) m = z[j] > m ? z[j] : m;
+        double s = 0.0;
+        for (int64_t j = 0; j < vocab; j++) s += exp((double)(z[j] - m));
+        double lse = (double)m + log(s);
+        double l = lse - (double)z[tg];
+        if (row_loss) row_loss[r] = (float)l;
+        total += l;
+        if (dlogits) {
+            float* dz = dlogits + r * vocab;
+            for (int64_t j = 0; j < vocab; j++) dz[j] = (float)exp((double)z[j] - lse) * grad_scale;
+            dz[tg] -= grad_scale;
+        }
+    }
+    return total;
+}
+
+/* ------------------------------------------------------------------------- */
+/* op_loss_backward.  cuda_tensor.cpp:465-697.                                  */
+/* x [B,T,H] (after ln_f), ids/mask [B,T], W [V,H].                             */
+/* x_g is zeroed then written for counted rows; w_g is ACCUMULATED (+=), as the */
+/* reference's host sgemm does with beta=1 (:515-533).  Returns mean NLL.       */
+/* ------------------------------------------------------------------------- */
+ORC_API float orc_loss_backward(const float* x, const int32_t* ids, const int32_t* mask, const float* w,
+                                float* x_g, float* w_g, int batch, int tokens, int64_t hidden, int64_t vocab) {
+    int64_t n = (int64_t)batch * tokens;
+    int32_t* target = (int32_t*)malloc((size_t)n * sizeof(int32_t));
+    int items = orc_loss_targets(ids, mask, batch, tokens, target);
+    if (x_g) memset(x_g, 0, (size_t)(n * hidden) * sizeof(float));
+    if (items == 0) {
+        free(target);
+        return 0.0f;
+    }
+    float scale = 1.0f / (float)items;
+    double total = 0.0;
+    float* z = (float*)malloc((size_t)vocab * sizeof(float));
+    float* dz = (float*)malloc((size_t)vocab * sizeof(float));
+    for (int64_t r = 0; r < n; r++) {
+        int32_t tg = target[r];
+        if (tg < 0 || tg >= vocab) continue;
+        const float* xr = x + r * hidden;
+#pragma omp parallel for schedule(static)
+        for (int64_t o = 0; o < vocab; o++) {
+            const float* wr = w + o * hidden;
+            float acc = 0.0f;
+            for (int64_t i = 0; i < hidden; i++) acc += xr[i] * wr[i];
+            z[o] = acc;
+        }
+        float rl;
+        total += orc_logsoftmax_nll(z, &tg, &rl, dz, 1, vocab, scale);
+        if (x_g) {
+            float* xg = x_g + r * hidden;
+            for (int64_t o = 0; o < vocab; o++) {
+                float g = dz[o];
+                const float* wr = w + o * hidden;
+                for (int64_t i = 0; i < hidden; i++) xg[i] += g * wr[i];
+            }
+        }
+        if (w_g) {
+#pragma omp parallel for schedule(static)
+            for (int64_t o = 0; o < vocab; o++) {
+                float g = dz[o];
+                float* wg = w_g + o * hidden;
+                for (int64_t i = 0; i < hidden; i++) wg[i] += g * xr[i];
+            }
+        }
+    }
+    free(z);
+    free(dz);
+    free(target);
+    return (float)(total / (double)items);
+}
+
+/* ------------------------------------------------------------------------- */
+/* op_last_logits.  cuda_tensor.cpp:415-462.  Row t* = first i with             */
+/* mask[i+1]==0, or 0 when no such i exists (so a full-length row picks 0).      */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_last_logits(const float* x, const int32_t* mask, const float* w, float* out,
+                             int batch, int tokens, int64_t hidden, int64_t vocab) {
+    for (int b = 0; b < batch; b++) {
+        const int32_t* m = mask + (int64_t)b * tokens;
+        int target = 0;
+        for (int i = 0; i < tokens - 1; i++) {
+            if (m[i + 1] == 0) {
+                target = i;
+                break;
+            }
+        }
+        orc_linear(x + ((int64_t)b * tokens + target) * hidden, w, NULL, out + (int64_t)b * vocab, 1, hidden, vocab);
+    }
+}
+
+/* ------------------------------------------------------------------------- */
+/* Adam with fp32 master weights (torch.optim.Adam defaults; not in the          */
+/* reference, which has no optimizer -- kernels.h:147 only declares one).        */
+/* ------------------------------------------------------------------------- */
+ORC_API void orc_adam(float* w, float* m, float* v, const float* g, int64_t n,
+                      float lr, float beta1, float beta2, float eps, int step, float grad_scale) {
+    double bc1 = 1.0 - pow((double)beta1, (double)step);
+    double bc2 = 1.0 - pow((double)beta2, (double)step);
+    float step_size = (float)((double)lr / bc1);
+    float inv_bc2_sqrt = (float)(1.0 / sqrt(bc2));
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; i++) {
+        float gi = g[i] * grad_scale;
+        float mi = beta1 * m[i] + (1.0f - beta1) * gi;
+        float vi = beta2 * v[i] + (1.0f - beta2) * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        float denom = sqrtf(vi) * inv_bc2_sqrt + eps;
+        w[i] -= step_size * mi / denom;
+    }
+}
