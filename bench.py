@@ -1,0 +1,435 @@
+#!/usr/bin/env python
+"""Benchmark of the BLOOM decoder hot-path kernels on B200.
+
+Workload (the operator microbench the headline metric is quoted on): fp16 storage, fp32
+accumulate, 8192 tokens per step, seed 1.  One step is one pass of
+
+    LayerNorm fwd + bwd              on [8192, 4096]
+    bloom-GELU fwd + bwd             on [8192, 4096] and [8192, 16384]
+    log-softmax + NLL fwd + gradient on [8192, 250880] logits ~ N(0, 2), 10 % rows ignored
+
+`value` is tokens/s with every input resident in HBM; `e2e` is the same pass driven from
+pinned HOST buffers through the C ABI, with the host->device copy of every input and the
+device->host read of the losses inside the timed region.  `roofline` describes the dominant
+kernel (log-softmax + NLL + gradient): algorithmic bytes / CUDA-event time / measured HBM peak.
+`cpu_baseline` times the CPU oracle on a bounded sample of the same workload.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+For N > 1 launch under torchrun; tokens are sharded by rank (no data-path collective, weak
+scaling: 8192 tokens per GPU).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+TOKENS = 8192
+HIDDEN = 4096
+HIDDEN4 = 16384
+VOCAB = 250880
+MASK_FRAC = 0.1
+SEED = 1
+WORKLOAD = ("operator microbench, fp16 storage / fp32 accumulate, 8192 tokens: LayerNorm fwd+bwd [8192,4096]; "
+            "bloom-GELU fwd+bwd [8192,4096] and [8192,16384]; log-softmax+NLL fwd+gradient [8192,250880], "
+            "10% rows ignored; seed 1")
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for ts, line in self.samples:
+            if ts < t0 or ts > t1 + 0.1:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+def make_host_inputs(torch, rank, dev):
+    """Seeded synthetic inputs of the microbench shapes, kept in pinned host memory (the caller's
+    copy).  The random draws are made by the device generator and copied out once, because
+    drawing two billion normals on the host takes minutes; the timed regions never draw."""
+    g = torch.Generator(device=dev).manual_seed(SEED + 1000 * rank)
+
+    def pinned(t):
+        out = torch.empty(t.shape, dtype=t.dtype).pin_memory()
+        out.copy_(t)
+        return out
+    h = {}
+    for s in range(2):
+        h[f"x{s}"] = pinned(torch.randn(TOKENS, HIDDEN, generator=g, device=dev).half())
+        h[f"dy{s}"] = pinned(torch.randn(TOKENS, HIDDEN, generator=g, device=dev).half())
+        h[f"x4_{s}"] = pinned(torch.randn(TOKENS, HIDDEN4, generator=g, device=dev).half())
+        h[f"dy4_{s}"] = pinned(torch.randn(TOKENS, HIDDEN4, generator=g, device=dev).half())
+    h["gamma"] = pinned((1.0 + 0.1 * torch.randn(HIDDEN, generator=g, device=dev)).half())
+    h["beta"] = pinned((0.1 * torch.randn(HIDDEN, generator=g, device=dev)).half())
+    logits = torch.empty((TOKENS, VOCAB), dtype=torch.float16).pin_memory()
+    for r0 in range(0, TOKENS, 1024):   # logits ~ N(0, sigma=2), drawn in row chunks
+        logits[r0:r0 + 1024].copy_((torch.randn(1024, VOCAB, generator=g, device=dev) * 2.0).half())
+    h["logits"] = logits
+    target = torch.randint(0, VOCAB, (TOKENS,), generator=g, device=dev, dtype=torch.int32)
+    target[torch.rand(TOKENS, generator=g, device=dev) < MASK_FRAC] = -100
+    h["target"] = pinned(target)
+    torch.cuda.synchronize()
+    return h
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from blackriver_b200 import ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    peak, peak_kind = load_peaks()
+
+    host = make_host_inputs(torch, rank, dev)
+    d = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+    torch.cuda.synchronize()
+    n_valid = int((host["target"] >= 0).sum())
+    grad_scale = 1.0 / max(n_valid, 1)
+
+    # outputs / scratch, allocated once (the C ABI itself never allocates)
+    o = {}
+    for s in range(2):
+        o[f"y{s}"] = torch.empty_like(d[f"x{s}"])
+        o[f"dx{s}"] = torch.empty_like(d[f"x{s}"])
+        o[f"g{s}"] = torch.empty_like(d[f"x{s}"])
+        o[f"dg{s}"] = torch.empty_like(d[f"x{s}"])
+        o[f"g4_{s}"] = torch.empty_like(d[f"x4_{s}"])
+        o[f"dg4_{s}"] = torch.empty_like(d[f"x4_{s}"])
+        o[f"var{s}"] = torch.empty(TOKENS, dtype=torch.float32, device=dev)
+    o["dgamma"] = torch.empty_like(d["gamma"])
+    o["dbeta"] = torch.empty_like(d["beta"])
+    o["dlogits"] = torch.empty_like(d["logits"])
+    o["row_loss"] = torch.empty(TOKENS, dtype=torch.float32, device=dev)
+    o["loss"] = torch.empty(1, dtype=torch.float32, device=dev)
+    from blackriver_b200 import brk
+    ws_bytes = brk.lib().brk_layernorm_bwd_workspace_bytes(TOKENS, HIDDEN)
+    o["ws"] = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
+    rows_host = torch.empty(TOKENS, dtype=torch.float32).pin_memory()
+
+    # fill both LayerNorm sets once so that backward has a valid (y, var) of the other set
+    for s in range(2):
+        _, _, var = ops.layernorm(d[f"x{s}"], d["gamma"], d["beta"], 1e-5, out=o[f"y{s}"])
+        o[f"var{s}"].copy_(var)
+    torch.cuda.synchronize()
+
+    KERNELS = ("ln_fwd", "gelu16k_fwd", "ln_bwd", "gelu16k_bwd", "gelu4k_fwd", "gelu4k_bwd", "nll_fwd_bwd")
+    LAUNCHES_PER_STEP = 1 + 1 + 2 + 1 + 1 + 1 + 1 + 1  # ln_bwd is two launches; + the loss sum
+
+    def step(i, ev=None):
+        a, b = i % 2, (i + 1) % 2   # set read by forward ops / by backward ops (last touched a step ago)
+
+        def mark(k):
+            if ev is not None:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                ev.append((k, e))
+        mark("start")
+        brk.call("brk_layernorm_fwd", d[f"x{a}"].data_ptr(), d["gamma"].data_ptr(), d["beta"].data_ptr(),
+                 o[f"y{a}"].data_ptr(), 0, o[f"var{a}"].data_ptr(), TOKENS, HIDDEN, 1e-5, brk.F16, ops.stream())
+        mark("ln_fwd")
+        ops.gelu(d[f"x4_{a}"], out=o[f"g4_{a}"])
+        mark("gelu16k_fwd")
+        ops.layernorm_backward(d[f"dy{b}"], d["gamma"], d["beta"], o[f"var{b}"], o[f"y{b}"], 1e-5, dgamma=o["dgamma"],
+                               dbeta=o["dbeta"], dx=o[f"dx{b}"], workspace=o["ws"])
+        mark("ln_bwd")
+        ops.gelu_backward(d[f"dy4_{b}"], d[f"x4_{b}"], out=o[f"dg4_{b}"])
+        mark("gelu16k_bwd")
+        ops.gelu(d[f"x{a}"], out=o[f"g{a}"])
+        mark("gelu4k_fwd")
+        ops.gelu_backward(d[f"dy{b}"], d[f"x{b}"], out=o[f"dg{b}"])
+        mark("gelu4k_bwd")
+        ops.logsoftmax_nll_backward(d["logits"], d["target"], grad_scale, row_loss=o["row_loss"], dlogits=o["dlogits"])
+        mark("nll_fwd_bwd")
+        ops.sum_f32(o["row_loss"], out=o["loss"])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    t_wall0 = time.time()
+    ev = []
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(args.warmup + i, ev)
+    e1.record()
+    barrier()
+    t_wall1 = time.time()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    loss_val = float(o["loss"].item()) * grad_scale
+
+    per_kernel = {k: [] for k in KERNELS}
+    for j in range(1, len(ev)):
+        k, e = ev[j]
+        if k != "start":
+            per_kernel[k].append(ev[j - 1][1].elapsed_time(e))
+
+    # ---- end to end: host buffers in, losses out, copies inside the timed region -------------
+    h2d_keys = ["x0", "dy0", "x4_0", "dy4_0", "gamma", "beta", "logits", "target"]
+    h2d_bytes = sum(host[k].numel() * host[k].element_size() for k in h2d_keys)
+    d2h_bytes = loss_host.numel() * 4 + rows_host.numel() * 4
+
+    def e2e_step(i):
+        for k in h2d_keys:
+            d[k].copy_(host[k], non_blocking=True)
+        # one set only: the caller hands over one batch; LayerNorm backward consumes this step's y
+        brk.call("brk_layernorm_fwd", d["x0"].data_ptr(), d["gamma"].data_ptr(), d["beta"].data_ptr(),
+                 o["y0"].data_ptr(), 0, o["var0"].data_ptr(), TOKENS, HIDDEN, 1e-5, brk.F16, ops.stream())
+        ops.gelu(d["x4_0"], out=o["g4_0"])
+        ops.layernorm_backward(d["dy0"], d["gamma"], d["beta"], o["var0"], o["y0"], 1e-5, dgamma=o["dgamma"],
+                               dbeta=o["dbeta"], dx=o["dx0"], workspace=o["ws"])
+        ops.gelu_backward(d["dy4_0"], d["x4_0"], out=o["dg4_0"])
+        ops.gelu(d["x0"], out=o["g0"])
+        ops.gelu_backward(d["dy0"], d["x0"], out=o["dg0"])
+        ops.logsoftmax_nll_backward(d["logits"], d["target"], grad_scale, row_loss=o["row_loss"], dlogits=o["dlogits"])
+        ops.sum_f32(o["row_loss"], out=o["loss"])
+        loss_host.copy_(o["loss"], non_blocking=True)
+        rows_host.copy_(o["row_loss"], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step(0)
+    barrier()
+    f0 = torch.cuda.Event(enable_timing=True)
+    f1 = torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    f1.record()
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+
+    # ---- max over ranks --------------------------------------------------------------------------
+    if world > 1:
+        t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e = float(t[0]), float(t[1])
+
+    ms_per_step = ms_total / args.steps
+    value = world * TOKENS / (ms_per_step * 1e-3)
+    e2e_value = world * TOKENS / (ms_e2e / e2e_steps * 1e-3)
+
+    if rank == 0:
+        es = 2
+        masked = TOKENS - n_valid
+        alg = {
+            "ln_fwd": 2 * TOKENS * HIDDEN * es + 2 * HIDDEN * es + 4 * TOKENS,
+            "ln_bwd": 3 * TOKENS * HIDDEN * es + 4 * TOKENS + 2 * HIDDEN * es * 2,
+            "gelu4k_fwd": 2 * TOKENS * HIDDEN * es, "gelu4k_bwd": 3 * TOKENS * HIDDEN * es,
+            "gelu16k_fwd": 2 * TOKENS * HIDDEN4 * es, "gelu16k_bwd": 3 * TOKENS * HIDDEN4 * es,
+            # ignored rows are never read; their gradient row is written as zeros
+            "nll_fwd_bwd": (2 * n_valid + masked) * VOCAB * es + 8 * TOKENS,
+        }
+        kern = {}
+        for k in KERNELS:
+            ms = statistics.mean(per_kernel[k])
+            gbs = alg[k] / (ms * 1e-3) / 1e9
+            kern[k] = {"ms": round(ms, 4), "algorithmic_bytes": alg[k], "gbs": round(gbs, 1),
+                       "frac_of_" + peak_kind + "_hbm": round(gbs / peak, 3)}
+        dom = "nll_fwd_bwd"
+        roofline = {"kernel": dom, "bound": "hbm", "achieved": kern[dom]["gbs"], "peak": peak, "unit": "GB/s",
+                    "frac": round(kern[dom]["gbs"] / peak, 3), "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)"
+                    if peak_kind == "measured" else "fallback 6650 GB/s", "traffic": load_traffic()}
+        cpu = cpu_baseline()
+        out = {
+            "metric": "tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "tokens_per_gpu": TOKENS,
+                       "l2": "inputs larger than L2: two rotating LN/GELU buffer sets and an 8 GB logits sweep per step "
+                             "separate every re-use"},
+            "clocks": clocks, "gpu_launches": LAUNCHES_PER_STEP * args.steps,
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
+            "roofline": roofline, "kernels": kern, "cpu_baseline": cpu, "loss": round(loss_val, 5),
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def load_traffic():
+    """Per-launch DRAM traffic of the dominant kernel from the committed ncu summary, if any."""
+    p = os.path.join(ROOT, "profiles", "nll_fwd_bwd_traffic.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p)).get("traffic_bytes_per_launch_full_size")
+        except (ValueError, OSError):
+            return None
+    return None
+
+
+# ------------------------------------------------------------------------------------------
+# CPU legs (the only place the benchmark touches oracle/)
+# ------------------------------------------------------------------------------------------
+CPU_SAMPLE_TOKENS = 1024
+
+
+def cpu_inputs(np, sample, rng):
+    f32 = np.float32
+    x = rng.standard_normal((sample, HIDDEN), dtype=f32)
+    dy = rng.standard_normal((sample, HIDDEN), dtype=f32)
+    x4 = rng.standard_normal((sample, HIDDEN4), dtype=f32)
+    dy4 = rng.standard_normal((sample, HIDDEN4), dtype=f32)
+    gamma = np.ones(HIDDEN, f32)
+    beta = np.zeros(HIDDEN, f32)
+    logits = rng.standard_normal((sample, VOCAB), dtype=f32) * f32(2)
+    target = rng.integers(0, VOCAB, sample).astype(np.int32)
+    target[rng.random(sample) < MASK_FRAC] = -100
+    return x, dy, x4, dy4, gamma, beta, logits, target
+
+
+def cpu_pass(orc, inputs):
+    """One pass of the same operator list with the CPU oracle on the sampled tokens; seconds."""
+    x, dy, x4, dy4, gamma, beta, logits, target = inputs
+    t0 = time.perf_counter()
+    y, _, var = orc.layernorm(x, gamma, beta)
+    orc.gelu(x4)
+    orc.layernorm_backward(dy, gamma, beta, var, y)
+    orc.gelu_backward(dy4, x4)
+    orc.gelu(x)
+    orc.gelu_backward(dy, x)
+    orc.logsoftmax_nll(logits, target, grad_scale=1.0 / len(target))
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(steps=3):
+    import numpy as np
+    from oracle import oracle as orc
+    rng = np.random.default_rng(SEED)
+    inputs = cpu_inputs(np, CPU_SAMPLE_TOKENS, rng)
+    cpu_pass(orc, inputs)
+    t = min(cpu_pass(orc, inputs) for _ in range(steps))
+    return {"value": round(CPU_SAMPLE_TOKENS / t, 1), "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port",
+            "sample": f"{CPU_SAMPLE_TOKENS} of the 8192 tokens per pass, same operator list and shapes, fp32 CPU oracle "
+                      f"(OpenMP), best of {steps}"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as orc
+    rng = np.random.default_rng(SEED)
+    inputs = cpu_inputs(np, CPU_SAMPLE_TOKENS, rng)
+    for _ in range(max(1, min(args.warmup, 3))):
+        cpu_pass(orc, inputs)
+    ts = [cpu_pass(orc, inputs) for _ in range(args.steps)]
+    t = sum(ts) / len(ts)
+    value = CPU_SAMPLE_TOKENS / t
+    out = {
+        "impl": "reference", "metric": "tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(t * 1e3, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "the reference has no CPU implementation of these operators "
+                   "(its cpu_tensor is storage only); this arm times the fp32 CPU restatement of its operator "
+                   "semantics on the host cores, each step a bounded sample of the pass"},
+        "cpu_baseline": {"value": round(value, 1), "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port",
+                         "sample": f"{CPU_SAMPLE_TOKENS} of the 8192 tokens per step"},
+        "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,137 @@
+/*
+ * brk.h -- C ABI of libbrk.so, the sm_100a kernel library behind BlackRiver's device tensor.
+ *
+ * Every entry point takes raw DEVICE pointers, sizes and a CUDA stream (passed as void*, a
+ * cudaStream_t), launches asynchronously on that stream, never allocates, never synchronises
+ * and never throws.  The return value is 0 (BRK_OK) or a negative code whose first four
+ * values are the reference's br::ComputingReturn (blackriver/operators.hpp:12-18), so the
+ * device-tensor shim can hand it straight back through the operator interface.
+ *
+ * `dtype` selects the storage type of activations / weights: BRK_F32 or BRK_F16.  All
+ * arithmetic accumulates in fp32.  Statistics (LayerNorm mean/var, per-row losses) are fp32
+ * regardless of dtype.
+ *
+ * Each declaration cites the reference interface it replaces (file:line inside the
+ * reference project).
+ */
+#ifndef BRK_H_
+#define BRK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Exported symbol marker: the library is built with hidden visibility by default. */
+#define BRK_API __attribute__((visibility("default")))
+
+#define BRK_OK 0
+#define BRK_TODO_ERROR (-1)   /* br::OP_TODO_ERROR   */
+#define BRK_INPUT_ERROR (-2)  /* br::OP_INPUT_ERROR  */
+#define BRK_OUTPUT_ERROR (-3) /* br::OP_OUTPUT_ERROR */
+#define BRK_ATTR_ERROR (-4)   /* br::OP_ATTR_ERROR   */
+#define BRK_CUDA_ERROR (-5)   /* a CUDA launch/runtime call failed; see brk_last_cuda_error() */
+
+#define BRK_F32 0
+#define BRK_F16 1
+
+/* Library / device introspection. */
+BRK_API int brk_version(void);
+BRK_API const char* brk_last_cuda_error(void);
+BRK_API int brk_sm_count(void);
+
+/* ---- LayerNorm -------------------------------------------------------------------------
+ * Replaces CUDATensor::op_layernorm (blackriver/cuda_tensor.cpp:236-255) and
+ * kernels::launch_layer_norm_float (blackriver/kernels/normalize_kernels.cu:87-102).
+ * y = (x-mean)*rsqrt(var)*gamma+beta per row; mean[row], var[row] = biased variance + eps
+ * (fp32, may be NULL).  x,y [rows,hidden]; gamma,beta [hidden] in `dtype`. y may alias x. */
+BRK_API int brk_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* var,
+                      int64_t rows, int64_t hidden, float eps, int dtype, void* stream);
+
+/* Replaces CUDATensor::op_layernorm_backward (blackriver/cuda_tensor.cpp:700-727) and
+ * kernels::launch_ln_bw_float (blackriver/kernels/normalize_kernels.cu:361-383).
+ * Inputs: dy, the LayerNorm OUTPUT y (not x), gamma, beta, var (= sigma^2+eps from the forward).
+ * Outputs: dx [rows,hidden]; dgamma, dbeta [hidden] in `dtype`, overwritten, or added to when
+ * `accumulate` != 0.  dx may alias dy or y.  `workspace` holds per-CTA partial column sums;
+ * its size must be at least brk_layernorm_bwd_workspace_bytes(rows, hidden). */
+BRK_API size_t brk_layernorm_bwd_workspace_bytes(int64_t rows, int64_t hidden);
+BRK_API int brk_layernorm_bwd(const void* dy, const void* gamma, const void* beta, const float* var, const void* y,
+                      void* dgamma, void* dbeta, void* dx, int64_t rows, int64_t hidden, float eps,
+                      void* workspace, size_t workspace_bytes, int accumulate, int dtype, void* stream);
+
+/* ---- bloom GELU ------------------------------------------------------------------------
+ * Replaces CUDATensor::op_gelu / op_gelu_backward (blackriver/cuda_tensor.cpp:401-412,
+ * 815-828) and kernels::gelu_forward / gelu_backward (blackriver/kernels/gelu.cu:46-85).
+ * y = 0.5x(1+tanh(0.79788456x(1+0.044715x^2))).  Outputs may alias inputs. */
+BRK_API int brk_gelu_fwd(const void* x, void* y, int64_t n, int dtype, void* stream);
+BRK_API int brk_gelu_bwd(const void* dy, const void* x, void* dx, int64_t n, int dtype, void* stream);
+
+/* ---- vocabulary log-softmax + NLL --------------------------------------------------------
+ * Replaces the cudnnSoftmaxForward(LOG) + kernels::nllloss_forward + cudnnSoftmaxBackward
+ * sequence of CUDATensor::op_loss_backward (blackriver/cuda_tensor.cpp:535-553, 642-671;
+ * blackriver/kernels/nll_loss.cu:10-58) with one kernel over materialised logits
+ * [rows,vocab].  target[row] outside [0,vocab) (e.g. -100) marks an ignored row: loss 0,
+ * gradient 0.  row_loss[row] = logsumexp - logit[target] (fp32).  row_lse may be NULL.
+ * The fwd_bwd form also writes dlogits = (softmax - onehot) * grad_scale in `dtype`;
+ * dlogits may alias logits. */
+BRK_API int brk_logsoftmax_nll_fwd(const void* logits, const int32_t* target, float* row_loss, float* row_lse,
+                           int64_t rows, int64_t vocab, int dtype, void* stream);
+BRK_API int brk_logsoftmax_nll_fwd_bwd(const void* logits, const int32_t* target, float* row_loss, void* dlogits,
+                               int64_t rows, int64_t vocab, float grad_scale, int dtype, void* stream);
+
+/* Deterministic sum of n fp32 values into out[0] (single CTA, fixed order); the loss total. */
+BRK_API int brk_sum_f32(const float* x, float* out, int64_t n, void* stream);
+
+/* Loss targets on the device, bit-exact restatement of the host loops at
+ * blackriver/cuda_tensor.cpp:555-568 and 597-625: target[b,t] = ids[b,t+1] when t < T-1 and
+ * mask[b,t] != 0 and mask[b,t+1] != 0, else -100.  count[0] receives the number of counted
+ * positions (int32, overwritten). */
+BRK_API int brk_loss_targets(const int32_t* ids, const int32_t* mask, int32_t* target, int32_t* count,
+                     int batch, int tokens, void* stream);
+
+/* ---- elementwise / data movement ---------------------------------------------------------
+ * brk_add_bcast replaces CUDATensor::op_add (blackriver/cuda_tensor.cpp:207-232): c = a + b,
+ * 4-D, dims of b that are 1 broadcast; c may alias a or b. */
+BRK_API int brk_add_bcast(const void* a, const void* b, void* c, const int64_t adims[4], const int64_t bdims[4],
+                  int dtype, void* stream);
+/* Replaces CUDATensor::op_fill / op_zero (blackriver/cuda_tensor.cpp:100-125). */
+BRK_API int brk_fill(void* x, float value, int64_t n, int dtype, void* stream);
+/* fp32 <-> fp16 conversion (new: the reference has no fp16 path). */
+BRK_API int brk_cast(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, void* stream);
+/* Replaces CUDATensor::op_transpos_0213 (blackriver/cuda_tensor.cpp:258-275) and
+ * kernels::launch_transform_0213 (blackriver/kernels/transform_kernels.cu:40-87):
+ * x [a,b,c,d] -> y [a,c,b,d]. */
+BRK_API int brk_transpose_0213(const void* x, void* y, int64_t a, int64_t b, int64_t c, int64_t d, int dtype, void* stream);
+/* Column sums, out[j] = sum_i x[i,j] (overwrite or accumulate): the bias gradient that the
+ * reference takes with cudnnReduceTensor (blackriver/cuda_tensor.cpp:738-761). */
+BRK_API int brk_colsum(const void* x, void* out, int64_t rows, int64_t cols, int accumulate, int dtype, void* stream);
+/* Row softmax and its backward on [rows,cols]: CUDATensor::op_softmax / op_softmax_backward
+ * (blackriver/cuda_tensor.cpp:333-356, 891-918).  In-place allowed. */
+BRK_API int brk_softmax_fwd(const void* x, void* y, int64_t rows, int64_t cols, int dtype, void* stream);
+BRK_API int brk_softmax_bwd(const void* dy, const void* out, void* dx, int64_t rows, int64_t cols, int dtype, void* stream);
+/* Embedding gather, x[i,:] = table[ids[i],:]: the host memcpy loop of BloomInput::fetch_data
+ * (blackriver/train_bloom.cpp:50-56), bit-exact.  ids outside [0,vocab) give a zero row. */
+BRK_API int brk_embedding_gather(const void* table, const int32_t* ids, void* out, int64_t n, int64_t hidden, int64_t vocab,
+                         int dtype, void* stream);
+/* ALiBi [heads,tokens] and additive mask [batch,tokens,tokens] in fp32, bit-exact restatement
+ * of BloomInput::fetch_data (blackriver/train_bloom.cpp:58-90).  slopes are computed on the
+ * host in double by brk_alibi_slopes and passed in. */
+BRK_API void brk_alibi_slopes(int heads, double* slopes_out);
+BRK_API int brk_alibi_build(const double* slopes_dev, float* alibi, int heads, int tokens, void* stream);
+BRK_API int brk_xmask_build(const int32_t* mask, float* xmask, int batch, int tokens, void* stream);
+
+/* ---- GEMM (fp32 SIMT parity path) ----------------------------------------------------------
+ * C[b] = alpha * op(A[b]) * op(B[b]) + beta * C[b], row-major, op = transpose when the flag is
+ * non-zero; op(A) is [m,k], op(B) is [k,n]; lda/ldb/ldc are row strides of the stored
+ * matrices; `batch` problems at element strides sa/sb/sc.  Stands in for kernels::LtSgemm
+ * (blackriver/kernels/LtSgemm.cu:55-126) on the fp32 path (fp16 storage is accepted too). */
+BRK_API int brk_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_a, int trans_b,
+             int64_t lda, int64_t ldb, int64_t ldc, int64_t batch, int64_t sa, int64_t sb, int64_t sc,
+             float alpha, float beta, const void* bias, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BRK_H_ */
