@@ -331,6 +331,47 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_case(args):
+    """A few launches of one kernel family on a small, larger-than-L2 case (for ncu captures)."""
+    import torch
+    from blackriver_b200 import ops
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(SEED)
+    rows = args.rows
+    reps = 3
+    if args.case == "nll":
+        logits = (torch.randn(rows, VOCAB, generator=g, device=dev) * 2).half()
+        target = torch.randint(0, VOCAB, (rows,), generator=g, device=dev, dtype=torch.int32)
+        target[torch.rand(rows, generator=g, device=dev) < MASK_FRAC] = -100
+        dl = torch.empty_like(logits)
+        rl = torch.empty(rows, dtype=torch.float32, device=dev)
+        for _ in range(reps):
+            ops.logsoftmax_nll_backward(logits, target, 1.0 / rows, row_loss=rl, dlogits=dl)
+        for _ in range(reps):
+            ops.logsoftmax_nll(logits, target, row_loss=rl)
+    elif args.case == "ln":
+        rows = max(rows, TOKENS * 2)      # 2 x 134 MB per tensor: larger than L2
+        x = torch.randn(rows, HIDDEN, generator=g, device=dev).half()
+        dy = torch.randn(rows, HIDDEN, generator=g, device=dev).half()
+        gamma = torch.ones(HIDDEN, device=dev).half()
+        beta = torch.zeros(HIDDEN, device=dev).half()
+        for _ in range(reps):
+            y, _, var = ops.layernorm(x, gamma, beta)
+        for _ in range(reps):
+            ops.layernorm_backward(dy, gamma, beta, var, y)
+    else:
+        x = torch.randn(TOKENS, HIDDEN4, generator=g, device=dev).half()
+        dy = torch.randn(TOKENS, HIDDEN4, generator=g, device=dev).half()
+        out = torch.empty_like(x)
+        for _ in range(reps):
+            ops.gelu(x, out=out)
+        for _ in range(reps):
+            ops.gelu_backward(dy, x, out=out)
+    torch.cuda.synchronize()
+    print(json.dumps({"case": args.case, "rows": rows, "launch_groups": 2, "reps": reps}))
+
+
 def load_traffic():
     """Per-launch DRAM traffic of the dominant kernel from the committed ncu summary, if any."""
     p = os.path.join(ROOT, "profiles", "nll_fwd_bwd_traffic.json")
@@ -419,10 +460,15 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu"],
+                    help="profiling aid: run a few launches of one kernel family on a small case and exit")
+    ap.add_argument("--rows", type=int, default=1024, help="rows of the --case run")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":

@@ -1,0 +1,81 @@
+// The tensor-operator interface of BlackRiver: the drop-in boundary.
+//
+// Method names, argument order, argument meaning and return conventions are those of
+// br::TransformerComputing in the reference (blackriver/operators.hpp:20-112); scripts and
+// word bindings written against the reference call these unchanged.  Every method gets the
+// tensor it is invoked on a second time as `self` (a shared_ptr to the same object), outputs
+// are caller-allocated tensors, and the default implementation answers OP_TODO_ERROR so that a
+// backend only overrides what it supports.
+#pragma once
+
+#include <memory>
+#include <variant>
+#include <vector>
+
+namespace br {
+
+struct TensorType;
+using tensor_t = std::shared_ptr<TensorType>;
+
+// blackriver/operators.hpp:12-18.  The kernel library's status codes reuse these values.
+enum ComputingReturn {
+    OP_OK = 0,
+    OP_TODO_ERROR = -1,
+    OP_INPUT_ERROR = -2,
+    OP_OUTPUT_ERROR = -3,
+    OP_ATTR_ERROR = -4,
+};
+
+using ViewReturn = std::variant<ComputingReturn, tensor_t>;
+using LossReturn = std::variant<ComputingReturn, float>;
+
+struct TransformerComputing {
+    virtual ~TransformerComputing() = default;
+
+    // ---- io: files, host transport, device transport (operators.hpp:21-44) ----
+    virtual ComputingReturn io_load(tensor_t self, const char* fileName) { return OP_TODO_ERROR; }
+    virtual ComputingReturn io_save(tensor_t self, const char* fileName) { return OP_TODO_ERROR; }
+    virtual ComputingReturn io_dump(tensor_t self) { return OP_TODO_ERROR; }
+    virtual ComputingReturn io_mpi_bcast(tensor_t self, int root) { return OP_TODO_ERROR; }
+    virtual ComputingReturn io_mpi_recv(tensor_t self, int source) { return OP_TODO_ERROR; }
+    virtual ComputingReturn io_mpi_send(tensor_t self, int dst) { return OP_TODO_ERROR; }
+    virtual ComputingReturn io_nccl_recv(tensor_t self, int source) { return OP_TODO_ERROR; }
+    virtual ComputingReturn io_nccl_send(tensor_t self, int dst) { return OP_TODO_ERROR; }
+
+    // ---- storage ops (operators.hpp:46-57) ----
+    virtual ComputingReturn op_zero(tensor_t self) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_fill(tensor_t self, float value) { return OP_TODO_ERROR; }
+    // copies `src` INTO self (the reference names the parameter dst in one place and src in another;
+    // every caller passes the source, nn.cpp:71-78)
+    virtual ComputingReturn op_copy(tensor_t self, tensor_t src) { return OP_TODO_ERROR; }
+    // non-owning view of `self` at an element offset; one 0 in newShape means "infer"
+    virtual ViewReturn op_view(tensor_t self, size_t offset, const std::vector<size_t>& newShape) { return OP_TODO_ERROR; }
+
+    // ---- forward math (operators.hpp:58-87) ----
+    virtual ComputingReturn op_add(tensor_t self, tensor_t b, tensor_t c) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_mul(tensor_t self, tensor_t b, tensor_t c) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_linear(tensor_t self, tensor_t w, tensor_t bias, tensor_t y) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_layernorm(tensor_t self, tensor_t mean, tensor_t var, tensor_t scale, tensor_t bias,
+                                         tensor_t y, float eps) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_transpos_0213(tensor_t self, tensor_t y) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_qk(tensor_t self, tensor_t k, tensor_t qk) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_softmax(tensor_t self, tensor_t out) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_attn(tensor_t self, tensor_t v, tensor_t attn) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_gelu(tensor_t self, tensor_t dst) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_last_logits(tensor_t self, tensor_t mask, tensor_t lm_head, tensor_t output) { return OP_TODO_ERROR; }
+
+    // ---- loss and backward math (operators.hpp:88-111) ----
+    virtual LossReturn op_loss_backward(tensor_t self, tensor_t ids, tensor_t mask, tensor_t lm_head, tensor_t all_logits,
+                                        tensor_t x_g, tensor_t lm_head_g) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_layernorm_backward(tensor_t self, tensor_t scale, tensor_t bias, tensor_t var, tensor_t y,
+                                                  tensor_t dscale, tensor_t dbias, tensor_t din, float eps) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_linear_backward(tensor_t self, tensor_t x, tensor_t weight, tensor_t bias, tensor_t x_g,
+                                               tensor_t weight_g, tensor_t bias_g) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_gelu_backward(tensor_t self, tensor_t x, tensor_t x_g) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_attn_backward(tensor_t self, tensor_t attn, tensor_t v, tensor_t attn_g, tensor_t v_g) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_softmax_backward(tensor_t self, tensor_t out, tensor_t x_g) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_softmax_attn_backward(tensor_t self, tensor_t attn, tensor_t v, tensor_t attn_g, tensor_t v_g) { return OP_TODO_ERROR; }
+    virtual ComputingReturn op_qk_backward(tensor_t self, tensor_t q, tensor_t k, tensor_t q_g, tensor_t k_g) { return OP_TODO_ERROR; }
+};
+
+}  // namespace br
