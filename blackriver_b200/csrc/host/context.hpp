@@ -1,0 +1,75 @@
+// Process-wide runtime state: the device context (streams, events, scratch), the collective
+// context (rank layout and the NCCL communicator) and the host memory arena.
+//
+// Same three singletons as the reference (blackriver/context.hpp:8-47) with these changes:
+//  * one rank per GPU; there is no extra CPU-only feeder rank, so nccl_rank == mpi_rank;
+//  * a compute stream plus a dedicated transfer stream with events between them, so stage
+//    hand-offs overlap with compute; no cuBLAS / cuDNN handles (the kernels are our own);
+//  * no MPI dependency: the NCCL unique id arrives from the launcher (a file, or bytes handed
+//    in by an embedding process) and host tensors travel through NCCL via device staging.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <nccl.h>
+
+#include <cstddef>
+#include <string>
+
+#include "common.hpp"
+
+namespace br {
+
+struct ComputingContext {
+    static int cuda_device;
+    static cudaStream_t cuda_stream;   // compute
+    static cudaStream_t comm_stream;   // NCCL send/recv and staged host transfers
+    static cudaEvent_t compute_done;   // recorded on cuda_stream before a send reads a tensor
+    static cudaEvent_t comm_done;      // recorded on comm_stream after a recv wrote a tensor
+
+    static void* cuda_workspace;       // device scratch handed to kernels that need it
+    static void* local_workspace;      // pinned host scratch of the same size
+    static size_t workspace_size;
+
+    static bool booted;
+    static void boot(int device, size_t workspace_bytes = (size_t)256 << 20);
+    // adopt a stream owned by an embedding process (e.g. torch's current stream)
+    static void boot_with_stream(int device, cudaStream_t compute, size_t workspace_bytes = (size_t)256 << 20);
+    static void shutdown();
+};
+
+struct CollectiveContext {
+    static int mpi_world;   // number of ranks == number of GPUs in the job
+    static int mpi_rank;
+    static int nccl_world;  // same values; both names are kept because callers use both
+    static int nccl_rank;
+    static ncclComm_t nccl_comm;
+    static ncclUniqueId nccl_id;
+    static bool has_comm;
+
+    // Rank layout only (no communicator): what host-only tools and tests need.
+    static void boot_local(int rank, int world);
+    // Creates the communicator from a unique id produced by make_unique_id() on rank 0.
+    static void boot(int rank, int world, const ncclUniqueId& id);
+    // Rendezvous through a file: rank 0 writes the id, the others poll for it (bounded wait).
+    static void boot_from_file(int rank, int world, const std::string& path, int timeout_s = 120);
+    static ncclUniqueId make_unique_id();
+    static void shutdown();
+    static int now();  // whole seconds since boot, as the reference's echo prints
+};
+
+struct MemoryContext {
+    static const size_t page_size;
+    static void* root;
+    static size_t total_size;
+    static size_t currentp;
+    static bool pinned;
+
+    // Bump allocator over one block, never freed piecewise (blackriver/context.cpp:96-121).
+    // Requests are rounded UP to the page size (the reference rejects unaligned sizes).  With
+    // pinned = true the block is page-locked so device copies from it are asynchronous.
+    static void boot(size_t total_bytes, bool pinned = false);
+    static void* alloc(size_t bytes);
+    static void shutdown();
+};
+
+}  // namespace br
