@@ -1,0 +1,274 @@
+#include "nn.hpp"
+
+#include <array>
+
+#include "context.hpp"
+#include "tensortype.hpp"
+
+namespace br {
+namespace {
+
+// Pops N tensors; the result is in PUSH order (index 0 = pushed first = deepest).
+template <size_t N>
+std::array<tensor_t, N> pop_tensors(Stack& stack) {
+    std::array<tensor_t, N> t;
+    for (size_t i = N; i-- > 0;) t[i] = stack.pop_tensor();
+    return t;
+}
+
+std::vector<size_t> pop_shape(Stack& stack) {
+    std::vector<size_t> shape;
+    for (double v : stack.pop_number_list()) shape.push_back((size_t)v);
+    return shape;
+}
+
+#define BR_WORD(NAME, BODY)                        \
+    struct NAME : public NativeWord {              \
+        void run(Stack& stack) override { BODY }   \
+        NWORD_CREATOR_DEFINE_LR(NAME)              \
+    };
+
+// ( -- )  wait for the compute stream
+BR_WORD(Sync, {
+    (void)stack;
+    if (ComputingContext::booted) {
+        BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::cuda_stream));
+        BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::comm_stream));
+    }
+})
+
+// ( d1 .. dn n device dtype -- t )   device: "cuda" | "cpu"; dtype: "float" | "half" | "int"
+BR_WORD(Create, {
+    std::string dtype = stack.pop_string();
+    std::string device = stack.pop_string();
+    auto shape = pop_shape(stack);
+    tensor_t t;
+    if (device == "cuda" && dtype == "float") t = create_cuda_float(shape);
+    else if (device == "cuda" && dtype == "half") t = create_cuda_half(shape);
+    else if (device == "cuda" && dtype == "int") t = create_cuda_int(shape);
+    else if (device == "cpu" && dtype == "float") t = create_cpu_float(shape);
+    else if (device == "cpu" && dtype == "half") t = create_cpu_half(shape);
+    else if (device == "cpu" && dtype == "int") t = create_cpu_int(shape);
+    else br_panic("op.create: unsupported device/dtype " + device + "/" + dtype);
+    stack.push_tensor(t);
+})
+
+BR_WORD(Zero, {
+    tensor_t t = stack.pop_tensor();
+    t->op_zero(t);
+})
+
+// ( t value -- )
+BR_WORD(Fill, {
+    double value = stack.pop_number();
+    tensor_t t = stack.pop_tensor();
+    t->op_fill(t, (float)value);
+})
+
+// ( t offset d1 .. dn n -- view )
+BR_WORD(View, {
+    auto shape = pop_shape(stack);
+    size_t offset = (size_t)stack.pop_number();
+    tensor_t t = stack.pop_tensor();
+    auto r = t->op_view(t, offset, shape);
+    stack.push_tensor(std::get<1>(r));
+})
+
+// ( dst src -- )
+BR_WORD(Copy, {
+    auto t = pop_tensors<2>(stack);
+    t[0]->op_copy(t[0], t[1]);
+})
+
+// ( x w b y -- )
+BR_WORD(Linear, {
+    auto t = pop_tensors<4>(stack);
+    t[0]->op_linear(t[0], t[1], t[2], t[3]);
+})
+
+// ( x mean var scale bias y eps -- )
+BR_WORD(Layernorm, {
+    float eps = (float)stack.pop_number();
+    auto t = pop_tensors<6>(stack);
+    t[0]->op_layernorm(t[0], t[1], t[2], t[3], t[4], t[5], eps);
+})
+
+// ( x y -- )
+BR_WORD(Transpos0213, {
+    auto t = pop_tensors<2>(stack);
+    t[0]->op_transpos_0213(t[0], t[1]);
+})
+
+// ( q k qk -- )
+BR_WORD(QueryKey, {
+    auto t = pop_tensors<3>(stack);
+    t[0]->op_qk(t[0], t[1], t[2]);
+})
+
+// ( a b c -- )  c = a + b
+BR_WORD(Add, {
+    auto t = pop_tensors<3>(stack);
+    t[0]->op_add(t[0], t[1], t[2]);
+})
+
+// ( x out -- )
+BR_WORD(Softmax, {
+    auto t = pop_tensors<2>(stack);
+    t[0]->op_softmax(t[0], t[1]);
+})
+
+// ( probs v out -- )
+BR_WORD(Attn, {
+    auto t = pop_tensors<3>(stack);
+    t[0]->op_attn(t[0], t[1], t[2]);
+})
+
+// ( x out -- )
+BR_WORD(Gelu, {
+    auto t = pop_tensors<2>(stack);
+    t[0]->op_gelu(t[0], t[1]);
+})
+
+// ( x mask lm_head out -- )
+BR_WORD(LastLogits, {
+    auto t = pop_tensors<4>(stack);
+    t[0]->op_last_logits(t[0], t[1], t[2], t[3]);
+})
+
+// ( x ids mask lm_head workspace x_g lm_head_g -- )   the reference word drops the loss value
+// (blackriver/nn.cpp:178-190); it is kept here for last_loss()
+float g_last_loss = 0.0f;
+BR_WORD(LossBackward, {
+    auto t = pop_tensors<7>(stack);
+    auto r = t[0]->op_loss_backward(t[0], t[1], t[2], t[3], t[4], t[5], t[6]);
+    if (r.index() == 1) g_last_loss = std::get<1>(r);
+})
+
+// ( dy scale bias var y dscale dbias din eps -- )
+BR_WORD(LayernormBackward, {
+    float eps = (float)stack.pop_number();
+    auto t = pop_tensors<8>(stack);
+    t[0]->op_layernorm_backward(t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7], eps);
+})
+
+// ( dy x w b x_g w_g b_g -- )
+BR_WORD(LinearBackward, {
+    auto t = pop_tensors<7>(stack);
+    t[0]->op_linear_backward(t[0], t[1], t[2], t[3], t[4], t[5], t[6]);
+})
+
+// ( dy x x_g -- )
+BR_WORD(GeluBackward, {
+    auto t = pop_tensors<3>(stack);
+    t[0]->op_gelu_backward(t[0], t[1], t[2]);
+})
+
+// ( dy attn v attn_g v_g -- )
+BR_WORD(AttnBackward, {
+    auto t = pop_tensors<5>(stack);
+    t[0]->op_attn_backward(t[0], t[1], t[2], t[3], t[4]);
+})
+
+// ( dy out x_g -- )
+BR_WORD(SoftmaxBackward, {
+    auto t = pop_tensors<3>(stack);
+    t[0]->op_softmax_backward(t[0], t[1], t[2]);
+})
+
+// ( dy attn v attn_g v_g -- )
+BR_WORD(SoftmaxAttnBackward, {
+    auto t = pop_tensors<5>(stack);
+    t[0]->op_softmax_attn_backward(t[0], t[1], t[2], t[3], t[4]);
+})
+
+// ( dS q k q_g k_g -- )
+BR_WORD(QueryKeyBackward, {
+    auto t = pop_tensors<5>(stack);
+    t[0]->op_qk_backward(t[0], t[1], t[2], t[3], t[4]);
+})
+
+BR_WORD(IoDump, {
+    tensor_t t = stack.pop_tensor();
+    t->io_dump(t);
+})
+
+// ( t file -- )
+BR_WORD(IoLoad, {
+    std::string file = stack.pop_string();
+    tensor_t t = stack.pop_tensor();
+    t->io_load(t, file.c_str());
+})
+
+BR_WORD(IoSave, {
+    std::string file = stack.pop_string();
+    tensor_t t = stack.pop_tensor();
+    t->io_save(t, file.c_str());
+})
+
+// ( t peer -- )
+BR_WORD(IoMpiRecv, {
+    int peer = (int)stack.pop_number();
+    tensor_t t = stack.pop_tensor();
+    t->io_mpi_recv(t, peer);
+})
+BR_WORD(IoMpiSend, {
+    int peer = (int)stack.pop_number();
+    tensor_t t = stack.pop_tensor();
+    t->io_mpi_send(t, peer);
+})
+BR_WORD(IoMpiBcast, {
+    int root = (int)stack.pop_number();
+    tensor_t t = stack.pop_tensor();
+    t->io_mpi_bcast(t, root);
+})
+BR_WORD(IoNcclRecv, {
+    int peer = (int)stack.pop_number();
+    tensor_t t = stack.pop_tensor();
+    t->io_nccl_recv(t, peer);
+})
+BR_WORD(IoNcclSend, {
+    int peer = (int)stack.pop_number();
+    tensor_t t = stack.pop_tensor();
+    t->io_nccl_send(t, peer);
+})
+
+}  // namespace
+
+float last_loss() { return g_last_loss; }
+
+void load_nn_words(Enviroment& env) {
+    env.insert_native_word("io.dump", IoDump::creator);
+    env.insert_native_word("io.load", IoLoad::creator);
+    env.insert_native_word("io.save", IoSave::creator);
+    env.insert_native_word("io.mpi.bcast", IoMpiBcast::creator);
+    env.insert_native_word("io.mpi.recv", IoMpiRecv::creator);
+    env.insert_native_word("io.mpi.send", IoMpiSend::creator);
+    env.insert_native_word("io.nccl.send", IoNcclSend::creator);
+    env.insert_native_word("io.nccl.recv", IoNcclRecv::creator);
+
+    env.insert_native_word("op.sync", Sync::creator);
+    env.insert_native_word("op.create", Create::creator);
+    env.insert_native_word("op.zero", Zero::creator);
+    env.insert_native_word("op.fill", Fill::creator);
+    env.insert_native_word("op.view", View::creator);
+    env.insert_native_word("op.copy", Copy::creator);
+    env.insert_native_word("op.linear", Linear::creator);
+    env.insert_native_word("op.layernorm", Layernorm::creator);
+    env.insert_native_word("op.transpos_0213", Transpos0213::creator);
+    env.insert_native_word("op.add", Add::creator);
+    env.insert_native_word("op.querykey", QueryKey::creator);
+    env.insert_native_word("op.softmax", Softmax::creator);
+    env.insert_native_word("op.attn", Attn::creator);
+    env.insert_native_word("op.gelu", Gelu::creator);
+    env.insert_native_word("op.last_logits", LastLogits::creator);
+    env.insert_native_word("op.loss_backward", LossBackward::creator);
+    env.insert_native_word("op.layernorm_backward", LayernormBackward::creator);
+    env.insert_native_word("op.linear_backward", LinearBackward::creator);
+    env.insert_native_word("op.gelu_backward", GeluBackward::creator);
+    env.insert_native_word("op.attn_backward", AttnBackward::creator);
+    env.insert_native_word("op.softmax_backward", SoftmaxBackward::creator);
+    env.insert_native_word("op.softmax_attn_backward", SoftmaxAttnBackward::creator);
+    env.insert_native_word("op.qk_backward", QueryKeyBackward::creator);
+}
+
+}  // namespace br

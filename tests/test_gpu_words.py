@@ -1,0 +1,161 @@
+"""GPU parity through the reference-facing interface: the words machine runs the generated
+model scripts (same words, tensor names and operator order as the reference's train.words) on
+device tensors, and the results are compared with the CPU oracle.
+
+Configuration of the main case: one BLOOM decoder layer forward + backward in fp32, hidden 1024,
+16 heads x 64, MLP 4096, batch 2, seq 128, valid lengths uniform in [64,128], weights N(0,0.02),
+biases 0, LayerNorm gamma 1 / beta 0, inputs and upstream gradient N(0,1), seed 0.
+Tolerance: max |err| / max |ref| <= 1e-4 per tensor (fp32 kernels)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL32 = 1e-4
+
+
+def relerr(a, b):
+    a = np.asarray(a, np.float64); b = np.asarray(b, np.float64)
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+@pytest.fixture(scope="module")
+def host():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from blackriver_b200 import host as _host
+    _host.context_boot(0, None, 256 << 20)
+    _host.collective_boot_local(0, 1)
+    yield _host
+    _host.context_shutdown()
+
+
+def make_layer(rng, hidden, trained_ln=False):
+    p = {}
+    for name in orc.LAYER_PARAMS:
+        if name.endswith("layernorm.weight"):
+            p[name] = (1 + 0.1 * rng.standard_normal(hidden)).astype(np.float32) if trained_ln else np.ones(hidden, np.float32)
+        elif name.endswith("layernorm.bias"):
+            p[name] = (0.1 * rng.standard_normal(hidden)).astype(np.float32) if trained_ln else np.zeros(hidden, np.float32)
+        elif name.endswith(".bias"):
+            n = {"query_key_value": 3, "dense_h_to_4h": 4}.get(name.split(".")[0], 1) * hidden
+            p[name] = (0.02 * rng.standard_normal(n)).astype(np.float32) if trained_ln else np.zeros(n, np.float32)
+        else:
+            o, i = {"query_key_value.weight": (3, 1), "dense.weight": (1, 1), "dense_h_to_4h.weight": (4, 1),
+                    "dense_4h_to_h.weight": (1, 4)}[name]
+            p[name] = (0.02 * rng.standard_normal((o * hidden, i * hidden))).astype(np.float32)
+    return p
+
+
+def run_layer_case(host, B, T, H, heads, lens, seed, trained_ln):
+    from blackriver_b200 import words
+    rng = np.random.default_rng(seed)
+    p = make_layer(rng, H, trained_ln)
+    x = rng.standard_normal((B, T, H)).astype(np.float32)
+    dy = rng.standard_normal((B, T, H)).astype(np.float32)
+    mask = np.zeros((B, T), np.int32)
+    for b, n in enumerate(lens):
+        mask[b, :n] = 1
+    al = orc.alibi(heads, T)
+    xm = orc.build_xmask(mask)
+    out_ref, saved = orc.layer_forward(x, p, al, xm, heads)
+    dx_ref, g_ref = orc.layer_backward(dy, p, saved, heads)
+
+    env = host.Env(2)
+    try:
+        env.execute(words.init_words(hidden=H, heads=heads, vocab=64, dtype="float", max_tokens=max(B * T, 64)))
+        env.execute(words.train_words())
+        env.execute('"cuda" $DEVICE ! create_layer_weight create_layer_grad zero_layer_grad')
+        env.execute(f"{words.var_elements(B, T, H, heads, 64, 4)} create_var  {B} {T} create_dynamic")
+        for k, v in p.items():
+            env.write(k, v)
+        env.write("xinput", x)
+        env.write("yout_g", dy)
+        env.write("alibi", al)
+        env.write("xmask", xm)
+        env.execute("layer_forward op.sync")
+        assert relerr(env.read("xa"), out_ref) <= TOL32
+        assert relerr(env.read("xll"), saved["xll"]) <= TOL32
+        env.execute("layer_backward op.sync")
+        assert relerr(env.read("xa"), dx_ref) <= TOL32
+        for k in orc.LAYER_PARAMS:
+            assert relerr(env.read(k + "_g"), g_ref[k + "_g"]) <= TOL32, k
+    finally:
+        env.close()
+
+
+def test_decoder_layer_fp32_parity_config(host):
+    rng = np.random.default_rng(0)
+    lens = rng.integers(64, 129, 2).tolist()
+    run_layer_case(host, B=2, T=128, H=1024, heads=16, lens=lens, seed=0, trained_ln=False)
+
+
+def test_decoder_layer_small_trained_layernorm_and_short_rows(host):
+    run_layer_case(host, B=3, T=20, H=64, heads=8, lens=(20, 1, 13), seed=1, trained_ln=True)
+
+
+def test_golden_block_through_words(host, golden_dir):
+    """The fixture produced by the reference's PyTorch BloomBlock, replayed through the words."""
+    import os
+    from blackriver_b200 import words
+    g = dict(np.load(os.path.join(golden_dir, "block_small.npz")))
+    heads = int(g["heads"])
+    B, T, H = g["x"].shape
+    env = host.Env(1)
+    try:
+        env.execute(words.init_words(hidden=H, heads=heads, vocab=64, dtype="float", max_tokens=64))
+        env.execute(words.train_words())
+        env.execute('"cuda" $DEVICE ! create_layer_weight create_layer_grad')
+        env.execute(f"{words.var_elements(B, T, H, heads, 64, 4)} create_var  {B} {T} create_dynamic")
+        for k in orc.LAYER_PARAMS:
+            env.write(k, g["p." + k])
+        env.write("xinput", g["x"]); env.write("yout_g", g["dy"])
+        env.write("alibi", orc.alibi(heads, T)); env.write("xmask", orc.build_xmask(g["mask"]))
+        env.execute("layer_forward op.sync")
+        assert relerr(env.read("xa"), g["out"]) <= TOL32
+        env.execute("layer_backward op.sync")
+        assert relerr(env.read("xa"), g["dx"]) <= TOL32
+        for k in orc.LAYER_PARAMS:
+            assert relerr(env.read(k + "_g"), g["g." + k]) <= TOL32, k
+    finally:
+        env.close()
+
+
+def test_loss_backward_word(host):
+    """ln_f + op.loss_backward + ln_f backward, the tail of the reference's train_0 word
+    (bloomz-7b/train.words:305-318), against the oracle; ids/mask stay on the host as there."""
+    from blackriver_b200 import words
+    rng = np.random.default_rng(5)
+    B, T, H, V = 2, 24, 64, 520
+    x = rng.standard_normal((B, T, H)).astype(np.float32)
+    w = (0.3 * rng.standard_normal((V, H))).astype(np.float32)
+    ids = rng.integers(0, V, (B, T)).astype(np.int32)
+    mask = np.zeros((B, T), np.int32); mask[0, :24] = 1; mask[1, :9] = 1
+    gamma = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32); beta = (0.1 * rng.standard_normal(H)).astype(np.float32)
+    xb_ref, _, var_ref = orc.layernorm(x, gamma, beta)
+    wg0 = rng.standard_normal((V, H)).astype(np.float32)
+    loss_ref, xg_ref, wg_ref = orc.loss_backward(xb_ref, ids, mask, w, w_g=wg0.copy())
+    dg_ref, db_ref, dx_ref = orc.layernorm_backward(xg_ref, gamma, beta, var_ref, xb_ref)
+
+    env = host.Env(1)
+    try:
+        env.execute(words.init_words(hidden=H, heads=4, vocab=V, dtype="float", max_tokens=64))
+        env.execute(words.train_words())
+        env.execute("create_main_weight create_main_grad zero_main_grad")
+        # a logits band of 7 rows forces several bands per sequence
+        env.execute(f"{words.var_elements(B, T, H, 4, V, 7)} create_var  {B} {T} create_dynamic")
+        env.write("ln_f.weight", gamma); env.write("ln_f.bias", beta); env.write("lm_head.weight", w)
+        env.write("lm_head.weight_g", wg0)
+        env.write("xa", x); env.write("ids_", ids); env.write("mask_", mask)
+        env.execute('"xa" @ "ln_mean" @ "post_ln_var" @ "ln_f.weight" @ "ln_f.bias" @ "xb" @ "LN_EPS" @ op.layernorm')
+        env.execute('"xb" @ "ids_" @ "mask_" @ "lm_head.weight" @ "all_logits" @ "xa" @ "lm_head.weight_g" @ op.loss_backward')
+        env.execute('"xa" @ "ln_f.weight" @ "ln_f.bias" @ "post_ln_var" @ "xb" @ "ln_f.weight_g" @ "ln_f.bias_g" @ "xc" @ "LN_EPS" @ op.layernorm_backward op.sync')
+        assert abs(host.last_loss() - loss_ref) <= TOL32 * abs(loss_ref)
+        assert relerr(env.read("xa"), xg_ref) <= TOL32
+        assert relerr(env.read("lm_head.weight_g"), wg_ref) <= TOL32      # accumulated onto the previous value
+        assert relerr(env.read("xc"), dx_ref) <= TOL32
+        assert relerr(env.read("ln_f.weight_g"), dg_ref) <= TOL32 and relerr(env.read("ln_f.bias_g"), db_ref) <= TOL32
+    finally:
+        env.close()
