@@ -6,11 +6,15 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <string>
+
 #include "brk.h"
 
 namespace brk {
 
 void set_cuda_error(cudaError_t e, const char* where);
+// Records a plain message for brk_last_cuda_error() (argument errors that deserve an explanation).
+void set_error_message(const std::string& msg);
 
 // Checks the launch that just happened; records the message for brk_last_cuda_error().
 inline int launch_status(const char* where) {

@@ -18,6 +18,11 @@ void set_cuda_error(cudaError_t e, const char* where) {
     g_err = std::string(where) + ": " + cudaGetErrorString(e);
 }
 
+void set_error_message(const std::string& msg) {
+    std::lock_guard<std::mutex> lk(g_err_mu);
+    g_err = msg;
+}
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;

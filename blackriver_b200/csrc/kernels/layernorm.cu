@@ -10,6 +10,9 @@
 // shared memory, dx is written, and the thread adds its columns' dgamma/dbeta terms into
 // registers.  At the end every CTA writes one partial row to the workspace and a second kernel
 // reduces the partials in a fixed order (deterministic, no atomics).
+#include <mutex>
+#include <string>
+
 #include "brk_common.cuh"
 
 namespace brk {
@@ -439,4 +442,80 @@ extern "C" int brk_layernorm_bwd(const void* dy, const void* gamma, const void* 
         return brk::ln_bwd_dispatch<__half>(dy, gamma, beta, var, y, dgamma, dbeta, dx, rows, hidden, eps, workspace,
                                             workspace_bytes, accumulate, st);
     return BRK_ATTR_ERROR;
+}
+
+// ------------------------------------------------------------------------------------------
+// LayerNorm backward without a caller-provided workspace.
+//
+// Some hosts of this library cannot give the backward pass a scratch buffer at call time: a
+// plugin that runs inside an engine which has already handed all device memory to its own pool,
+// a process confined to a fixed memory quota on a shared GPU, or code that is reached while
+// the engine is capturing a stream, where the allocation calls are not permitted.  For them the
+// per-CTA partial column sums live in a fixed array that is part of the library image.
+//
+// The array is reserved on every GPU that loads the library and stays reserved until the process
+// ends.  It is shared by all calls: each call overwrites exactly the part it reads back (every
+// CTA stores a full row of partials before the reduce kernel runs), so nothing needs clearing
+// between calls, but two calls whose kernels can overlap on the GPU (different streams, or
+// different host threads without ordering) race on it.
+// ------------------------------------------------------------------------------------------
+namespace brk {
+
+constexpr size_t LN_BWD_STATIC_BYTES = (size_t)16 << 20;  // 16 MiB: e.g. 296 CTAs x 2 x 4096 columns x 4 B = 9.25 MiB
+static __device__ __align__(256) unsigned char g_ln_bwd_static_scratch[LN_BWD_STATIC_BYTES];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel can
+// use; the device address is looked up once per device and cached.
+static void* g_ln_bwd_static_ptr[64] = {nullptr};
+static std::mutex g_ln_bwd_static_mu;
+
+static int ln_bwd_static_address(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        set_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidDevice, "brk_layernorm_bwd_static: current device");
+        return BRK_CUDA_ERROR;
+    }
+    std::lock_guard<std::mutex> lk(g_ln_bwd_static_mu);
+    if (g_ln_bwd_static_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_ln_bwd_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            set_cuda_error(e, "brk_layernorm_bwd_static: cudaGetSymbolAddress");
+            return BRK_CUDA_ERROR;
+        }
+        g_ln_bwd_static_ptr[dev] = p;
+    }
+    *out = g_ln_bwd_static_ptr[dev];
+    return BRK_OK;
+}
+
+}  // namespace brk
+
+extern "C" size_t brk_layernorm_bwd_static_capacity(void) { return brk::LN_BWD_STATIC_BYTES; }
+
+extern "C" int brk_layernorm_bwd_static(const void* dy, const void* gamma, const void* beta, const float* var, const void* y,
+                                        void* dgamma, void* dbeta, void* dx, int64_t rows, int64_t hidden, float eps,
+                                        int accumulate, int dtype, void* stream) {
+    if (!dy || !gamma || !beta || !var || !y) return BRK_INPUT_ERROR;
+    if (!dgamma || !dbeta || !dx) return BRK_OUTPUT_ERROR;
+    if (rows < 0 || hidden <= 0 || hidden > (1 << 30) || rows > 0x7fffffffLL) return BRK_ATTR_ERROR;
+    if (dtype != BRK_F32 && dtype != BRK_F16) return BRK_ATTR_ERROR;
+    if (rows == 0) return BRK_OK;
+    const size_t need = brk_layernorm_bwd_workspace_bytes(rows, hidden);
+    if (need > brk::LN_BWD_STATIC_BYTES) {
+        brk::set_error_message("brk_layernorm_bwd_static: rows x hidden needs " + std::to_string(need) +
+                               " bytes of scratch but the built-in array holds " + std::to_string(brk::LN_BWD_STATIC_BYTES) +
+                               "; use brk_layernorm_bwd with a caller workspace");
+        return BRK_ATTR_ERROR;
+    }
+    void* scratch = nullptr;
+    int rc = brk::ln_bwd_static_address(&scratch);
+    if (rc != BRK_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == BRK_F32)
+        return brk::ln_bwd_dispatch<float>(dy, gamma, beta, var, y, dgamma, dbeta, dx, rows, hidden, eps, scratch,
+                                           brk::LN_BWD_STATIC_BYTES, accumulate, st);
+    return brk::ln_bwd_dispatch<__half>(dy, gamma, beta, var, y, dgamma, dbeta, dx, rows, hidden, eps, scratch,
+                                        brk::LN_BWD_STATIC_BYTES, accumulate, st);
 }

@@ -61,6 +61,25 @@ BRK_API int brk_layernorm_bwd(const void* dy, const void* gamma, const void* bet
                       void* dgamma, void* dbeta, void* dx, int64_t rows, int64_t hidden, float eps,
                       void* workspace, size_t workspace_bytes, int accumulate, int dtype, void* stream);
 
+/* LayerNorm backward for callers that cannot hand over a workspace.  It has no counterpart in the
+ * reference.  Same arguments and results as brk_layernorm_bwd, but the partial column sums go to
+ * an array built into the library (brk_layernorm_bwd_static_capacity() bytes, 16 MiB, reserved on
+ * every GPU that loads the library for the life of the process), so the call performs no device
+ * or host allocation of any kind.  Meant for plugins living inside an engine that owns all device
+ * memory, for processes under a fixed GPU memory quota, and for code reached during stream capture,
+ * where allocation calls are not allowed.
+ *  - Problem sizes whose brk_layernorm_bwd_workspace_bytes(rows, hidden) exceeds the capacity are
+ *    refused with BRK_ATTR_ERROR and an explanatory brk_last_cuda_error() message.
+ *  - The first call on each device looks up the array's device address (once, cached); make that
+ *    first call before any stream capture begins.
+ *  - All calls share the one array.  Each call fully rewrites the part it uses, so no clearing is
+ *    needed, but calls that may execute concurrently on the GPU (two streams, unordered threads)
+ *    corrupt each other: serialise them. */
+BRK_API size_t brk_layernorm_bwd_static_capacity(void);
+BRK_API int brk_layernorm_bwd_static(const void* dy, const void* gamma, const void* beta, const float* var, const void* y,
+                             void* dgamma, void* dbeta, void* dx, int64_t rows, int64_t hidden, float eps,
+                             int accumulate, int dtype, void* stream);
+
 /* ---- bloom GELU ------------------------------------------------------------------------
  * Replaces CUDATensor::op_gelu / op_gelu_backward (blackriver/cuda_tensor.cpp:401-412,
  * 815-828) and kernels::gelu_forward / gelu_backward (blackriver/kernels/gelu.cu:46-85).
