@@ -198,6 +198,15 @@ def gemm(a, b, c, m, n, k, trans_a, trans_b, lda, ldb, ldc, batch=1, sa=0, sb=0,
     return c
 
 
+def gemm_f16(a, b, c, m, n, k, trans_a, trans_b, lda, ldb, ldc, bias=None, residual=None, ldr=0, gelu_out=None, ldg=0,
+             accumulate=False):
+    """fp16 tensor-core GEMM (tcgen05/TMEM); raises if the layout is not supported."""
+    _chk(a, b, c, bias, residual, gelu_out)
+    brk.call("brk_gemm_f16", _ptr(a), _ptr(b), _ptr(c), m, n, k, int(trans_a), int(trans_b), lda, ldb, ldc, _ptr(bias),
+             _ptr(residual), ldr, _ptr(gelu_out), ldg, int(accumulate), stream())
+    return c
+
+
 # --- operator-level compositions with the reference's semantics (blackriver/cuda_tensor.cpp) ---
 def linear(x, w, bias, out=None):
     """op_linear (:147-193): y[n,o] = sum_i x[n,i] w[o,i] + b[o]."""

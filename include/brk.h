@@ -150,6 +150,24 @@ BRK_API int brk_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n
              int64_t lda, int64_t ldb, int64_t ldc, int64_t batch, int64_t sa, int64_t sb, int64_t sc,
              float alpha, float beta, const void* bias, int dtype, void* stream);
 
+/* ---- GEMM, fp16 on the tcgen05 tensor cores ------------------------------------------------------
+ * Same row-major convention as brk_gemm (op(A) [m,k], op(B) [k,n]; trans flag = stored transposed),
+ * fp16 operands and output, fp32 accumulation in tensor memory.  This is the throughput path that
+ * stands in for kernels::LtSgemm (blackriver/kernels/LtSgemm.cu:55-126) and for the bias pass that
+ * follows it (cudnnAddTensor, blackriver/cuda_tensor.cpp:180-188), with the epilogue
+ *     out = acc (+ bias[n]) (+ residual[m,n]) (+ C[m,n] when accumulate != 0);  C = fp16(out);
+ *     gelu_out = fp16(bloom_gelu(out)) when gelu_out != NULL.
+ * Requirements: lda, ldb multiples of 8 elements and a, b 16-byte aligned (TMA); any m, n, k.
+ * brk_gemm_f16_supported() answers whether a problem meets them (callers fall back to brk_gemm).
+ * The kernels bound every internal wait; brk_gemm_f16_status() (synchronous) returns non-zero if
+ * one of them gave up since the last query. */
+BRK_API int brk_gemm_f16_supported(int64_t m, int64_t n, int64_t k, int trans_a, int trans_b, int64_t lda, int64_t ldb,
+                           const void* a, const void* b);
+BRK_API int brk_gemm_f16(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_a, int trans_b,
+                 int64_t lda, int64_t ldb, int64_t ldc, const void* bias, const void* residual, int64_t ldr,
+                 void* gelu_out, int64_t ldg, int accumulate, void* stream);
+BRK_API int brk_gemm_f16_status(void);
+
 #ifdef __cplusplus
 }
 #endif
