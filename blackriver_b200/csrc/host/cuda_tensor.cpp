@@ -56,6 +56,16 @@ struct Scratch {
     }
 };
 
+// One GEMM, routed to the tensor-core kernel when the element type is fp16 and the layout meets
+// TMA's rules (single problem, alpha 1, beta 0 or 1), otherwise to the general SIMT kernel.
+template <DataType DT>
+inline int gemm_any(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int ta, int tb, int64_t lda,
+                    int64_t ldb, int64_t ldc, float beta, const void* bias) {
+    if (DT == DataType::F16 && (beta == 0.0f || beta == 1.0f) && brk_gemm_f16_supported(m, n, k, ta, tb, lda, ldb, a, b))
+        return brk_gemm_f16(a, b, c, m, n, k, ta, tb, lda, ldb, ldc, bias, nullptr, 0, nullptr, 0, beta == 1.0f ? 1 : 0, sptr());
+    return brk_gemm(a, b, c, m, n, k, ta, tb, lda, ldb, ldc, 1, 0, 0, 0, 1.0f, beta, bias, brk_dtype<DT>(), sptr());
+}
+
 }  // namespace
 
 template <DataType DT>
@@ -196,8 +206,7 @@ ComputingReturn CUDATensor<DT>::op_linear(tensor_t self, tensor_t w, tensor_t bi
     if ((int64_t)w->shape()[1] != in || (int64_t)bias->items() != out) return OP_INPUT_ERROR;
     int64_t n = (int64_t)self->items() / in;
     if ((int64_t)y->items() != n * out) return OP_OUTPUT_ERROR;
-    return ret(brk_gemm(mem_, w->data(), y->data(), n, out, in, 0, 1, in, in, out, 1, 0, 0, 0, 1.0f, 0.0f, bias->data(),
-                        brk_dtype<DT>(), sptr()));
+    return ret(gemm_any<DT>(mem_, w->data(), y->data(), n, out, in, 0, 1, in, in, out, 0.0f, bias->data()));
 }
 
 template <DataType DT>
@@ -348,13 +357,13 @@ LossReturn CUDATensor<DT>::op_loss_backward(tensor_t self, tensor_t ids_, tensor
         const unsigned char* x = (const unsigned char*)mem_ + r0 * hidden * es;
         unsigned char* dx = (unsigned char*)x_g->data() + r0 * hidden * es;
         // logits = x W^T
-        st = brk_gemm(x, lm_head->data(), logits, rows, vocab, hidden, 0, 1, hidden, hidden, vocab, 1, 0, 0, 0, 1.0f, 0.0f, nullptr, dt, sptr());
+        st = gemm_any<DT>(x, lm_head->data(), logits, rows, vocab, hidden, 0, 1, hidden, hidden, vocab, 0.0f, nullptr);
         // row losses and dlogits (in place)
         if (st == BRK_OK) st = brk_logsoftmax_nll_fwd_bwd(logits, d_target + r0, d_rowloss + r0, logits, rows, vocab, scale, dt, sptr());
         // x_g = dlogits W
-        if (st == BRK_OK) st = brk_gemm(logits, lm_head->data(), dx, rows, hidden, vocab, 0, 0, vocab, hidden, hidden, 1, 0, 0, 0, 1.0f, 0.0f, nullptr, dt, sptr());
+        if (st == BRK_OK) st = gemm_any<DT>(logits, lm_head->data(), dx, rows, hidden, vocab, 0, 0, vocab, hidden, hidden, 0.0f, nullptr);
         // W_g += dlogits^T x
-        if (st == BRK_OK) st = brk_gemm(logits, x, d_wg, vocab, hidden, rows, 1, 0, vocab, hidden, hidden, 1, 0, 0, 0, 1.0f, 1.0f, nullptr, dt, sptr());
+        if (st == BRK_OK) st = gemm_any<DT>(logits, x, d_wg, vocab, hidden, rows, 1, 0, vocab, hidden, hidden, 1.0f, nullptr);
     }
     if (st == BRK_OK) st = brk_sum_f32(d_rowloss, d_total, n, sptr());
     float total = 0.0f;
@@ -401,8 +410,8 @@ ComputingReturn CUDATensor<DT>::op_linear_backward(tensor_t self, tensor_t x, te
     if (x_g->items() != x->items() || weight_g->items() != weight->items() || (int64_t)bias_g->items() != out) return OP_OUTPUT_ERROR;
     constexpr int dt = brk_dtype<DT>();
     int st = brk_colsum(mem_, bias_g->data(), n, out, 0, dt, sptr());
-    if (st == BRK_OK) st = brk_gemm(mem_, x->data(), weight_g->data(), out, in, n, 1, 0, out, in, in, 1, 0, 0, 0, 1.0f, 0.0f, nullptr, dt, sptr());
-    if (st == BRK_OK) st = brk_gemm(mem_, weight->data(), x_g->data(), n, in, out, 0, 0, out, in, in, 1, 0, 0, 0, 1.0f, 0.0f, nullptr, dt, sptr());
+    if (st == BRK_OK) st = gemm_any<DT>(mem_, x->data(), weight_g->data(), out, in, n, 1, 0, out, in, in, 0.0f, nullptr);
+    if (st == BRK_OK) st = gemm_any<DT>(mem_, weight->data(), x_g->data(), n, in, out, 0, 0, out, in, in, 0.0f, nullptr);
     return ret(st);
 }
 

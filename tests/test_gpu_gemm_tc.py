@@ -1,0 +1,101 @@
+"""tcgen05 / TMEM fp16 GEMM through the C ABI against fp32 references.
+
+Small problems are checked against the CPU oracle's linear operator, larger ones against a
+float64 numpy product of the same fp16-rounded operands.  fp16 storage tolerance from the task:
+2e-2 (the observed error is the fp16 rounding of the output, ~4e-4).  After every case the
+kernel's status word must be 0 (no bounded wait gave up)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL16 = 2e-2
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from blackriver_b200 import ops as _ops
+    return _ops
+
+
+def relerr(a, b):
+    a = np.asarray(a, np.float64); b = np.asarray(b, np.float64)
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def h16(a):
+    return np.asarray(a, np.float32).astype(np.float16)
+
+
+def gelu_ref(x):
+    return x * 0.5 * (1 + np.tanh(0.79788456 * x * (1 + 0.044715 * x * x)))
+
+
+def run(ops, m, n, k, ta, tb, seed, bias=False, res=False, acc=False, gelu=False):
+    from blackriver_b200 import brk
+    rng = np.random.default_rng(seed)
+    A = h16(rng.standard_normal((k, m) if ta else (m, k)))
+    B = h16(rng.standard_normal((n, k) if tb else (k, n)))
+    C0 = h16(rng.standard_normal((m, n)))
+    bs = h16(rng.standard_normal(n)) if bias else None
+    R = h16(rng.standard_normal((m, n))) if res else None
+    dev = lambda x: None if x is None else torch.from_numpy(x).cuda()
+    C = dev(C0); G = torch.empty_like(C) if gelu else None
+    ops.gemm_f16(dev(A), dev(B), C, m, n, k, ta, tb, A.shape[1], B.shape[1], n, bias=dev(bs), residual=dev(R), ldr=n,
+                 gelu_out=G, ldg=n, accumulate=acc)
+    torch.cuda.synchronize()
+    assert brk.lib().brk_gemm_f16_status() == 0
+    a = (A.T if ta else A).astype(np.float64); b = (B.T if tb else B).astype(np.float64)
+    ref = a @ b
+    if bias: ref = ref + bs.astype(np.float64)
+    if res: ref = ref + R.astype(np.float64)
+    if acc: ref = ref + C0.astype(np.float64)
+    assert relerr(C.float().cpu().numpy(), ref) <= TOL16
+    if gelu:
+        assert relerr(G.float().cpu().numpy(), gelu_ref(ref)) <= TOL16
+
+
+@pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 1), (1, 0)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 512, 128), (200, 328, 136), (130, 72, 40), (1, 8, 8), (384, 1000, 264)])
+def test_all_layouts_and_tails(ops, m, n, k, ta, tb):
+    if (ta and m % 8) or (not tb and n % 8):
+        pytest.skip("this storage order needs a leading dimension that is a multiple of 8")
+    run(ops, m, n, k, ta, tb, seed=m + n + k)
+
+
+def test_epilogues(ops):
+    run(ops, 256, 512, 128, 0, 1, 1, bias=True)
+    run(ops, 256, 512, 128, 0, 1, 2, bias=True, res=True)
+    run(ops, 256, 512, 128, 1, 0, 3, acc=True)
+    run(ops, 200, 328, 136, 0, 1, 4, bias=True, res=True, acc=True, gelu=True)
+
+
+def test_matches_oracle_linear_and_backward(ops):
+    rng = np.random.default_rng(7)
+    n_tok, i, o = 96, 128, 192
+    x = h16(rng.standard_normal((n_tok, i))); w = h16(rng.standard_normal((o, i)) * 0.1); b = h16(rng.standard_normal(o))
+    dy = h16(rng.standard_normal((n_tok, o)))
+    dev = lambda a: torch.from_numpy(a).cuda()
+    y = torch.empty((n_tok, o), dtype=torch.float16, device="cuda")
+    ops.gemm_f16(dev(x), dev(w), y, n_tok, o, i, 0, 1, i, i, o, bias=dev(b))
+    assert relerr(y.float().cpu().numpy(), orc.linear(x.astype(np.float32), w.astype(np.float32), b.astype(np.float32))) <= TOL16
+    xg_ref, wg_ref, _ = orc.linear_backward(dy.astype(np.float32), x.astype(np.float32), w.astype(np.float32))
+    wg = torch.empty((o, i), dtype=torch.float16, device="cuda"); xg = torch.empty((n_tok, i), dtype=torch.float16, device="cuda")
+    ops.gemm_f16(dev(dy), dev(x), wg, o, i, n_tok, 1, 0, o, i, i)       # W_g = dy^T x
+    ops.gemm_f16(dev(dy), dev(w), xg, n_tok, i, o, 0, 0, o, i, i)       # x_g = dy W
+    assert relerr(wg.float().cpu().numpy(), wg_ref) <= TOL16 and relerr(xg.float().cpu().numpy(), xg_ref) <= TOL16
+
+
+def test_model_shape_against_numpy(ops):
+    run(ops, 2048, 4096, 4096, 0, 1, 11, bias=True)
+
+
+def test_rejects_unsupported_layout(ops):
+    from blackriver_b200 import brk
+    a = torch.zeros(64, device="cuda", dtype=torch.float16)
+    assert brk.lib().brk_gemm_f16_supported(8, 8, 12, 0, 1, 12, 12, a.data_ptr(), a.data_ptr()) == 0
+    assert brk.raw("brk_gemm_f16", a.data_ptr(), a.data_ptr(), a.data_ptr(), 8, 8, 12, 0, 1, 12, 12, 8, 0, 0, 0, 0, 0, 0, 0) == brk.ATTR_ERROR

@@ -96,6 +96,41 @@ def test_decoder_layer_small_trained_layernorm_and_short_rows(host):
     run_layer_case(host, B=3, T=20, H=64, heads=8, lens=(20, 1, 13), seed=1, trained_ln=True)
 
 
+def test_decoder_layer_fp16_storage(host):
+    """Same layer in fp16 storage (tensor-core GEMMs for the linear layers) against the fp32 oracle:
+    <= 2e-2 on activations and gradients."""
+    from blackriver_b200 import words
+    B, T, H, heads = 2, 128, 1024, 16
+    rng = np.random.default_rng(3)
+    p = make_layer(rng, H, trained_ln=False)
+    r16 = lambda a: a.astype(np.float16).astype(np.float32)
+    p = {k: r16(v) for k, v in p.items()}
+    x = r16(rng.standard_normal((B, T, H)).astype(np.float32))
+    dy = r16(rng.standard_normal((B, T, H)).astype(np.float32))
+    mask = np.zeros((B, T), np.int32); mask[0, :128] = 1; mask[1, :77] = 1
+    al = orc.alibi(heads, T); xm = orc.build_xmask(mask)
+    out_ref, saved = orc.layer_forward(x, p, al, xm, heads)
+    dx_ref, g_ref = orc.layer_backward(dy, p, saved, heads)
+    env = host.Env(1)
+    try:
+        env.execute(words.init_words(hidden=H, heads=heads, vocab=64, dtype="half", max_tokens=256))
+        env.execute(words.train_words())
+        env.execute('"cuda" $DEVICE ! create_layer_weight create_layer_grad')
+        env.execute(f"{words.var_elements(B, T, H, heads, 64, 4)} create_var  {B} {T} create_dynamic")
+        for k, v in p.items():
+            env.write(k, v)
+        env.write("xinput", x); env.write("yout_g", dy); env.write("alibi", al)
+        env.write("xmask", np.maximum(xm, -60000.0))      # -FLT_MAX does not exist in fp16
+        env.execute("layer_forward op.sync")
+        assert relerr(env.read("xa"), out_ref) <= 2e-2
+        env.execute("layer_backward op.sync")
+        assert relerr(env.read("xa"), dx_ref) <= 2e-2
+        for k in orc.LAYER_PARAMS:
+            assert relerr(env.read(k + "_g"), g_ref[k + "_g"]) <= 2e-2, k
+    finally:
+        env.close()
+
+
 def test_golden_block_through_words(host, golden_dir):
     """The fixture produced by the reference's PyTorch BloomBlock, replayed through the words."""
     import os
