@@ -168,6 +168,24 @@ BRK_API int brk_gemm_f16(const void* a, const void* b, void* c, int64_t m, int64
                  void* gelu_out, int64_t ldg, int accumulate, void* stream);
 BRK_API int brk_gemm_f16_status(void);
 
+/* ---- fused attention (fp16, tcgen05) ------------------------------------------------------------
+ * Replaces the op_qk -> op_add(alibi) -> op_add(xmask) -> op_softmax -> op_attn chain of layer_forward
+ * (bloomz-7b/train.words:147-166; blackriver/cuda_tensor.cpp:207-232, 278-398) and the four
+ * op_transpos_0213 calls around it, plus the host-built ALiBi and additive mask tensors
+ * (blackriver/train_bloom.cpp:58-90), with one kernel:
+ *     P = softmax(Q K^T / sqrt(d) + slopes[h] * key_index) over keys with key <= query and key < lens[b]
+ *     out = P V
+ * q, k, v: token-major fp16, head h at columns h*head_dim.., common row stride ld_qkv (so the three
+ * thirds of a fused QKV projection [batch*tokens, 3*heads*head_dim] can be passed as q, q+H, q+2H).
+ * out: token-major [batch*tokens, ld_out].  lse: [batch, heads, tokens] fp32 (may be NULL when no
+ * backward follows).  lens: [batch] int32 valid lengths (right padding, the assumption the
+ * reference mask builder makes) or NULL for full length; slopes: [heads] fp32 or NULL.
+ * head_dim 64 or 128; ld_qkv a multiple of 8; pointers 16-byte aligned. */
+BRK_API int brk_flash_attn_fwd(const void* q, const void* k, const void* v, int64_t ld_qkv, void* out, int64_t ld_out,
+                       float* lse, const int32_t* lens, const float* slopes, int batch, int tokens, int heads,
+                       int head_dim, void* stream);
+BRK_API int brk_flash_attn_status(void);
+
 #ifdef __cplusplus
 }
 #endif
