@@ -1,0 +1,920 @@
+// Fused causal attention forward with ALiBi and right-padding masks on the tcgen05 tensor cores.
+//
+//   S = Q K^T / sqrt(d) + slope_h * key_index,   keys allowed:  key <= query  and  key < len[b]
+//   P = softmax(S),   O = P V
+//
+// Q, K, V are read in place from token-major activations ([batch*tokens, ld] with head h at
+// columns h*d .. h*d+d-1, e.g. the three thirds of the fused QKV projection output), O is
+// written token-major too, so the four [B,T,h,d] <-> [B,h,T,d] transposes of the unfused path
+// and the T x T score / mask tensors never exist.  Also emitted: the row log-sum-exp [B,h,T]
+// that the backward kernels need.
+//
+// One CTA per (128-query block, head, batch), 192 threads:
+//   warp 0     TMA producer (Q once, then K / V tiles of 128 keys through 2-stage rings);
+//   warp 1     issues tcgen05.mma: S = Q K_j^T into one of two TMEM score buffers, O += P V_j;
+//   warps 2-5  one thread per query row: tcgen05.ld the scores, mask, exponentiate, write P as
+//              fp16 into shared memory in the tensor core's swizzled operand layout.
+// Softmax is two-sweep: sweep A accumulates the row maximum and normaliser over all key blocks,
+// sweep B recomputes the scores and feeds normalised probabilities to the second contraction, so
+// the output accumulator in TMEM never needs rescaling.  The score contraction runs twice; it is
+// a third of the attention FLOPs, which are a few per cent of a decoder layer.
+// Every mbarrier wait is bounded (see brk_ptx.cuh); a give-up raises g_attn_error.
+#include <mutex>
+
+#include "brk_common.cuh"
+#include "brk_ptx.cuh"
+#include "brk_attn.cuh"
+
+namespace brk {
+
+using namespace ptx;
+
+__device__ int g_attn_error = 0;
+
+struct AttnFwdParams {
+    __half* out;
+    float* lse;            // [batch, heads, tokens], natural log
+    const int32_t* lens;   // [batch] or null
+    const float* slopes;   // [heads] or null
+    int64_t ld_out;
+    int batch, tokens, heads;
+    float scale_log2;      // log2(e) / sqrt(d)
+};
+
+template <int D>
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, AttnFwdParams p) {
+    constexpr uint32_t TILE_BYTES = 128 * D * 2;          // Q, K, V tiles: 128 rows x D
+    constexpr uint32_t P_BYTES = 128 * AT_BKV * 2;
+    constexpr int KSTAGES = 2, VSTAGES = 2;
+    constexpr uint32_t TMEM_COLS = 512;                   // S0 [0,128) S1 [128,256) O [256,256+D)
+    constexpr uint32_t IDESC_S = make_idesc_f16_f32(128, AT_BKV, 0, 0);
+    constexpr uint32_t IDESC_PV = make_idesc_f16_f32(128, D, 0, 1);
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = base;
+    unsigned char* sK = sQ + TILE_BYTES;
+    unsigned char* sV = sK + KSTAGES * TILE_BYTES;
+    unsigned char* sP = sV + VSTAGES * TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+    uint64_t* q_full = bars;                 // 1
+    uint64_t* k_full = bars + 1;             // KSTAGES
+    uint64_t* k_empty = k_full + KSTAGES;
+    uint64_t* v_full = k_empty + KSTAGES;    // VSTAGES
+    uint64_t* v_empty = v_full + VSTAGES;
+    uint64_t* s_full = v_empty + VSTAGES;    // 2
+    uint64_t* s_empty = s_full + 2;          // 2
+    uint64_t* p_full = s_empty + 2;          // 1
+    uint64_t* p_empty = p_full + 1;          // 1
+    uint64_t* o_full = p_empty + 1;          // 1
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(o_full + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // heavy (late) query blocks are scheduled first
+    const int qblk = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int head = blockIdx.y, b = blockIdx.z;
+    const int q0 = qblk * AT_BQ;
+    const int len = p.lens ? min(max(p.lens[b], 0), p.tokens) : p.tokens;
+    const int key_end = min(q0 + AT_BQ, len);                     // keys beyond are masked for every row of the tile
+    const int nkb = key_end > 0 ? (key_end + AT_BKV - 1) / AT_BKV : 0;
+    const int row_base = b * p.tokens;                             // first row of this sequence in the [B*T, ld] matrices
+    const int col = head * D;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < KSTAGES; s++) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+        for (int s = 0; s < VSTAGES; s++) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128); }
+        mbar_init(p_full, 128);
+        mbar_init(p_empty, 1);
+        mbar_init(o_full, 1);
+        fence_barrier_init();
+        prefetch_tensormap(&tmap_q);
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+    const uint32_t tmem_o = tmem_base + 256;
+
+    if (nkb > 0) {
+        if (warp == 0) {
+            // ---------------- TMA producer ----------------
+            if (lane == 0) {
+                bool ok = true;
+                mbar_arrive_expect_tx(q_full, TILE_BYTES);
+#pragma unroll
+                for (int a = 0; a < D / 64; a++) tma_load_2d(sQ + a * 16384, &tmap_q, q_full, col + a * 64, row_base + q0);
+                uint32_t kit = 0, vit = 0;
+                for (int sweep = 0; sweep < 2 && ok; sweep++) {
+                    for (int j = 0; j < nkb && ok; j++) {
+                        {
+                            const int s = kit % KSTAGES;
+                            ok = mbar_wait(&k_empty[s], ((kit / KSTAGES) & 1) ^ 1);
+                            if (!ok) break;
+                            mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
+#pragma unroll
+                            for (int a = 0; a < D / 64; a++)
+                                tma_load_2d(sK + s * TILE_BYTES + a * 16384, &tmap_k, &k_full[s], col + a * 64, row_base + j * AT_BKV);
+                            kit++;
+                        }
+                        if (sweep == 1) {
+                            const int s = vit % VSTAGES;
+                            ok = mbar_wait(&v_empty[s], ((vit / VSTAGES) & 1) ^ 1);
+                            if (!ok) break;
+                            mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
+#pragma unroll
+                            for (int a = 0; a < D / 64; a++)
+                                tma_load_2d(sV + s * TILE_BYTES + a * 16384, &tmap_v, &v_full[s], col + a * 64, row_base + j * AT_BKV);
+                            vit++;
+                        }
+                    }
+                }
+                if (!ok) atomicExch(&g_attn_error, 1);
+            }
+        } else if (warp == 1) {
+            // ---------------- MMA issuer ----------------
+            if (lane == 0) {
+                bool ok = mbar_wait(q_full, 0);
+                tcgen05_fence_after();
+                const uint32_t q_addr = smem_u32(sQ);
+                const uint32_t p_addr = smem_u32(sP);
+                uint32_t kit = 0, vit = 0, sit = 0;   // K tiles consumed, V tiles consumed, score tiles produced
+                auto issue_scores = [&](void) -> bool {
+                    const int s = kit % KSTAGES, sb = sit & 1;
+                    if (!mbar_wait(&s_empty[sb], ((sit >> 1) & 1) ^ 1)) return false;
+                    if (!mbar_wait(&k_full[s], (kit / KSTAGES) & 1)) return false;
+                    tcgen05_fence_after();
+                    const uint32_t k_addr = smem_u32(sK + s * TILE_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; kk++) {
+                        const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+                        umma_f16_ss(tmem_base + sb * 128, make_smem_desc_sw128(q_addr + off, 16, 1024),
+                                    make_smem_desc_sw128(k_addr + off, 16, 1024), IDESC_S, kk != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&k_empty[s]);
+                    umma_commit(&s_full[sb]);
+                    kit++;
+                    sit++;
+                    return true;
+                };
+                // sweep A: scores only
+                for (int j = 0; j < nkb && ok; j++) ok = issue_scores();
+                // sweep B: scores one block ahead of the P V contraction
+                if (ok) ok = issue_scores();
+                for (int j = 0; j < nkb && ok; j++) {
+                    if (j + 1 < nkb) ok = issue_scores();
+                    if (!ok) break;
+                    const int s = vit % VSTAGES;
+                    ok = mbar_wait(&v_full[s], (vit / VSTAGES) & 1) && mbar_wait(p_full, j & 1);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t v_addr = smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < AT_BKV / 16; kk++) {
+                        // A = P [128 q x 128 keys], K-major; B = V [128 keys x D], d contiguous (MN-major)
+                        const uint64_t da = make_smem_desc_sw128(p_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+                        const uint64_t db = make_smem_desc_sw128(v_addr + kk * 2048, 16384, 1024);
+                        umma_f16_ss(tmem_o, da, db, IDESC_PV, (j | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&v_empty[s]);
+                    umma_commit(p_empty);
+                    vit++;
+                }
+                if (ok) umma_commit(o_full);
+                if (!ok) atomicExch(&g_attn_error, 2);
+            }
+        } else {
+            // ---------------- softmax / epilogue: one thread per query row ----------------
+            const int quarter = warp & 3;
+            const int r = quarter * 32 + lane;          // row inside the tile == TMEM lane
+            const int qi = q0 + r;                       // query position in the sequence
+            const int klimit = min(qi + 1, len);         // keys [0, klimit) are visible to this row
+            const float slope2 = p.slopes ? p.slopes[head] * 1.4426950408889634f : 0.0f;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            float m = -INFINITY, l = 0.0f;
+            uint32_t sit = 0;
+            bool ok = true;
+            // sweep A
+            for (int j = 0; j < nkb && ok; j++, sit++) {
+                const int sb = sit & 1;
+                ok = mbar_wait(&s_full[sb], (sit >> 1) & 1);
+                if (!ok) break;
+                tcgen05_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < AT_BKV; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(lane_addr + sb * 128 + c0, v);
+                    tmem_ld_wait();
+                    const int kbase = j * AT_BKV + c0;
+                    float t[32];
+                    float cm = m;
+#pragma unroll
+                    for (int e = 0; e < 32; e++) {
+                        const int kj = kbase + e;
+                        t[e] = kj < klimit ? fmaf(__uint_as_float(v[e]), p.scale_log2, slope2 * (float)kj) : -INFINITY;
+                        cm = fmaxf(cm, t[e]);
+                    }
+                    if (cm > m) {
+                        l *= fast_exp2(m - cm);
+                        m = cm;
+                    }
+                    if (m > -INFINITY) {
+#pragma unroll
+                        for (int e = 0; e < 32; e++) l += fast_exp2(t[e] - m);
+                    }
+                }
+                tcgen05_fence_before();
+                mbar_arrive(&s_empty[sb]);
+            }
+            const float lse2 = (l > 0.0f) ? m + __log2f(l) : 0.0f;
+            if (ok && qi < p.tokens && p.lse)
+                p.lse[((int64_t)b * p.heads + head) * p.tokens + qi] = lse2 * 0.6931471805599453f;
+            // sweep B
+            for (int j = 0; j < nkb && ok; j++, sit++) {
+                const int sb = sit & 1;
+                ok = mbar_wait(&s_full[sb], (sit >> 1) & 1);
+                if (!ok) break;
+                if (j > 0) ok = mbar_wait(p_empty, (j - 1) & 1);   // previous P consumed by the tensor core
+                if (!ok) break;
+                tcgen05_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < AT_BKV; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(lane_addr + sb * 128 + c0, v);
+                    tmem_ld_wait();
+                    const int kbase = j * AT_BKV + c0;
+#pragma unroll
+                    for (int g = 0; g < 4; g++) {
+                        uint4 pk;
+                        __half2* h2 = reinterpret_cast<__half2*>(&pk);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const int k0 = kbase + g * 8 + e * 2;
+                            float p0 = k0 < klimit ? fast_exp2(fmaf(__uint_as_float(v[g * 8 + e * 2]), p.scale_log2, slope2 * (float)k0) - lse2) : 0.0f;
+                            float p1 = k0 + 1 < klimit ? fast_exp2(fmaf(__uint_as_float(v[g * 8 + e * 2 + 1]), p.scale_log2, slope2 * (float)(k0 + 1)) - lse2) : 0.0f;
+                            h2[e] = __floats2half2_rn(p0, p1);
+                        }
+                        *reinterpret_cast<uint4*>(sP + sw128_offset(r, c0 + g * 8)) = pk;
+                    }
+                }
+                tcgen05_fence_before();
+                mbar_arrive(&s_empty[sb]);
+                fence_proxy_async();          // make the generic-proxy writes of P visible to the tensor core
+                mbar_arrive(p_full);
+            }
+            // epilogue: O -> fp16 -> global, token-major
+            if (ok) ok = mbar_wait(o_full, 0);
+            if (ok) {
+                tcgen05_fence_after();
+                __half* orow = p.out + (int64_t)(row_base + qi) * p.ld_out + col;
+                const bool vec = (p.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(lane_addr + 256 + c0, v);
+                    tmem_ld_wait();
+                    if (qi < p.tokens) {
+                        if (vec) {
+#pragma unroll
+                            for (int g = 0; g < 4; g++) {
+                                Vec<__half> o;
+#pragma unroll
+                                for (int e = 0; e < 8; e++) o.v[e] = __uint_as_float(v[g * 8 + e]);
+                                o.store(orow + c0 + g * 8);
+                            }
+                        } else {
+                            for (int e = 0; e < 32; e++) orow[c0 + e] = __float2half_rn(__uint_as_float(v[e]));
+                        }
+                    }
+                }
+            }
+            if (!ok && lane == 0) atomicExch(&g_attn_error, 3);
+        }
+    } else if (warp >= 2) {
+        // no visible key for any row of this tile (len == 0): zero output, lse 0
+        const int r = (warp & 3) * 32 + lane, qi = q0 + r;
+        if (qi < p.tokens) {
+            __half* orow = p.out + (int64_t)(row_base + qi) * p.ld_out + col;
+            for (int e = 0; e < D; e++) orow[e] = __float2half_rn(0.0f);
+            if (p.lse) p.lse[((int64_t)b * p.heads + head) * p.tokens + qi] = 0.0f;
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int D>
+static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnFwdParams& p, cudaStream_t st) {
+    constexpr size_t smem = 1024 + (size_t)128 * D * 2 * 5 + 128 * AT_BKV * 2 + 256;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] { attr_err = cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
+    if (attr_err != cudaSuccess) {
+        set_cuda_error(attr_err, "attn_fwd smem attribute");
+        return BRK_CUDA_ERROR;
+    }
+    dim3 grid((unsigned)((p.tokens + AT_BQ - 1) / AT_BQ), (unsigned)p.heads, (unsigned)p.batch);
+    attn_fwd_kernel<D><<<grid, AT_THREADS, smem, st>>>(tq, tk, tv, p);
+    return launch_status("attn_fwd_kernel");
+}
+
+
+// ==========================================================================================
+// backward
+//   delta_i = sum_d dO_i O_i                      (small pre-pass, [B,h,T] fp32)
+//   P_ij  = exp(s_ij - lse_i)  (0 where masked)   recomputed from Q, K and the saved lse
+//   dV_j  = sum_i P_ij dO_i            dP_ij = dO_i . V_j          dS_ij = P_ij (dP_ij - delta_i)
+//   dQ_i  = (1/sqrt d) sum_j dS_ij K_j            dK_j = (1/sqrt d) sum_i dS_ij Q_i
+// Two kernels, both with the forward's structure (TMA producer warp, one MMA-issuing thread,
+// 128 row-owner threads): the first owns a 128-key block and walks the query blocks at or after
+// it, accumulating dK and dV in tensor memory; the second owns a 128-query block and walks the
+// key blocks before it, accumulating dQ.  P and dS are written to shared memory once per tile
+// pair and reach the tensor core either as K-major operands (dQ) or, transposed for free through
+// the MN-major descriptor, as the A operand of dV = P^T dO and dK = dS^T Q.
+// ==========================================================================================
+struct AttnBwdParams {
+    const float* lse;      // [B,h,T] natural log, from the forward
+    const float* delta;    // [B,h,T]
+    const int32_t* lens;
+    const float* slopes;
+    __half* dq;
+    __half* dk;
+    __half* dv;
+    int64_t ld_g;
+    int batch, tokens, heads;
+    float scale_log2;      // log2(e)/sqrt(d)
+    float scale;           // 1/sqrt(d)
+};
+
+// one warp per (token row, head): delta = sum_d dO * O
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __half* out, const __half* dout, int64_t ld, float* delta, int batch, int tokens, int heads, int d) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t total = (int64_t)batch * tokens * heads;
+    if (w >= total) return;
+    const int h = (int)(w % heads);
+    const int64_t row = w / heads;
+    const int b = (int)(row / tokens), t = (int)(row % tokens);
+    const __half* o = out + row * ld + (int64_t)h * d;
+    const __half* g = dout + row * ld + (int64_t)h * d;
+    float s = 0.0f;
+    for (int e = lane * 2; e < d; e += 64) {
+        float2 a = __half22float2(*reinterpret_cast<const __half2*>(o + e));
+        float2 c = __half22float2(*reinterpret_cast<const __half2*>(g + e));
+        s += a.x * c.x + a.y * c.y;
+    }
+    s = warp_sum(s);
+    if (lane == 0) delta[((int64_t)b * heads + h) * tokens + t] = s;
+}
+
+// writes 32 consecutive fp16 values of row r, columns [c0, c0+32) of a swizzled operand tile
+__device__ __forceinline__ void store_tile_chunk(unsigned char* tile, int r, int c0, const float (&x)[32]) {
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        uint4 pk;
+        __half2* h2 = reinterpret_cast<__half2*>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; e++) h2[e] = __floats2half2_rn(x[g * 8 + e * 2], x[g * 8 + e * 2 + 1]);
+        *reinterpret_cast<uint4*>(tile + sw128_offset(r, c0 + g * 8)) = pk;
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do, AttnBwdParams p) {
+    constexpr uint32_t TILE_BYTES = 128 * D * 2;
+    constexpr uint32_t PT_BYTES = 128 * 128 * 2;
+    constexpr uint32_t TMEM_COLS = 512;   // S [0,128) dP [128,256) dV [256,256+D) dK [256+D,256+2D)
+    constexpr uint32_t IDESC_S = make_idesc_f16_f32(128, 128, 0, 0);
+    constexpr uint32_t IDESC_ACC = make_idesc_f16_f32(128, D, 1, 1);
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sK = base;
+    unsigned char* sV = sK + TILE_BYTES;
+    unsigned char* sQ = sV + TILE_BYTES;
+    unsigned char* sDO = sQ + TILE_BYTES;
+    unsigned char* sP = sDO + TILE_BYTES;
+    unsigned char* sDS = sP + PT_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + PT_BYTES);
+    uint64_t* kv_full = bars;
+    uint64_t* qdo_full = bars + 1;
+    uint64_t* qdo_empty = bars + 2;
+    uint64_t* sdp_full = bars + 3;
+    uint64_t* sdp_empty = bars + 4;
+    uint64_t* pds_full = bars + 5;
+    uint64_t* pds_empty = bars + 6;
+    uint64_t* acc_full = bars + 7;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int jblk = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+    const int k0 = jblk * AT_BKV;
+    const int len = p.lens ? min(max(p.lens[b], 0), p.tokens) : p.tokens;
+    const int nqb = (p.tokens + AT_BQ - 1) / AT_BQ;
+    const int row_base = b * p.tokens;
+    const int col = head * D;
+    const bool active = k0 < len;           // otherwise no query sees any key of this block
+    const int niter = active ? nqb - jblk : 0;
+
+    if (threadIdx.x == 0) {
+        mbar_init(kv_full, 1);
+        mbar_init(qdo_full, 1);
+        mbar_init(qdo_empty, 1);
+        mbar_init(sdp_full, 1);
+        mbar_init(sdp_empty, 128);
+        mbar_init(pds_full, 128);
+        mbar_init(pds_empty, 1);
+        mbar_init(acc_full, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    if (active) {
+        if (warp == 0) {
+            if (lane == 0) {
+                bool ok = true;
+                mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+#pragma unroll
+                for (int a = 0; a < D / 64; a++) {
+                    tma_load_2d(sK + a * 16384, &tmap_k, kv_full, col + a * 64, row_base + k0);
+                    tma_load_2d(sV + a * 16384, &tmap_v, kv_full, col + a * 64, row_base + k0);
+                }
+                for (int it = 0; it < niter && ok; it++) {
+                    ok = mbar_wait(qdo_empty, (it & 1) ^ 1);
+                    if (!ok) break;
+                    const int q0 = (jblk + it) * AT_BQ;
+                    mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
+#pragma unroll
+                    for (int a = 0; a < D / 64; a++) {
+                        tma_load_2d(sQ + a * 16384, &tmap_q, qdo_full, col + a * 64, row_base + q0);
+                        tma_load_2d(sDO + a * 16384, &tmap_do, qdo_full, col + a * 64, row_base + q0);
+                    }
+                }
+                if (!ok) atomicExch(&g_attn_error, 11);
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {
+                bool ok = mbar_wait(kv_full, 0);
+                const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
+                const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
+                for (int it = 0; it < niter && ok; it++) {
+                    ok = mbar_wait(qdo_full, it & 1) && mbar_wait(sdp_empty, (it & 1) ^ 1);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; kk++) {
+                        const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+                        umma_f16_ss(tmem_base, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
+                                    IDESC_S, kk != 0 ? 1u : 0u);
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; kk++) {
+                        const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+                        umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(do_addr + off, 16, 1024), make_smem_desc_sw128(v_addr + off, 16, 1024),
+                                    IDESC_S, kk != 0 ? 1u : 0u);
+                    }
+                    umma_commit(sdp_full);
+                    ok = mbar_wait(pds_full, it & 1);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < AT_BQ / 16; kk++) {
+                        // dV += P^T dO ; dK += dS^T Q   (contraction over the 128 query rows)
+                        umma_f16_ss(tmem_base + 256, make_smem_desc_sw128(p_addr + kk * 2048, 16384, 1024),
+                                    make_smem_desc_sw128(do_addr + kk * 2048, 16384, 1024), IDESC_ACC, (it | kk) != 0 ? 1u : 0u);
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < AT_BQ / 16; kk++) {
+                        umma_f16_ss(tmem_base + 256 + D, make_smem_desc_sw128(ds_addr + kk * 2048, 16384, 1024),
+                                    make_smem_desc_sw128(q_addr + kk * 2048, 16384, 1024), IDESC_ACC, (it | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(qdo_empty);
+                    umma_commit(pds_empty);
+                }
+                if (ok) umma_commit(acc_full);
+                if (!ok) atomicExch(&g_attn_error, 12);
+            }
+        } else {
+            const int quarter = warp & 3;
+            const int r = quarter * 32 + lane;
+            const float slope2 = p.slopes ? p.slopes[head] * 1.4426950408889634f : 0.0f;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const int64_t stat_base = ((int64_t)b * p.heads + head) * p.tokens;
+            bool ok = true;
+            for (int it = 0; it < niter && ok; it++) {
+                const int qi = (jblk + it) * AT_BQ + r;
+                const bool q_ok = qi < p.tokens;
+                const float lse2 = q_ok ? p.lse[stat_base + qi] * 1.4426950408889634f : 0.0f;
+                const float dlt = q_ok ? p.delta[stat_base + qi] : 0.0f;
+                const int klimit = q_ok ? min(qi + 1, len) : 0;
+                ok = mbar_wait(sdp_full, it & 1);
+                if (!ok) break;
+                if (it > 0) ok = mbar_wait(pds_empty, (it - 1) & 1);
+                if (!ok) break;
+                tcgen05_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < AT_BKV; c0 += 32) {
+                    uint32_t sv[32], dv[32];
+                    tmem_ld_32x32b_x32(lane_addr + c0, sv);
+                    tmem_ld_32x32b_x32(lane_addr + 128 + c0, dv);
+                    tmem_ld_wait();
+                    float pr[32], ds[32];
+#pragma unroll
+                    for (int e = 0; e < 32; e++) {
+                        const int kj = k0 + c0 + e;
+                        const float pe = kj < klimit ? fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, slope2 * (float)kj) - lse2) : 0.0f;
+                        pr[e] = pe;
+                        ds[e] = pe * (__uint_as_float(dv[e]) - dlt);
+                    }
+                    store_tile_chunk(sP, r, c0, pr);
+                    store_tile_chunk(sDS, r, c0, ds);
+                }
+                tcgen05_fence_before();
+                mbar_arrive(sdp_empty);
+                fence_proxy_async();
+                mbar_arrive(pds_full);
+            }
+            if (ok) ok = mbar_wait(acc_full, 0);
+            if (ok) {
+                tcgen05_fence_after();
+                const int kj = k0 + r;
+                __half* dvrow = p.dv + (int64_t)(row_base + kj) * p.ld_g + col;
+                __half* dkrow = p.dk + (int64_t)(row_base + kj) * p.ld_g + col;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t a[32], c[32];
+                    tmem_ld_32x32b_x32(lane_addr + 256 + c0, a);
+                    tmem_ld_32x32b_x32(lane_addr + 256 + D + c0, c);
+                    tmem_ld_wait();
+                    if (kj < p.tokens) {
+#pragma unroll
+                        for (int g = 0; g < 4; g++) {
+                            Vec<__half> o1, o2;
+#pragma unroll
+                            for (int e = 0; e < 8; e++) {
+                                o1.v[e] = __uint_as_float(a[g * 8 + e]);
+                                o2.v[e] = __uint_as_float(c[g * 8 + e]) * p.scale;
+                            }
+                            o1.store(dvrow + c0 + g * 8);
+                            o2.store(dkrow + c0 + g * 8);
+                        }
+                    }
+                }
+            }
+            if (!ok && lane == 0) atomicExch(&g_attn_error, 13);
+        }
+    } else if (warp >= 2) {
+        const int kj = k0 + (warp & 3) * 32 + lane;
+        if (kj < p.tokens) {
+            __half* dvrow = p.dv + (int64_t)(row_base + kj) * p.ld_g + col;
+            __half* dkrow = p.dk + (int64_t)(row_base + kj) * p.ld_g + col;
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            for (int e = 0; e < D; e += 8) {
+                *reinterpret_cast<uint4*>(dvrow + e) = z;
+                *reinterpret_cast<uint4*>(dkrow + e) = z;
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do, AttnBwdParams p) {
+    constexpr uint32_t TILE_BYTES = 128 * D * 2;
+    constexpr uint32_t PT_BYTES = 128 * 128 * 2;
+    constexpr uint32_t TMEM_COLS = 512;   // S [0,128) dP [128,256) dQ [256,256+D)
+    constexpr uint32_t IDESC_S = make_idesc_f16_f32(128, 128, 0, 0);
+    constexpr uint32_t IDESC_DQ = make_idesc_f16_f32(128, D, 0, 1);
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = base;
+    unsigned char* sDO = sQ + TILE_BYTES;
+    unsigned char* sK = sDO + TILE_BYTES;
+    unsigned char* sV = sK + TILE_BYTES;
+    unsigned char* sDS = sV + TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + PT_BYTES);
+    uint64_t* qdo_full = bars;
+    uint64_t* kv_full = bars + 1;
+    uint64_t* kv_empty = bars + 2;
+    uint64_t* sdp_full = bars + 3;
+    uint64_t* sdp_empty = bars + 4;
+    uint64_t* ds_full = bars + 5;
+    uint64_t* ds_empty = bars + 6;
+    uint64_t* acc_full = bars + 7;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qblk = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int head = blockIdx.y, b = blockIdx.z;
+    const int q0 = qblk * AT_BQ;
+    const int len = p.lens ? min(max(p.lens[b], 0), p.tokens) : p.tokens;
+    const int key_end = min(q0 + AT_BQ, len);
+    const int nkb = key_end > 0 ? (key_end + AT_BKV - 1) / AT_BKV : 0;
+    const int row_base = b * p.tokens;
+    const int col = head * D;
+
+    if (threadIdx.x == 0) {
+        mbar_init(qdo_full, 1);
+        mbar_init(kv_full, 1);
+        mbar_init(kv_empty, 1);
+        mbar_init(sdp_full, 1);
+        mbar_init(sdp_empty, 128);
+        mbar_init(ds_full, 128);
+        mbar_init(ds_empty, 1);
+        mbar_init(acc_full, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_smem, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    if (nkb > 0) {
+        if (warp == 0) {
+            if (lane == 0) {
+                bool ok = true;
+                mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
+#pragma unroll
+                for (int a = 0; a < D / 64; a++) {
+                    tma_load_2d(sQ + a * 16384, &tmap_q, qdo_full, col + a * 64, row_base + q0);
+                    tma_load_2d(sDO + a * 16384, &tmap_do, qdo_full, col + a * 64, row_base + q0);
+                }
+                for (int j = 0; j < nkb && ok; j++) {
+                    ok = mbar_wait(kv_empty, (j & 1) ^ 1);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+#pragma unroll
+                    for (int a = 0; a < D / 64; a++) {
+                        tma_load_2d(sK + a * 16384, &tmap_k, kv_full, col + a * 64, row_base + j * AT_BKV);
+                        tma_load_2d(sV + a * 16384, &tmap_v, kv_full, col + a * 64, row_base + j * AT_BKV);
+                    }
+                }
+                if (!ok) atomicExch(&g_attn_error, 21);
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {
+                bool ok = mbar_wait(qdo_full, 0);
+                const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
+                const uint32_t ds_addr = smem_u32(sDS);
+                for (int j = 0; j < nkb && ok; j++) {
+                    ok = mbar_wait(kv_full, j & 1) && mbar_wait(sdp_empty, (j & 1) ^ 1);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; kk++) {
+                        const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+                        umma_f16_ss(tmem_base, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
+                                    IDESC_S, kk != 0 ? 1u : 0u);
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; kk++) {
+                        const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+                        umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(do_addr + off, 16, 1024), make_smem_desc_sw128(v_addr + off, 16, 1024),
+                                    IDESC_S, kk != 0 ? 1u : 0u);
+                    }
+                    umma_commit(sdp_full);
+                    ok = mbar_wait(ds_full, j & 1);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < AT_BKV / 16; kk++) {
+                        // dQ += dS K_j : A = dS [q x keys] K-major, B = K_j [keys x d], d contiguous (MN-major)
+                        umma_f16_ss(tmem_base + 256, make_smem_desc_sw128(ds_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                                    make_smem_desc_sw128(k_addr + kk * 2048, 16384, 1024), IDESC_DQ, (j | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(kv_empty);
+                    umma_commit(ds_empty);
+                }
+                if (ok) umma_commit(acc_full);
+                if (!ok) atomicExch(&g_attn_error, 22);
+            }
+        } else {
+            const int quarter = warp & 3;
+            const int r = quarter * 32 + lane;
+            const int qi = q0 + r;
+            const bool q_ok = qi < p.tokens;
+            const float slope2 = p.slopes ? p.slopes[head] * 1.4426950408889634f : 0.0f;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const int64_t stat_base = ((int64_t)b * p.heads + head) * p.tokens;
+            const float lse2 = q_ok ? p.lse[stat_base + qi] * 1.4426950408889634f : 0.0f;
+            const float dlt = q_ok ? p.delta[stat_base + qi] : 0.0f;
+            const int klimit = q_ok ? min(qi + 1, len) : 0;
+            bool ok = true;
+            for (int j = 0; j < nkb && ok; j++) {
+                ok = mbar_wait(sdp_full, j & 1);
+                if (!ok) break;
+                if (j > 0) ok = mbar_wait(ds_empty, (j - 1) & 1);
+                if (!ok) break;
+                tcgen05_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < AT_BKV; c0 += 32) {
+                    uint32_t sv[32], dv[32];
+                    tmem_ld_32x32b_x32(lane_addr + c0, sv);
+                    tmem_ld_32x32b_x32(lane_addr + 128 + c0, dv);
+                    tmem_ld_wait();
+                    float ds[32];
+#pragma unroll
+                    for (int e = 0; e < 32; e++) {
+                        const int kj = j * AT_BKV + c0 + e;
+                        const float pe = kj < klimit ? fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, slope2 * (float)kj) - lse2) : 0.0f;
+                        ds[e] = pe * (__uint_as_float(dv[e]) - dlt);
+                    }
+                    store_tile_chunk(sDS, r, c0, ds);
+                }
+                tcgen05_fence_before();
+                mbar_arrive(sdp_empty);
+                fence_proxy_async();
+                mbar_arrive(ds_full);
+            }
+            if (ok) ok = mbar_wait(acc_full, 0);
+            if (ok) {
+                tcgen05_fence_after();
+                __half* dqrow = p.dq + (int64_t)(row_base + qi) * p.ld_g + col;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t a[32];
+                    tmem_ld_32x32b_x32(lane_addr + 256 + c0, a);
+                    tmem_ld_wait();
+                    if (q_ok) {
+#pragma unroll
+                        for (int g = 0; g < 4; g++) {
+                            Vec<__half> o;
+#pragma unroll
+                            for (int e = 0; e < 8; e++) o.v[e] = __uint_as_float(a[g * 8 + e]) * p.scale;
+                            o.store(dqrow + c0 + g * 8);
+                        }
+                    }
+                }
+            }
+            if (!ok && lane == 0) atomicExch(&g_attn_error, 23);
+        }
+    } else if (warp >= 2) {
+        const int qi = q0 + (warp & 3) * 32 + lane;
+        if (qi < p.tokens) {
+            __half* dqrow = p.dq + (int64_t)(row_base + qi) * p.ld_g + col;
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            for (int e = 0; e < D; e += 8) *reinterpret_cast<uint4*>(dqrow + e) = z;
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int D>
+static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                           const AttnBwdParams& p, cudaStream_t st) {
+    constexpr size_t smem_dkv = 1024 + (size_t)128 * D * 2 * 4 + 2 * 128 * 128 * 2 + 256;
+    constexpr size_t smem_dq = 1024 + (size_t)128 * D * 2 * 4 + 128 * 128 * 2 + 256;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(attn_bwd_dkv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dkv);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq);
+    });
+    if (attr_err != cudaSuccess) {
+        set_cuda_error(attr_err, "attn_bwd smem attribute");
+        return BRK_CUDA_ERROR;
+    }
+    dim3 grid((unsigned)((p.tokens + AT_BQ - 1) / AT_BQ), (unsigned)p.heads, (unsigned)p.batch);
+    attn_bwd_dkv_kernel<D><<<grid, AT_THREADS, smem_dkv, st>>>(tq, tk, tv, tdo, p);
+    int rc = launch_status("attn_bwd_dkv_kernel");
+    if (rc) return rc;
+    attn_bwd_dq_kernel<D><<<grid, AT_THREADS, smem_dq, st>>>(tq, tk, tv, tdo, p);
+    return launch_status("attn_bwd_dq_kernel");
+}
+
+}  // namespace brk
+
+extern "C" int brk_flash_attn_fwd(const void* q, const void* k, const void* v, int64_t ld_qkv, void* out, int64_t ld_out,
+                                  float* lse, const int32_t* lens, const float* slopes, int batch, int tokens, int heads,
+                                  int head_dim, void* stream) {
+    using namespace brk;
+    if (!q || !k || !v) return BRK_INPUT_ERROR;
+    if (!out) return BRK_OUTPUT_ERROR;
+    if (batch < 0 || tokens < 0 || heads <= 0 || (head_dim != 64 && head_dim != 128)) return BRK_ATTR_ERROR;
+    if (ld_qkv % 8 != 0 || ld_qkv < (int64_t)heads * head_dim || ld_out < (int64_t)heads * head_dim) return BRK_ATTR_ERROR;
+    if (batch == 0 || tokens == 0) return BRK_OK;
+    if ((int64_t)batch * tokens > 0x7fffffff || heads > 65535 || batch > 65535) return BRK_ATTR_ERROR;
+    const uint64_t rows = (uint64_t)batch * tokens, cols = (uint64_t)heads * head_dim;
+    CUtensorMap tq, tk, tv;
+    if (!make_tmap_2d_f16(&tq, q, rows, cols, (uint64_t)ld_qkv, 64, 128) || !make_tmap_2d_f16(&tk, k, rows, cols, (uint64_t)ld_qkv, 64, 128) ||
+        !make_tmap_2d_f16(&tv, v, rows, cols, (uint64_t)ld_qkv, 64, 128)) {
+        set_error_message("brk_flash_attn_fwd: could not encode a tensor map (pointers must be 16-byte aligned)");
+        return BRK_CUDA_ERROR;
+    }
+    AttnFwdParams p;
+    p.out = (__half*)out;
+    p.lse = lse;
+    p.lens = lens;
+    p.slopes = slopes;
+    p.ld_out = ld_out;
+    p.batch = batch;
+    p.tokens = tokens;
+    p.heads = heads;
+    p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)head_dim));
+    cudaStream_t st = (cudaStream_t)stream;
+    if (head_dim == 128) return launch_attn_fwd<128>(tq, tk, tv, p, st);
+    return launch_attn_fwd<64>(tq, tk, tv, p, st);
+}
+
+// Synchronous: non-zero if an attention kernel gave up on a bounded wait since the last query.
+extern "C" int brk_flash_attn_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, brk::g_attn_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(brk::g_attn_error, &zero, sizeof(int));
+    return v;
+}
+
+extern "C" size_t brk_flash_attn_bwd_workspace_bytes(int batch, int tokens, int heads) {
+    if (batch <= 0 || tokens <= 0 || heads <= 0) return 0;
+    return (size_t)batch * tokens * heads * sizeof(float);
+}
+
+extern "C" int brk_flash_attn_bwd(const void* q, const void* k, const void* v, int64_t ld_qkv, const void* out, const void* d_out,
+                                  int64_t ld_out, const float* lse, void* dq, void* dk, void* dv, int64_t ld_g,
+                                  const int32_t* lens, const float* slopes, int batch, int tokens, int heads, int head_dim,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+    using namespace brk;
+    if (!q || !k || !v || !out || !d_out || !lse) return BRK_INPUT_ERROR;
+    if (!dq || !dk || !dv) return BRK_OUTPUT_ERROR;
+    if (batch < 0 || tokens < 0 || heads <= 0 || (head_dim != 64 && head_dim != 128)) return BRK_ATTR_ERROR;
+    const int64_t hd = (int64_t)heads * head_dim;
+    if (ld_qkv % 8 != 0 || ld_out % 8 != 0 || ld_g % 8 != 0 || ld_qkv < hd || ld_out < hd || ld_g < hd) return BRK_ATTR_ERROR;
+    if ((reinterpret_cast<uintptr_t>(dq) & 15) || (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15)) return BRK_ATTR_ERROR;
+    if (batch == 0 || tokens == 0) return BRK_OK;
+    if ((int64_t)batch * tokens > 0x7fffffff || heads > 65535 || batch > 65535) return BRK_ATTR_ERROR;
+    if (!workspace || workspace_bytes < brk_flash_attn_bwd_workspace_bytes(batch, tokens, heads)) return BRK_ATTR_ERROR;
+    cudaStream_t st = (cudaStream_t)stream;
+    float* delta = (float*)workspace;
+    {
+        int64_t warps = (int64_t)batch * tokens * heads;
+        unsigned blocks = (unsigned)((warps * 32 + 255) / 256);
+        attn_delta_kernel<<<blocks, 256, 0, st>>>((const __half*)out, (const __half*)d_out, ld_out, delta, batch, tokens, heads, head_dim);
+        int rc = launch_status("attn_delta_kernel");
+        if (rc) return rc;
+    }
+    const uint64_t rows = (uint64_t)batch * tokens, cols = (uint64_t)hd;
+    CUtensorMap tq, tk, tv, tdo;
+    if (!make_tmap_2d_f16(&tq, q, rows, cols, (uint64_t)ld_qkv, 64, 128) || !make_tmap_2d_f16(&tk, k, rows, cols, (uint64_t)ld_qkv, 64, 128) ||
+        !make_tmap_2d_f16(&tv, v, rows, cols, (uint64_t)ld_qkv, 64, 128) || !make_tmap_2d_f16(&tdo, d_out, rows, cols, (uint64_t)ld_out, 64, 128)) {
+        set_error_message("brk_flash_attn_bwd: could not encode a tensor map (pointers must be 16-byte aligned)");
+        return BRK_CUDA_ERROR;
+    }
+    AttnBwdParams p;
+    p.lse = lse;
+    p.delta = delta;
+    p.lens = lens;
+    p.slopes = slopes;
+    p.dq = (__half*)dq;
+    p.dk = (__half*)dk;
+    p.dv = (__half*)dv;
+    p.ld_g = ld_g;
+    p.batch = batch;
+    p.tokens = tokens;
+    p.heads = heads;
+    p.scale = (float)(1.0 / sqrt((double)head_dim));
+    p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)head_dim));
+    if (head_dim == 128) return launch_attn_bwd<128>(tq, tk, tv, tdo, p, st);
+    return launch_attn_bwd<64>(tq, tk, tv, tdo, p, st);
+}

@@ -184,6 +184,17 @@ BRK_API int brk_gemm_f16_status(void);
 BRK_API int brk_flash_attn_fwd(const void* q, const void* k, const void* v, int64_t ld_qkv, void* out, int64_t ld_out,
                        float* lse, const int32_t* lens, const float* slopes, int batch, int tokens, int heads,
                        int head_dim, void* stream);
+/* Backward of brk_flash_attn_fwd; replaces op_softmax_attn_backward + op_qk_backward and the four
+ * transposes of layer_backward (bloomz-7b/train.words:215-227; blackriver/cuda_tensor.cpp:921-1063).
+ * Inputs: q, k, v as in the forward, the forward's out and lse, the upstream gradient d_out
+ * (token-major, row stride ld_out like out).  Outputs dq, dk, dv: token-major with row stride ld_g
+ * (e.g. the three thirds of one [batch*tokens, 3H] buffer), overwritten.  workspace: at least
+ * brk_flash_attn_bwd_workspace_bytes() bytes of device scratch (row sums of d_out * out). */
+BRK_API size_t brk_flash_attn_bwd_workspace_bytes(int batch, int tokens, int heads);
+BRK_API int brk_flash_attn_bwd(const void* q, const void* k, const void* v, int64_t ld_qkv, const void* out, const void* d_out,
+                       int64_t ld_out, const float* lse, void* dq, void* dk, void* dv, int64_t ld_g,
+                       const int32_t* lens, const float* slopes, int batch, int tokens, int heads, int head_dim,
+                       void* workspace, size_t workspace_bytes, void* stream);
 BRK_API int brk_flash_attn_status(void);
 
 #ifdef __cplusplus

@@ -88,3 +88,50 @@ def test_flash_attention_empty_sequence_and_no_alibi():
     pr = np.exp(s - s.max(-1, keepdims=True)); pr /= pr.sum(-1, keepdims=True)
     ref = np.einsum("bhij,bjhd->bihd", pr, vf)
     assert relerr(o[1:], ref) <= TOL16
+
+
+@pytest.mark.parametrize("B,T,heads,d,lens", [
+    (2, 128, 4, 64, (128, 77)),
+    (2, 300, 2, 128, (300, 131)),
+    (1, 512, 2, 128, (512,)),
+    (3, 200, 2, 64, (1, 200, 0)),
+])
+def test_flash_attention_backward(B, T, heads, d, lens):
+    from blackriver_b200 import brk, ops
+    rng = np.random.default_rng(T * 3 + d)
+    H = heads * d
+    qkv = rng.standard_normal((B * T, 3 * H)).astype(np.float16)
+    dout = rng.standard_normal((B * T, H)).astype(np.float16)
+    q, k, v = (qkv[:, i * H:(i + 1) * H].astype(np.float32).reshape(B, T, heads, d) for i in range(3))
+    # oracle: unfused backward chain of the layer_backward word
+    ref_lens = [max(n, 0) for n in lens]
+    out_ref, lse_ref, p = reference(q, k, v, ref_lens, heads)
+    if 0 in ref_lens:                      # an empty sequence has no visible key: probabilities are all zero
+        for b, n in enumerate(ref_lens):
+            if n == 0:
+                p[b] = 0
+    zb = orc.transpose_0213(dout.astype(np.float32).reshape(B, T, heads, d))
+    zq, zk, zv = (orc.transpose_0213(x) for x in (q, k, v))
+    ds_ref, dv_ref = orc.softmax_attn_backward(zb, p, zv)
+    dq_ref, dk_ref = orc.qk_backward(ds_ref, zq, zk)
+    dq_ref, dk_ref, dv_ref = (orc.transpose_0213(x) for x in (dq_ref, dk_ref, dv_ref))
+
+    dqkv = torch.from_numpy(qkv).cuda()
+    ddo = torch.from_numpy(dout).cuda()
+    out = torch.empty((B * T, H), dtype=torch.float16, device="cuda")
+    lse = torch.empty((B, heads, T), dtype=torch.float32, device="cuda")
+    dl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    dsl = torch.from_numpy(slopes_f32(heads)).cuda()
+    grads = torch.full((B * T, 3 * H), 5.0, dtype=torch.float16, device="cuda")
+    ws = torch.empty(brk.lib().brk_flash_attn_bwd_workspace_bytes(B, T, heads), dtype=torch.uint8, device="cuda")
+    base, gb = dqkv.data_ptr(), grads.data_ptr()
+    brk.call("brk_flash_attn_fwd", base, base + 2 * H, base + 4 * H, 3 * H, out.data_ptr(), H, lse.data_ptr(), dl.data_ptr(),
+             dsl.data_ptr(), B, T, heads, d, ops.stream())
+    brk.call("brk_flash_attn_bwd", base, base + 2 * H, base + 4 * H, 3 * H, out.data_ptr(), ddo.data_ptr(), H, lse.data_ptr(),
+             gb, gb + 2 * H, gb + 4 * H, 3 * H, dl.data_ptr(), dsl.data_ptr(), B, T, heads, d, ws.data_ptr(), ws.numel(), ops.stream())
+    torch.cuda.synchronize()
+    assert brk.lib().brk_flash_attn_status() == 0
+    g = grads.float().cpu().numpy()
+    got = [g[:, i * H:(i + 1) * H].reshape(B, T, heads, d) for i in range(3)]
+    for name, a, r in zip(("dq", "dk", "dv"), got, (dq_ref, dk_ref, dv_ref)):
+        assert relerr(a, r) <= TOL16, name
