@@ -17,6 +17,8 @@ cudaEvent_t ComputingContext::comm_done = nullptr;
 void* ComputingContext::cuda_workspace = nullptr;
 void* ComputingContext::local_workspace = nullptr;
 size_t ComputingContext::workspace_size = 0;
+int ComputingContext::grad_accumulate = 0;
+float ComputingContext::loss_scale = 1.0f;
 bool ComputingContext::booted = false;
 static bool g_owns_compute_stream = false;
 

@@ -30,6 +30,10 @@ struct ComputingContext {
     static void* local_workspace;      // pinned host scratch of the same size
     static size_t workspace_size;
 
+    // training-step switches read by the device backend
+    static int grad_accumulate;        // 1: op_linear_backward / op_layernorm_backward add into W_g, b_g (micro-batches)
+    static float loss_scale;           // multiplies the loss gradient (fp16 gradients); Adam divides it out
+
     static bool booted;
     static void boot(int device, size_t workspace_bytes = (size_t)256 << 20);
     // adopt a stream owned by an embedding process (e.g. torch's current stream)

@@ -5,6 +5,8 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <utility>
+#include <vector>
 
 #include "brk.h"
 #include "cpu_tensor.hpp"
@@ -337,7 +339,7 @@ LossReturn CUDATensor<DT>::op_loss_backward(tensor_t self, tensor_t ids_, tensor
     BR_CUDA_CHECK(cudaStreamSynchronize(stream()));
     BR_CUDA_CHECK(cudaMemsetAsync(x_g->data(), 0, x_g->bytes(), stream()));
     if (items == 0) return 0.0f;
-    const float scale = 1.0f / (float)items;
+    const float scale = ComputingContext::loss_scale / (float)items;
 
     // the weight gradient accumulates on the device; a host-resident gradient gets a device twin
     void* d_wg = lm_head_g->data();
@@ -393,7 +395,7 @@ ComputingReturn CUDATensor<DT>::op_layernorm_backward(tensor_t self, tensor_t sc
     if (need > ComputingContext::workspace_size) return OP_ATTR_ERROR;
     return ret(brk_layernorm_bwd(mem_, scale->data(), bias->data(), (const float*)var->data(), y->data(), dscale->data(),
                                  dbias->data(), din->data(), rows, hidden, eps, ComputingContext::cuda_workspace,
-                                 ComputingContext::workspace_size, 0, brk_dtype<DT>(), sptr()));
+                                 ComputingContext::workspace_size, ComputingContext::grad_accumulate, brk_dtype<DT>(), sptr()));
 }
 
 // b_g = sum_n dy ; W_g = dy^T x ; x_g = dy W, all overwritten, W_g before x_g because x_g may be x
@@ -409,8 +411,9 @@ ComputingReturn CUDATensor<DT>::op_linear_backward(tensor_t self, tensor_t x, te
     if ((int64_t)x->items() != n * in) return OP_INPUT_ERROR;
     if (x_g->items() != x->items() || weight_g->items() != weight->items() || (int64_t)bias_g->items() != out) return OP_OUTPUT_ERROR;
     constexpr int dt = brk_dtype<DT>();
-    int st = brk_colsum(mem_, bias_g->data(), n, out, 0, dt, sptr());
-    if (st == BRK_OK) st = gemm_any<DT>(mem_, x->data(), weight_g->data(), out, in, n, 1, 0, out, in, in, 0.0f, nullptr);
+    const int acc = ComputingContext::grad_accumulate;
+    int st = brk_colsum(mem_, bias_g->data(), n, out, acc, dt, sptr());
+    if (st == BRK_OK) st = gemm_any<DT>(mem_, x->data(), weight_g->data(), out, in, n, 1, 0, out, in, in, acc ? 1.0f : 0.0f, nullptr);
     if (st == BRK_OK) st = gemm_any<DT>(mem_, weight->data(), x_g->data(), n, in, out, 0, 0, out, in, in, 0.0f, nullptr);
     return ret(st);
 }
@@ -489,6 +492,158 @@ ComputingReturn CUDATensor<DT>::op_qk_backward(tensor_t self, tensor_t q, tensor
     int st = brk_gemm(mem_, k->data(), q_g->data(), t, d, t, 0, 0, t, d, d, bh, t * t, t * d, t * d, alpha, 0.0f, nullptr, dt, sptr());
     if (st == BRK_OK) st = brk_gemm(mem_, q->data(), k_g->data(), t, d, t, 1, 0, t, d, d, bh, t * t, t * d, t * d, alpha, 0.0f, nullptr, dt, sptr());
     return ret(st);
+}
+
+// ---- extensions ------------------------------------------------------------------------------------------
+namespace {
+
+// ALiBi slopes of the reference formula (blackriver/train_bloom.cpp:61-66) as fp32 on the device, cached
+// per head count for the life of the process.
+const float* device_slopes(int heads) {
+    static std::vector<std::pair<int, float*>> cache;
+    for (auto& e : cache)
+        if (e.first == heads) return e.second;
+    std::vector<double> sd(heads);
+    brk_alibi_slopes(heads, sd.data());
+    std::vector<float> sf(sd.begin(), sd.end());
+    float* d = nullptr;
+    BR_CUDA_CHECK(cudaMalloc(&d, heads * sizeof(float)));
+    BR_CUDA_CHECK(cudaMemcpyAsync(d, sf.data(), heads * sizeof(float), cudaMemcpyHostToDevice, stream()));
+    BR_CUDA_CHECK(cudaStreamSynchronize(stream()));
+    cache.emplace_back(heads, d);
+    return d;
+}
+
+// int32 tensor -> device pointer; host tensors are staged through `scratch`
+const int32_t* int_on_device(const tensor_t& t, Scratch& sc) {
+    if (t->is_cuda()) return (const int32_t*)t->data();
+    int32_t* d = (int32_t*)sc.take(t->bytes());
+    BR_CUDA_CHECK(cudaMemcpyAsync(d, t->data(), t->bytes(), cudaMemcpyHostToDevice, stream()));
+    return d;
+}
+
+}  // namespace
+
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_flash_attn(tensor_t self, tensor_t lens, tensor_t out, tensor_t lse, int heads) {
+    if (DT != DataType::F16) return OP_TODO_ERROR;   // the fp32 parity path keeps the unfused operator chain
+    if (self->shape().dim() != 3 || heads <= 0) return OP_INPUT_ERROR;
+    const int batch = (int)self->shape()[0], tokens = (int)self->shape()[1];
+    const int64_t h3 = (int64_t)self->shape()[2];
+    if (h3 % 3 != 0 || (h3 / 3) % heads != 0) return OP_INPUT_ERROR;
+    const int64_t hidden = h3 / 3;
+    const int d = (int)(hidden / heads);
+    if (!dev_ok<DT>({out}) || (int64_t)out->items() != (int64_t)batch * tokens * hidden) return OP_OUTPUT_ERROR;
+    if (!dev_ok<DataType::Float>({lse}) || (int64_t)lse->items() < (int64_t)batch * heads * tokens) return OP_OUTPUT_ERROR;
+    if (lens && (lens->dtype() != DataType::Int || (int)lens->items() < batch)) return OP_INPUT_ERROR;
+    Scratch sc;
+    const int32_t* dlens = lens ? int_on_device(lens, sc) : nullptr;
+    const __half* q = (const __half*)mem_;
+    return ret(brk_flash_attn_fwd(q, q + hidden, q + 2 * hidden, h3, out->data(), hidden, (float*)lse->data(), dlens,
+                                  device_slopes(heads), batch, tokens, heads, d, sptr()));
+}
+
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_flash_attn_backward(tensor_t self, tensor_t qkv, tensor_t out, tensor_t lse, tensor_t lens,
+                                                       tensor_t dqkv, int heads) {
+    if (DT != DataType::F16) return OP_TODO_ERROR;
+    if (!dev_ok<DT>({qkv, out}) || qkv->shape().dim() != 3 || heads <= 0 || !dev_ok<DataType::Float>({lse})) return OP_INPUT_ERROR;
+    const int batch = (int)qkv->shape()[0], tokens = (int)qkv->shape()[1];
+    const int64_t h3 = (int64_t)qkv->shape()[2], hidden = h3 / 3;
+    if (h3 % 3 != 0 || hidden % heads != 0) return OP_INPUT_ERROR;
+    const int d = (int)(hidden / heads);
+    if (self->items() != out->items() || (int64_t)out->items() != (int64_t)batch * tokens * hidden) return OP_INPUT_ERROR;
+    if (!dev_ok<DT>({dqkv}) || dqkv->items() != qkv->items()) return OP_OUTPUT_ERROR;
+    if (lens && (lens->dtype() != DataType::Int || (int)lens->items() < batch)) return OP_INPUT_ERROR;
+    Scratch sc;
+    const int32_t* dlens = lens ? int_on_device(lens, sc) : nullptr;
+    size_t need = brk_flash_attn_bwd_workspace_bytes(batch, tokens, heads);
+    void* ws = sc.take(need);
+    const __half* q = (const __half*)qkv->data();
+    __half* g = (__half*)dqkv->data();
+    return ret(brk_flash_attn_bwd(q, q + hidden, q + 2 * hidden, h3, out->data(), mem_, hidden, (const float*)lse->data(), g,
+                                  g + hidden, g + 2 * hidden, h3, dlens, device_slopes(heads), batch, tokens, heads, d, ws, need, sptr()));
+}
+
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_linear_residual(tensor_t self, tensor_t w, tensor_t bias, tensor_t residual, tensor_t y) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (!dev_ok<DT>({w, bias, residual}) || w->shape().dim() != 2) return OP_INPUT_ERROR;
+    if (!dev_ok<DT>({y})) return OP_OUTPUT_ERROR;
+    int64_t in = (int64_t)self->shape().vec().back(), out = (int64_t)w->shape()[0];
+    int64_t n = (int64_t)self->items() / in;
+    if ((int64_t)w->shape()[1] != in || (int64_t)bias->items() != out || (int64_t)residual->items() != n * out) return OP_INPUT_ERROR;
+    if ((int64_t)y->items() != n * out) return OP_OUTPUT_ERROR;
+    if (DT == DataType::F16 && brk_gemm_f16_supported(n, out, in, 0, 1, in, in, mem_, w->data()))
+        return ret(brk_gemm_f16(mem_, w->data(), y->data(), n, out, in, 0, 1, in, in, out, bias->data(), residual->data(), out,
+                                nullptr, 0, 0, sptr()));
+    int st = brk_gemm(mem_, w->data(), y->data(), n, out, in, 0, 1, in, in, out, 1, 0, 0, 0, 1.0f, 0.0f, bias->data(), brk_dtype<DT>(), sptr());
+    int64_t dims[4] = {1, 1, n, out};
+    if (st == BRK_OK) st = brk_add_bcast(y->data(), residual->data(), y->data(), dims, dims, brk_dtype<DT>(), sptr());
+    return ret(st);
+}
+
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_linear_gelu(tensor_t self, tensor_t w, tensor_t bias, tensor_t y, tensor_t y_gelu) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (!dev_ok<DT>({w, bias}) || w->shape().dim() != 2) return OP_INPUT_ERROR;
+    if (!dev_ok<DT>({y, y_gelu})) return OP_OUTPUT_ERROR;
+    int64_t in = (int64_t)self->shape().vec().back(), out = (int64_t)w->shape()[0];
+    int64_t n = (int64_t)self->items() / in;
+    if ((int64_t)w->shape()[1] != in || (int64_t)bias->items() != out) return OP_INPUT_ERROR;
+    if ((int64_t)y->items() != n * out || y_gelu->items() != y->items()) return OP_OUTPUT_ERROR;
+    if (DT == DataType::F16 && brk_gemm_f16_supported(n, out, in, 0, 1, in, in, mem_, w->data()))
+        return ret(brk_gemm_f16(mem_, w->data(), y->data(), n, out, in, 0, 1, in, in, out, bias->data(), nullptr, 0, y_gelu->data(), out,
+                                0, sptr()));
+    int st = brk_gemm(mem_, w->data(), y->data(), n, out, in, 0, 1, in, in, out, 1, 0, 0, 0, 1.0f, 0.0f, bias->data(), brk_dtype<DT>(), sptr());
+    if (st == BRK_OK) st = brk_gelu_fwd(y->data(), y_gelu->data(), n * out, brk_dtype<DT>(), sptr());
+    return ret(st);
+}
+
+// self = ids; the call is routed here through the TABLE's backend, so DT is the table's type
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_embed(tensor_t self, tensor_t table, tensor_t out) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (self->dtype() != DataType::Int || table->shape().dim() != 2) return OP_INPUT_ERROR;
+    const int64_t n = (int64_t)self->items(), vocab = (int64_t)table->shape()[0], hidden = (int64_t)table->shape()[1];
+    if (!dev_ok<DT>({out}) || (int64_t)out->items() != n * hidden) return OP_OUTPUT_ERROR;
+    Scratch sc;
+    const int32_t* ids = int_on_device(self, sc);
+    return ret(brk_embedding_gather(table->data(), ids, out->data(), n, hidden, vocab, brk_dtype<DT>(), sptr()));
+}
+
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_embed_backward(tensor_t self, tensor_t ids_, tensor_t table_g) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (!ids_ || ids_->dtype() != DataType::Int) return OP_INPUT_ERROR;
+    if (!dev_ok<DT>({table_g}) || table_g->shape().dim() != 2) return OP_OUTPUT_ERROR;
+    const int64_t n = (int64_t)ids_->items(), vocab = (int64_t)table_g->shape()[0], hidden = (int64_t)table_g->shape()[1];
+    if ((int64_t)self->items() != n * hidden) return OP_INPUT_ERROR;
+    Scratch sc;
+    const int32_t* ids = int_on_device(ids_, sc);
+    return ret(brk_embedding_scatter_add(mem_, ids, table_g->data(), n, hidden, vocab, brk_dtype<DT>(), sptr()));
+}
+
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_adam(tensor_t self, tensor_t grad, tensor_t master, tensor_t m, tensor_t v, float lr, float beta1,
+                                        float beta2, float eps, int step, float grad_scale) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (!dev_ok<DT>({grad}) || !dev_ok<DataType::Float>({master, m, v})) return OP_INPUT_ERROR;
+    const int64_t n = (int64_t)self->items();
+    if ((int64_t)grad->items() != n || (int64_t)master->items() != n || (int64_t)m->items() != n || (int64_t)v->items() != n) return OP_INPUT_ERROR;
+    // fp16 working weights are refreshed by the kernel; fp32 working weights are a copy of the master
+    void* w16 = DT == DataType::F16 ? mem_ : nullptr;
+    int st = brk_adam_step(master->data(), m->data(), v->data(), grad->data(), brk_dtype<DT>(), w16, n, lr, beta1, beta2, eps, step,
+                           grad_scale, sptr());
+    if (st == BRK_OK && DT == DataType::Float && master->data() != mem_)
+        BR_CUDA_CHECK(cudaMemcpyAsync(mem_, master->data(), self->bytes(), cudaMemcpyDeviceToDevice, stream()));
+    return ret(st);
+}
+
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_randn(tensor_t self, float mean, float std, uint64_t seed) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    return ret(brk_init_normal(mem_, (int64_t)self->items(), mean, std, seed, brk_dtype<DT>(), sptr()));
 }
 
 template struct CUDATensor<DataType::Float>;

@@ -187,6 +187,65 @@ BR_WORD(QueryKeyBackward, {
     t[0]->op_qk_backward(t[0], t[1], t[2], t[3], t[4]);
 })
 
+// ---- extension words ----
+// ( qkv lens out lse heads -- )
+BR_WORD(FlashAttn, {
+    int heads = (int)stack.pop_number();
+    auto t = pop_tensors<4>(stack);
+    t[0]->op_flash_attn(t[0], t[1], t[2], t[3], heads);
+})
+// ( dout qkv out lse lens dqkv heads -- )
+BR_WORD(FlashAttnBackward, {
+    int heads = (int)stack.pop_number();
+    auto t = pop_tensors<6>(stack);
+    t[0]->op_flash_attn_backward(t[0], t[1], t[2], t[3], t[4], t[5], heads);
+})
+// ( x w b residual y -- )
+BR_WORD(LinearResidual, {
+    auto t = pop_tensors<5>(stack);
+    t[0]->op_linear_residual(t[0], t[1], t[2], t[3], t[4]);
+})
+// ( x w b y y_gelu -- )
+BR_WORD(LinearGelu, {
+    auto t = pop_tensors<5>(stack);
+    t[0]->op_linear_gelu(t[0], t[1], t[2], t[3], t[4]);
+})
+// ( ids table out -- )
+BR_WORD(Embed, {
+    auto t = pop_tensors<3>(stack);
+    t[0]->op_embed(t[0], t[1], t[2]);
+})
+// ( dx ids table_g -- )
+BR_WORD(EmbedBackward, {
+    auto t = pop_tensors<3>(stack);
+    t[0]->op_embed_backward(t[0], t[1], t[2]);
+})
+// ( w grad master m v lr beta1 beta2 eps step grad_scale -- )
+BR_WORD(Adam, {
+    float gscale = (float)stack.pop_number();
+    int step = (int)stack.pop_number();
+    float eps = (float)stack.pop_number();
+    float b2 = (float)stack.pop_number();
+    float b1 = (float)stack.pop_number();
+    float lr = (float)stack.pop_number();
+    auto t = pop_tensors<5>(stack);
+    t[0]->op_adam(t[0], t[1], t[2], t[3], t[4], lr, b1, b2, eps, step, gscale);
+})
+// ( t mean std seed -- )
+BR_WORD(Randn, {
+    uint64_t seed = (uint64_t)stack.pop_number();
+    float std = (float)stack.pop_number();
+    float mean = (float)stack.pop_number();
+    tensor_t t = stack.pop_tensor();
+    t->op_randn(t, mean, std, seed);
+})
+// ( flag -- )  1: weight / bias gradients are added to, 0: overwritten (the reference behaviour)
+BR_WORD(Accumulate, { ComputingContext::grad_accumulate = stack.pop_number() != 0.0 ? 1 : 0; })
+// ( value -- )  factor applied to the loss gradient
+BR_WORD(LossScale, { ComputingContext::loss_scale = (float)stack.pop_number(); })
+// ( -- loss )  value of the most recent op.loss_backward
+BR_WORD(LastLoss, { stack.push_number((double)g_last_loss); })
+
 BR_WORD(IoDump, {
     tensor_t t = stack.pop_tensor();
     t->io_dump(t);
@@ -245,6 +304,18 @@ void load_nn_words(Enviroment& env) {
     env.insert_native_word("io.mpi.send", IoMpiSend::creator);
     env.insert_native_word("io.nccl.send", IoNcclSend::creator);
     env.insert_native_word("io.nccl.recv", IoNcclRecv::creator);
+
+    env.insert_native_word("op.flash_attn", FlashAttn::creator);
+    env.insert_native_word("op.flash_attn_backward", FlashAttnBackward::creator);
+    env.insert_native_word("op.linear_residual", LinearResidual::creator);
+    env.insert_native_word("op.linear_gelu", LinearGelu::creator);
+    env.insert_native_word("op.embed", Embed::creator);
+    env.insert_native_word("op.embed_backward", EmbedBackward::creator);
+    env.insert_native_word("op.adam", Adam::creator);
+    env.insert_native_word("op.randn", Randn::creator);
+    env.insert_native_word("op.accumulate", Accumulate::creator);
+    env.insert_native_word("op.loss_scale", LossScale::creator);
+    env.insert_native_word("op.last_loss", LastLoss::creator);
 
     env.insert_native_word("op.sync", Sync::creator);
     env.insert_native_word("op.create", Create::creator);

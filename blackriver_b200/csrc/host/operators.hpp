@@ -8,6 +8,7 @@
 // backend only overrides what it supports.
 #pragma once
 
+#include <cstdint>
 #include <memory>
 #include <variant>
 #include <vector>
@@ -76,6 +77,28 @@ struct TransformerComputing {
     virtual ComputingReturn op_softmax_backward(tensor_t self, tensor_t out, tensor_t x_g) { return OP_TODO_ERROR; }
     virtual ComputingReturn op_softmax_attn_backward(tensor_t self, tensor_t attn, tensor_t v, tensor_t attn_g, tensor_t v_g) { return OP_TODO_ERROR; }
     virtual ComputingReturn op_qk_backward(tensor_t self, tensor_t q, tensor_t k, tensor_t q_g, tensor_t k_g) { return OP_TODO_ERROR; }
+
+    // ---- extensions: not part of the reference interface (operators.hpp there ends above) ----
+    // Fused attention on the fused QKV projection.  self = qkv [B,T,3H] (q | k | v thirds), lens = int
+    // [B] valid lengths (host or device), out [B,T,H], lse [B,heads,T] fp32.  Stands for the
+    // transpos_0213 x3 / querykey / add alibi / add xmask / softmax / attn / transpos_0213 chain.
+    virtual ComputingReturn op_flash_attn(tensor_t self, tensor_t lens, tensor_t out, tensor_t lse, int heads) { return OP_TODO_ERROR; }
+    // self = d_out [B,T,H]; writes dqkv [B,T,3H].
+    virtual ComputingReturn op_flash_attn_backward(tensor_t self, tensor_t qkv, tensor_t out, tensor_t lse, tensor_t lens,
+                                                   tensor_t dqkv, int heads) { return OP_TODO_ERROR; }
+    // y = x W^T + b + residual  (op_linear followed by op_add, in the GEMM epilogue)
+    virtual ComputingReturn op_linear_residual(tensor_t self, tensor_t w, tensor_t bias, tensor_t residual, tensor_t y) { return OP_TODO_ERROR; }
+    // y = x W^T + b ; y_gelu = bloom_gelu(y)  (op_linear followed by op_gelu, in the GEMM epilogue)
+    virtual ComputingReturn op_linear_gelu(tensor_t self, tensor_t w, tensor_t bias, tensor_t y, tensor_t y_gelu) { return OP_TODO_ERROR; }
+    // self = ids (int, host or device) ; out[i,:] = table[ids[i],:]   (the feeder rank's gather, on the device)
+    virtual ComputingReturn op_embed(tensor_t self, tensor_t table, tensor_t out) { return OP_TODO_ERROR; }
+    // self = dx ; table_g[ids[i],:] += dx[i,:]
+    virtual ComputingReturn op_embed_backward(tensor_t self, tensor_t ids, tensor_t table_g) { return OP_TODO_ERROR; }
+    // self = working weights (fp16 or fp32) ; Adam on fp32 master / m / v, gradient multiplied by grad_scale
+    virtual ComputingReturn op_adam(tensor_t self, tensor_t grad, tensor_t master, tensor_t m, tensor_t v, float lr, float beta1,
+                                    float beta2, float eps, int step, float grad_scale) { return OP_TODO_ERROR; }
+    // self[i] ~ N(mean, std), seeded
+    virtual ComputingReturn op_randn(tensor_t self, float mean, float std, uint64_t seed) { return OP_TODO_ERROR; }
 };
 
 }  // namespace br

@@ -179,6 +179,48 @@ ComputingReturn TensorType::op_qk_backward(tensor_t self, tensor_t q, tensor_t k
     op_check(r, "qk_backward");
 }
 
+ComputingReturn TensorType::op_flash_attn(tensor_t self, tensor_t lens, tensor_t out, tensor_t lse, int heads) {
+    SELF_CHECK();
+    auto r = impl_->op_flash_attn(self, lens, out, lse, heads);
+    op_check(r, "flash_attn");
+}
+ComputingReturn TensorType::op_flash_attn_backward(tensor_t self, tensor_t qkv, tensor_t out, tensor_t lse, tensor_t lens, tensor_t dqkv, int heads) {
+    SELF_CHECK();
+    auto r = impl_->op_flash_attn_backward(self, qkv, out, lse, lens, dqkv, heads);
+    op_check(r, "flash_attn_backward");
+}
+ComputingReturn TensorType::op_linear_residual(tensor_t self, tensor_t w, tensor_t bias, tensor_t residual, tensor_t y) {
+    SELF_CHECK();
+    auto r = impl_->op_linear_residual(self, w, bias, residual, y);
+    op_check(r, "linear_residual");
+}
+ComputingReturn TensorType::op_linear_gelu(tensor_t self, tensor_t w, tensor_t bias, tensor_t y, tensor_t y_gelu) {
+    SELF_CHECK();
+    auto r = impl_->op_linear_gelu(self, w, bias, y, y_gelu);
+    op_check(r, "linear_gelu");
+}
+ComputingReturn TensorType::op_embed(tensor_t self, tensor_t table, tensor_t out) {
+    SELF_CHECK();
+    // ids may live on the host: the math runs in the table's backend
+    auto r = table->impl()->op_embed(self, table, out);
+    op_check(r, "embed");
+}
+ComputingReturn TensorType::op_embed_backward(tensor_t self, tensor_t ids, tensor_t table_g) {
+    SELF_CHECK();
+    auto r = impl_->op_embed_backward(self, ids, table_g);
+    op_check(r, "embed_backward");
+}
+ComputingReturn TensorType::op_adam(tensor_t self, tensor_t grad, tensor_t master, tensor_t m, tensor_t v, float lr, float beta1, float beta2, float eps, int step, float grad_scale) {
+    SELF_CHECK();
+    auto r = impl_->op_adam(self, grad, master, m, v, lr, beta1, beta2, eps, step, grad_scale);
+    op_check(r, "adam");
+}
+ComputingReturn TensorType::op_randn(tensor_t self, float mean, float std, uint64_t seed) {
+    SELF_CHECK();
+    auto r = impl_->op_randn(self, mean, std, seed);
+    op_check(r, "randn");
+}
+
 ComputingReturn TensorType::io_load(tensor_t self, const char* fileName) {
     SELF_CHECK();
     auto r = impl_->io_load(self, fileName);

@@ -144,6 +144,15 @@ struct TensorType : public TransformerComputing {
     ComputingReturn op_softmax_attn_backward(tensor_t self, tensor_t attn, tensor_t v, tensor_t attn_g, tensor_t v_g) override;
     ComputingReturn op_qk_backward(tensor_t self, tensor_t q, tensor_t k, tensor_t q_g, tensor_t k_g) override;
 
+    ComputingReturn op_flash_attn(tensor_t self, tensor_t lens, tensor_t out, tensor_t lse, int heads) override;
+    ComputingReturn op_flash_attn_backward(tensor_t self, tensor_t qkv, tensor_t out, tensor_t lse, tensor_t lens, tensor_t dqkv, int heads) override;
+    ComputingReturn op_linear_residual(tensor_t self, tensor_t w, tensor_t bias, tensor_t residual, tensor_t y) override;
+    ComputingReturn op_linear_gelu(tensor_t self, tensor_t w, tensor_t bias, tensor_t y, tensor_t y_gelu) override;
+    ComputingReturn op_embed(tensor_t self, tensor_t table, tensor_t out) override;
+    ComputingReturn op_embed_backward(tensor_t self, tensor_t ids, tensor_t table_g) override;
+    ComputingReturn op_adam(tensor_t self, tensor_t grad, tensor_t master, tensor_t m, tensor_t v, float lr, float beta1, float beta2, float eps, int step, float grad_scale) override;
+    ComputingReturn op_randn(tensor_t self, float mean, float std, uint64_t seed) override;
+
     ComputingReturn io_load(tensor_t self, const char* fileName) override;
     ComputingReturn io_save(tensor_t self, const char* fileName) override;
     ComputingReturn io_dump(tensor_t self) override;

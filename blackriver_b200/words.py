@@ -202,3 +202,220 @@ def var_elements(batch, tokens, hidden, heads, vocab, logits_rows):
     s = batch * tokens * hidden
     n = 2 * s + heads * tokens + batch * tokens * tokens + 3 * s + 2 * s + 3 * s + 8 * s + batch * heads * tokens * tokens
     return n + logits_rows * vocab
+
+
+# ==========================================================================================
+# Fused training scripts: whole model (or one pipeline stage of it) resident in HBM.
+#
+# Hash table 0 holds the constants, the stage-level parameters (embedding table / LM head,
+# embedding LayerNorm, final LayerNorm), the input tensors and the gradient scratch shared by all
+# layers; hash table i (1..n_layers) holds layer i-1 of the stage: its parameters as views of one
+# flat buffer (so the optimizer is one launch per layer), the matching flat gradient / master /
+# moment buffers, and the activations its backward pass needs.  Where the reference copies a
+# layer's weights from host memory into one device working set before every use (sync_layer,
+# bloomz-7b/init.words:237-293), here a layer is "brought in" by switching the hash table.
+# ==========================================================================================
+def _layer_param_layout(hidden):
+    """(name, shape, elements) in flat-buffer order; every offset is a multiple of 8 elements."""
+    h = hidden
+    spec = [
+        ("input_layernorm.weight", (h,)), ("input_layernorm.bias", (h,)),
+        ("query_key_value.weight", (3 * h, h)), ("query_key_value.bias", (3 * h,)),
+        ("dense.weight", (h, h)), ("dense.bias", (h,)),
+        ("post_attention_layernorm.weight", (h,)), ("post_attention_layernorm.bias", (h,)),
+        ("dense_h_to_4h.weight", (4 * h, h)), ("dense_h_to_4h.bias", (4 * h,)),
+        ("dense_4h_to_h.weight", (h, 4 * h)), ("dense_4h_to_h.bias", (h,)),
+    ]
+    out, off = [], 0
+    for name, shape in spec:
+        n = 1
+        for d in shape:
+            n *= d
+        out.append((name, shape, off, n))
+        off += (n + 7) // 8 * 8
+    return out, off
+
+
+def layer_param_elements(hidden):
+    return _layer_param_layout(hidden)[1]
+
+
+def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps=1e-5, first_stage=True, last_stage=True,
+                logits_rows=None, init_std=0.02, seed=0, layer_offset=0):
+    """Script text defining the whole stage.  After executing it:
+         build_model            allocates everything (call once)
+         init_model             seeded random initialisation (weights N(0, init_std), biases 0, LN 1/0)
+         model_forward / model_backward / zero_grads / ( lr step grad_scale -- ) optimizer_step
+       Inputs are written to "ids_", "mask_", "lens_" (host int tensors) in hash 0; on a stage that is
+       not the first the incoming activations go to "stage_in" and the outgoing gradient is
+       "stage_in_g"; on a stage that is not the last "stage_out" / "stage_out_g" play the same roles."""
+    assert hidden % heads == 0 and hidden % 8 == 0
+    layout, flat = _layer_param_layout(hidden)
+    n = batch * tokens
+    logits_rows = logits_rows or n
+    L = []
+    w = L.append
+    for name, val in (("VOCAB_SIZE", vocab), ("HIDDEN_SIZE", hidden), ("HEADS_NUM", heads), ("HEAD_HIDDEN", hidden // heads),
+                      ("LN_EPS", repr(float(eps))), ("HIDDEN_SIZE_x3", 3 * hidden), ("HIDDEN_SIZE_x4", 4 * hidden),
+                      ("LAYER_PARAMS", flat), ("TOKENS", n)):
+        w(f'{val} "{name}" !')
+    w(f'"{dtype}" "DTYPE" !')
+    w(f"{batch} $batch !  {tokens} $tokens !")
+    BTH = f'{batch} {tokens} "HIDDEN_SIZE" @ 3'
+
+    # ---- per-layer allocation (run inside the layer's hash) ----
+    w("%def create_layer_fused")      # runs inside a layer's hash table, so sizes and types are spelled out
+    for suffix, dt in (("", dtype), ("_g", dtype), (".master", "float"), (".m", "float"), (".v", "float")):
+        w(f'    {flat} 1 "cuda" "{dt}" op.create "_flat{suffix}" !')
+    for suffix in ("", "_g"):
+        for name, shape, off, cnt in layout:
+            dims = " ".join(str(d) for d in shape)
+            w(f'    "_flat{suffix}" @ {off} {dims} {len(shape)} op.view "{name}{suffix}" !')
+    for name, cols in (("xattn_in", 1), ("qkv", 3), ("attn_out", 1), ("xa", 1), ("xb", 1), ("x4a", 4), ("x4b", 4), ("xout", 1)):
+        w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "{dtype}" op.create "{name}" !')
+    w(f'    {batch} {heads} {tokens} 3 "cuda" "float" op.create "lse" !')
+    for name in ("ln_mean", "input_ln_var", "post_ln_var"):
+        w(f'    {n} 1 "cuda" "float" op.create "{name}" !')
+    w("%end")
+
+    # ---- layer math (run inside the layer's hash; xinput / yout_g / xin_g and the scratch are bound there) ----
+    def g(*names):
+        return " ".join(_get(x) for x in names)
+
+    w("%def layer_forward_fused")
+    w(f'    {g("xinput", "ln_mean", "input_ln_var", "input_layernorm.weight", "input_layernorm.bias", "xattn_in", "LN_EPS")} op.layernorm')
+    w(f'    {g("xattn_in", "query_key_value.weight", "query_key_value.bias", "qkv")} op.linear')
+    w(f'    {g("qkv", "lens_", "attn_out", "lse", "HEADS_NUM")} op.flash_attn')
+    w(f'    {g("attn_out", "dense.weight", "dense.bias", "xinput", "xa")} op.linear_residual')
+    w(f'    {g("xa", "ln_mean", "post_ln_var", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "xb", "LN_EPS")} op.layernorm')
+    w(f'    {g("xb", "dense_h_to_4h.weight", "dense_h_to_4h.bias", "x4a", "x4b")} op.linear_gelu')
+    w(f'    {g("x4b", "dense_4h_to_h.weight", "dense_4h_to_h.bias", "xa", "xout")} op.linear_residual')
+    w("%end")
+
+    w("%def layer_backward_fused")
+    w(f'    {g("yout_g", "x4b", "dense_4h_to_h.weight", "dense_4h_to_h.bias", "d4", "dense_4h_to_h.weight_g", "dense_4h_to_h.bias_g")} op.linear_backward')
+    w(f'    {g("d4", "x4a", "d4")} op.gelu_backward')
+    w(f'    {g("d4", "xb", "dense_h_to_4h.weight", "dense_h_to_4h.bias", "dh1", "dense_h_to_4h.weight_g", "dense_h_to_4h.bias_g")} op.linear_backward')
+    w(f'    {g("dh1", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "post_ln_var", "xb", "post_attention_layernorm.weight_g", "post_attention_layernorm.bias_g", "dh2", "LN_EPS")} op.layernorm_backward')
+    w(f'    {g("yout_g", "dh2", "dh2")} op.add')
+    w(f'    {g("dh2", "attn_out", "dense.weight", "dense.bias", "dh1", "dense.weight_g", "dense.bias_g")} op.linear_backward')
+    w(f'    {g("dh1", "qkv", "attn_out", "lse", "lens_", "dqkv", "HEADS_NUM")} op.flash_attn_backward')
+    w(f'    {g("dqkv", "xattn_in", "query_key_value.weight", "query_key_value.bias", "dh1", "query_key_value.weight_g", "query_key_value.bias_g")} op.linear_backward')
+    w(f'    {g("dh1", "input_layernorm.weight", "input_layernorm.bias", "input_ln_var", "xattn_in", "input_layernorm.weight_g", "input_layernorm.bias_g", "dh3", "LN_EPS")} op.layernorm_backward')
+    w(f'    {g("dh3", "dh2", "xin_g")} op.add')
+    w("%end")
+
+    # ---- ( seed -- ) seeded initialisation of one layer ----
+    w("%def init_layer_fused")
+    w('    "seed_" !')
+    w('    "_flat" @ op.zero')
+    for i, (name, shape, off, cnt) in enumerate(layout):
+        if name.endswith("layernorm.weight"):
+            w(f'    "{name}" @ 1.0 op.fill')
+        elif name.endswith(".weight"):
+            w(f'    "{name}" @ 0.0 {init_std} "seed_" @ 100 * {i} + op.randn')
+    w('    "_flat.master" @ "_flat" @ op.copy  "_flat.m" @ op.zero  "_flat.v" @ op.zero  "_flat_g" @ op.zero')
+    w('    "seed_" !!')
+    w("%end")
+
+    # ---- whole stage ----
+    w("%def build_model")
+    w("    0 #")
+    w(f'    {batch} {tokens} 2 "cpu" "int" op.create "ids_" !  {batch} {tokens} 2 "cpu" "int" op.create "mask_" !  {batch} 1 "cpu" "int" op.create "lens_" !')
+    for name, cols in (("d4", 4), ("dqkv", 3), ("dh1", 1), ("dh2", 1), ("dh3", 1), ("gA", 1), ("gB", 1)):
+        w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "DTYPE" @ op.create "{name}" !')
+    w(f'    {n} 1 "cuda" "float" op.create "ln_mean" !  {n} 1 "cuda" "float" op.create "emb_ln_var" !  {n} 1 "cuda" "float" op.create "ln_f_var" !')
+    main_params = []
+    if first_stage:
+        main_params += [("word_embeddings.weight", (vocab, hidden)), ("word_embeddings_layernorm.weight", (hidden,)),
+                        ("word_embeddings_layernorm.bias", (hidden,))]
+        w(f'    {BTH} "cuda" "DTYPE" @ op.create "emb_raw" !  {BTH} "cuda" "DTYPE" @ op.create "emb_out" !')
+    else:
+        w(f'    {BTH} "cuda" "DTYPE" @ op.create "stage_in" !')
+    if last_stage:
+        if not first_stage:
+            main_params += [("word_embeddings.weight", (vocab, hidden))]       # the tied LM head lives on this stage too
+        main_params += [("ln_f.weight", (hidden,)), ("ln_f.bias", (hidden,))]
+        w(f'    {BTH} "cuda" "DTYPE" @ op.create "xf" !  {BTH} "cuda" "DTYPE" @ op.create "xf_g" !')
+        w(f'    {logits_rows} "VOCAB_SIZE" @ 2 "cuda" "DTYPE" @ op.create "all_logits" !')
+    for name, shape in main_params:
+        dims = " ".join(str(d) for d in shape)
+        for suffix, dt in (("", '"DTYPE" @'), ("_g", '"DTYPE" @'), (".master", '"float"'), (".m", '"float"'), (".v", '"float"')):
+            w(f'    {dims} {len(shape)} "cuda" {dt} op.create "{name}{suffix}" !')
+    for i in range(1, n_layers + 1):
+        w(f"    {i} # create_layer_fused")
+    # bindings: scratch and inputs into every layer hash; activations chained layer to layer
+    shared = ("d4", "dqkv", "dh1", "dh2", "dh3", "lens_", "LN_EPS", "HEADS_NUM")
+    for i in range(1, n_layers + 1):
+        for name in shared:
+            w(f'    0 # "{name}" @ {i} # "{name}" !')
+        src = (f'{i - 1} # "xout" @' if i > 1 else ('0 # "emb_out" @' if first_stage else '0 # "stage_in" @'))
+        w(f'    {src} {i} # "xinput" !')
+        # gradient buffers alternate so a layer never reads and writes the same one
+        gin, gout = ("gA", "gB") if (n_layers - i) % 2 == 0 else ("gB", "gA")
+        w(f'    0 # "{gin}" @ {i} # "yout_g" !  0 # "{gout}" @ {i} # "xin_g" !')
+    w("    0 #")
+    w(f'    {n_layers} # "xout" @ 0 # "stage_out" !  {n_layers} # "yout_g" @ 0 # "stage_out_g" !  1 # "xin_g" @ 0 # "stage_in_g" !  0 #')
+    w("%end")
+
+    w("%def init_model")
+    w("    0 #")
+    sd = seed * 1000003
+    for k, (name, shape) in enumerate(main_params):
+        if name.endswith("layernorm.weight") or name == "ln_f.weight":
+            w(f'    "{name}" @ 1.0 op.fill')
+        elif name.endswith(".bias"):
+            w(f'    "{name}" @ op.zero')
+        else:
+            w(f'    "{name}" @ 0.0 {init_std} {sd + 7} op.randn')       # same seed on every stage that holds the tied table
+        w(f'    "{name}.master" @ "{name}" @ op.copy  "{name}.m" @ op.zero  "{name}.v" @ op.zero  "{name}_g" @ op.zero')
+    for i in range(1, n_layers + 1):
+        w(f"    {i} # {sd + 11 + layer_offset + i} init_layer_fused")
+    w("    0 #")
+    w("%end")
+
+    w("%def zero_grads")
+    w("    0 #")
+    for name, _ in main_params:
+        w(f'    "{name}_g" @ op.zero')
+    for i in range(1, n_layers + 1):
+        w(f'    {i} # "_flat_g" @ op.zero')
+    w("    0 #")
+    w("%end")
+
+    w("%def model_forward")
+    w("    0 #")
+    if first_stage:
+        w(f'    {g("ids_", "word_embeddings.weight", "emb_raw")} op.embed')
+        w(f'    {g("emb_raw", "ln_mean", "emb_ln_var", "word_embeddings_layernorm.weight", "word_embeddings_layernorm.bias", "emb_out", "LN_EPS")} op.layernorm')
+    for i in range(1, n_layers + 1):
+        w(f"    {i} # layer_forward_fused")
+    w("    0 #")
+    if last_stage:
+        w(f'    {g("stage_out", "ln_mean", "ln_f_var", "ln_f.weight", "ln_f.bias", "xf", "LN_EPS")} op.layernorm')
+    w("%end")
+
+    w("%def model_backward")
+    w("    0 #")
+    if last_stage:
+        w(f'    {g("xf", "ids_", "mask_", "word_embeddings.weight", "all_logits", "xf_g", "word_embeddings.weight_g")} op.loss_backward')
+        w(f'    {g("xf_g", "ln_f.weight", "ln_f.bias", "ln_f_var", "xf", "ln_f.weight_g", "ln_f.bias_g", "stage_out_g", "LN_EPS")} op.layernorm_backward')
+    for i in range(n_layers, 0, -1):
+        w(f"    {i} # layer_backward_fused")
+    w("    0 #")
+    if first_stage:
+        w(f'    {g("stage_in_g", "word_embeddings_layernorm.weight", "word_embeddings_layernorm.bias", "emb_ln_var", "emb_out", "word_embeddings_layernorm.weight_g", "word_embeddings_layernorm.bias_g", "emb_raw", "LN_EPS")} op.layernorm_backward')
+        w(f'    {g("emb_raw", "ids_", "word_embeddings.weight_g")} op.embed_backward')
+    w("%end")
+
+    # ( lr step grad_scale -- )
+    w("%def optimizer_step")
+    w('    0 #  "gs_" ! "step_" ! "lr_" !')
+    adam = '"lr_" @ 0.9 0.999 1e-08 "step_" @ "gs_" @ op.adam'
+    for name, _ in main_params:
+        w(f'    {g(name, name + "_g", name + ".master", name + ".m", name + ".v")} {adam}')
+    for i in range(1, n_layers + 1):
+        w(f'    0 # "lr_" @ "step_" @ "gs_" @  {i} # "gs_" ! "step_" ! "lr_" !  {g("_flat", "_flat_g", "_flat.master", "_flat.m", "_flat.v")} {adam}')
+    w('    0 #  "gs_" !! "step_" !! "lr_" !!')
+    w("%end")
+    return "\n".join(L) + "\n"

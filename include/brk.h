@@ -141,6 +141,19 @@ BRK_API void brk_alibi_slopes(int heads, double* slopes_out);
 BRK_API int brk_alibi_build(const double* slopes_dev, float* alibi, int heads, int tokens, void* stream);
 BRK_API int brk_xmask_build(const int32_t* mask, float* xmask, int batch, int tokens, void* stream);
 
+/* ---- parameter-side kernels (new: the reference has no optimizer, no embedding gradient and
+ * loads pretrained weights; kernels.h:147 only declares a parameter update) ------------------------
+ * Adam with torch.optim.Adam semantics on fp32 master weights and moments; `grad` is fp16 or fp32 and
+ * is multiplied by grad_scale first (un-scaling of loss-scaled gradients); w16 (may be NULL) receives
+ * the fp16 working copy.  step counts from 1.  Pointers 16-byte aligned. */
+BRK_API int brk_adam_step(void* master_w, void* m, void* v, const void* grad, int grad_dtype, void* w16, int64_t n, float lr,
+                  float beta1, float beta2, float eps, int step, float grad_scale, void* stream);
+/* table_g[ids[r], :] += dx[r, :]: gradient of brk_embedding_gather (atomic adds). */
+BRK_API int brk_embedding_scatter_add(const void* dx, const int32_t* ids, void* table_g, int64_t n, int64_t hidden, int64_t vocab,
+                              int dtype, void* stream);
+/* x[i] ~ N(mean, std), a pure function of (seed, i): seeded random initialisation on the device. */
+BRK_API int brk_init_normal(void* x, int64_t n, float mean, float std, uint64_t seed, int dtype, void* stream);
+
 /* ---- GEMM (fp32 SIMT parity path) ----------------------------------------------------------
  * C[b] = alpha * op(A[b]) * op(B[b]) + beta * C[b], row-major, op = transpose when the flag is
  * non-zero; op(A) is [m,k], op(B) is [k,n]; lda/ldb/ldc are row strides of the stored

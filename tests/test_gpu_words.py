@@ -26,10 +26,15 @@ def host():
     if not torch.cuda.is_available():
         pytest.fail("GPU tests need a CUDA device")
     from blackriver_b200 import host as _host
-    _host.context_boot(0, None, 256 << 20)
-    _host.collective_boot_local(0, 1)
+    try:
+        _host.context_boot(0, None, 256 << 20)
+        _host.collective_boot_local(0, 1)
+        owned = True
+    except _host.HostError:
+        owned = False          # another test module of this process booted it already
     yield _host
-    _host.context_shutdown()
+    if owned:
+        _host.context_shutdown()
 
 
 def make_layer(rng, hidden, trained_ln=False):
