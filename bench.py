@@ -1,23 +1,23 @@
 #!/usr/bin/env python
-"""Benchmark of the BLOOM decoder hot-path kernels on B200.
+"""Benchmark of the B200-native BLOOM decoder hot path.
 
-Workload (the operator microbench the headline metric is quoted on): fp16 storage, fp32
-accumulate, 8192 tokens per step, seed 1.  One step is one pass of
+Default workload (`--workload finetune`): one BLOOM-7b1-architecture fine-tune step with random
+initialisation -- 30 layers, hidden 4096, 32 heads x 128, MLP 16384, vocabulary 250880 with tied
+embedding, embedding LayerNorm, ALiBi; fp16 weights/activations, fp32 master weights and Adam;
+16 micro-batches of batch 2 x seq 1024 (32768 tokens per step) with right padding, valid lengths
+uniform in [512, 1024], seed 3; gradient accumulation over the micro-batches, then one optimizer
+step.  It runs through the reference-facing interface: the generated words scripts executed by the
+words machine on device tensors.  With N > 1 GPUs (torchrun) the 30 layers are split into N
+contiguous pipeline stages (embedding on the first rank, final LayerNorm + LM head + loss on the
+last) and the same 16 micro-batches flow through NCCL send/recv, so total work is fixed
+("scaling": "strong").  `value` is tokens/s; `e2e` times the same step including the host->device
+copy of every micro-batch's ids/mask/lengths and the device->host read of every loss (both are
+part of the step as the interface defines it).  `roofline` describes the dominant kernel of the
+step, the tcgen05 GEMM: FLOPs of all GEMM launches of one step / their summed CUDA-event time /
+measured bf16 tensor peak.  `kernels` adds the HBM-bound operator microbench (`--workload ops`:
+fp16, 8192 tokens, LayerNorm / GELU / log-softmax+NLL) in GB/s against the measured HBM peak.
 
-    LayerNorm fwd + bwd              on [8192, 4096]
-    bloom-GELU fwd + bwd             on [8192, 4096] and [8192, 16384]
-    log-softmax + NLL fwd + gradient on [8192, 250880] logits ~ N(0, 2), 10 % rows ignored
-
-`value` is tokens/s with every input resident in HBM; `e2e` is the same pass driven from
-pinned HOST buffers through the C ABI, with the host->device copy of every input and the
-device->host read of the losses inside the timed region.  `roofline` describes the dominant
-kernel (log-softmax + NLL + gradient): algorithmic bytes / CUDA-event time / measured HBM peak.
-`cpu_baseline` times the CPU oracle on a bounded sample of the same workload.
-
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-
-For N > 1 launch under torchrun; tokens are sharded by rank (no data-path collective, weak
-scaling: 8192 tokens per GPU).
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload finetune|ops]
 """
 import argparse
 import json
@@ -134,7 +134,7 @@ def make_host_inputs(torch, rank, dev):
     return h
 
 
-def run_ours(args):
+def run_ops(args, emit=True):
     import torch
     import torch.distributed as dist
     from blackriver_b200 import ops
@@ -145,7 +145,7 @@ def run_ours(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
     torch.cuda.set_device(local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
     peak, peak_kind = load_peaks()
@@ -292,6 +292,7 @@ def run_ours(args):
     value = world * TOKENS / (ms_per_step * 1e-3)
     e2e_value = world * TOKENS / (ms_e2e / e2e_steps * 1e-3)
 
+    out = None
     if rank == 0:
         es = 2
         masked = TOKENS - n_valid
@@ -326,9 +327,232 @@ def run_ours(args):
                     "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
             "roofline": roofline, "kernels": kern, "cpu_baseline": cpu, "loss": round(loss_val, 5),
         }
-        print(json.dumps(out), flush=True)
-    if world > 1:
+        if emit:
+            print(json.dumps(out), flush=True)
+    if world > 1 and emit:
         dist.destroy_process_group()
+    result = out if rank == 0 else None
+    del d, o, host
+    torch.cuda.empty_cache()
+    return result
+
+
+
+# ------------------------------------------------------------------------------------------
+# fine-tune workload (the default)
+# ------------------------------------------------------------------------------------------
+FT = dict(hidden=4096, heads=32, vocab=VOCAB, n_layers=30, batch=2, tokens=1024, n_micro=16, min_len=512, seed=3)
+FT_WORKLOAD = ("BLOOM-7b1-architecture fine-tune step, random init: 30 layers, hidden 4096, 32 heads x 128, MLP 16384, vocab 250880 "
+               "tied, embedding LayerNorm, ALiBi; fp16 weights/activations, fp32 master weights + Adam; 16 micro-batches of "
+               "batch 2 x seq 1024 (32768 tokens/step), right padding with lengths U[512,1024], seed 3; contiguous pipeline "
+               "stages over the GPUs")
+
+
+def load_tensor_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured sustained (MEASURED_PEAKS.json bf16_tflops_sustained)"
+    return 1400.0, "fallback 1.4 PFLOP/s sustained"
+
+
+def run_finetune(args):
+    import torch
+    import torch.distributed as dist
+    from blackriver_b200 import finetune, host
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = dict(FT)
+    if args.layers:
+        cfg["n_layers"] = args.layers
+    if args.micro:
+        cfg["n_micro"] = args.micro
+
+    # the HBM-bound operator microbench first (its buffers are released before the model is built)
+    ops_line = None
+    if not args.skip_ops and world == 1:
+        ops_args = argparse.Namespace(steps=50, warmup=3)
+        ops_line = run_ops(ops_args, emit=False)
+
+    # the library computes on torch's current stream so that torch events bracket its work
+    stream = torch.cuda.current_stream().cuda_stream
+    host.context_boot(local, stream, 512 << 20)
+    if world > 1:
+        box = [host.collective_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        host.collective_boot(rank, world, box[0])
+    else:
+        host.collective_boot_local(0, 1)
+
+    tr = finetune.Trainer(cfg["hidden"], cfg["heads"], cfg["vocab"], cfg["n_layers"], cfg["batch"], cfg["tokens"], cfg["n_micro"],
+                          rank=rank, world=world, seed=cfg["seed"], logits_rows=cfg["batch"] * cfg["tokens"])
+    mbs = finetune.make_microbatches(cfg["n_micro"], cfg["batch"], cfg["tokens"], cfg["vocab"], cfg["min_len"], cfg["seed"])
+    tokens_per_step = cfg["n_micro"] * cfg["batch"] * cfg["tokens"]
+    valid_per_step = int(sum(int(m[2].sum()) for m in mbs))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    loss = None
+    for _ in range(args.warmup):
+        loss = tr.step(mbs)
+    barrier()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    t0w = time.time()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = tr.step(mbs)
+    e1.record()
+    barrier()
+    t1w = time.time()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop(t0w, t1w) if rank == 0 else None
+
+    # ---- end to end: every micro-batch's ids / mask / lengths go host -> device and every loss comes
+    # back device -> host inside the step; here the step result is also read after each step --------
+    e2e_steps = max(1, min(args.steps, 3))
+    barrier()
+    f0 = torch.cuda.Event(enable_timing=True)
+    f1 = torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(e2e_steps):
+        loss = tr.step(mbs)
+        tr.sync()
+    f1.record()
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+
+    # ---- one instrumented step: device time per kernel family (CUDA events around every library call)
+    host.profile_start()
+    tr.step(mbs)
+    prof = host.profile_stop()
+    barrier()
+
+    if world > 1:
+        t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e = float(t[0]), float(t[1])
+        box = [loss]
+        dist.broadcast_object_list(box, src=world - 1)
+        loss = box[0]
+
+    if rank == 0:
+        ms_per_step = ms_total / args.steps
+        value = tokens_per_step / (ms_per_step * 1e-3)
+        e2e_value = tokens_per_step / (ms_e2e / e2e_steps * 1e-3)
+        feeds = 1 if world == 1 else 2
+        h2d = feeds * sum(m[0].nbytes + m[1].nbytes + m[2].nbytes for m in mbs)
+        d2h = cfg["n_micro"] * 8
+        peak_tf, peak_src = load_tensor_peak()
+        my_layers = tr.counts[0]
+        flops = cfg["n_micro"] * finetune.gemm_flops_per_microbatch(cfg["hidden"], cfg["vocab"], my_layers, cfg["batch"] * cfg["tokens"],
+                                                                  with_head=(world == 1))
+        gemm_ms = prof.get("gemm_f16", {}).get("ms", 0.0)
+        achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+        fam = {k: {"ms": round(v["ms"], 3), "calls": v["calls"]} for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"])}
+        launches = sum(v["calls"] for v in prof.values())
+        out = {
+            "metric": "tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate, f32 master weights",
+            "data": "synthetic",
+            "config": {"workload": FT_WORKLOAD, "layers": cfg["n_layers"], "micro_batches": cfg["n_micro"],
+                       "tokens_per_step": tokens_per_step, "valid_tokens_per_step": valid_per_step,
+                       "parallelism": "pp%d" % world, "stage_layers": tr.counts, "schedule": "all-forward-all-backward over micro-batch slots",
+                       "l2": "inputs larger than L2: per step every kernel streams >= 14 GB of weights and activations between re-uses"},
+            "clocks": clocks, "gpu_launches": launches * args.steps,
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps},
+            "roofline": {"kernel": "gemm_tc_kernel (tcgen05/TMEM, all GEMM launches of rank 0's stage in one step)",
+                         "bound": "tensor", "achieved": None if achieved is None else round(achieved, 1), "peak": peak_tf,
+                         "unit": "TFLOP/s", "frac": None if achieved is None else round(achieved / peak_tf, 3),
+                         "peak_source": peak_src, "traffic": None, "flops_per_step": flops, "ms_per_step": round(gemm_ms, 3)},
+            "step_profile_ms": fam,
+            "kernels": None if ops_line is None else ops_line.get("kernels"),
+            "ops_microbench": None if ops_line is None else {"value": ops_line["value"], "unit": "tokens/s",
+                                                             "roofline": ops_line["roofline"]},
+            "cpu_baseline": cpu_baseline_finetune(), "loss": None if loss is None else round(loss, 4),
+        }
+        print(json.dumps(out), flush=True)
+    tr.close()
+    if world > 1:
+        host.collective_shutdown()
+        dist.destroy_process_group()
+
+
+FT_CPU_LAYER_TOKENS = 32
+
+
+def cpu_finetune_parts(np, orc, layer_tokens, rng):
+    """Inputs of the CPU sample: one 7b1-shaped decoder layer on `layer_tokens` tokens and the LM head."""
+    H, heads = FT["hidden"], FT["heads"]
+    p = {}
+    for name in orc.LAYER_PARAMS:
+        if name.endswith("layernorm.weight"):
+            p[name] = np.ones(H, np.float32)
+        elif name.endswith(".bias"):
+            k = {"query_key_value": 3, "dense_h_to_4h": 4}.get(name.split(".")[0], 1)
+            p[name] = np.zeros(k * H, np.float32)
+        else:
+            o, i = {"query_key_value.weight": (3, 1), "dense.weight": (1, 1), "dense_h_to_4h.weight": (4, 1),
+                    "dense_4h_to_h.weight": (1, 4)}[name]
+            p[name] = rng.standard_normal((o * H, i * H), dtype=np.float32) * np.float32(0.02)
+    x = rng.standard_normal((1, layer_tokens, H), dtype=np.float32)
+    mask = np.ones((1, layer_tokens), np.int32)
+    return p, x, orc.alibi(heads, layer_tokens), orc.build_xmask(mask), heads
+
+
+def cpu_layer_seconds(orc, parts):
+    p, x, al, xm, heads = parts
+    t0 = time.perf_counter()
+    out, saved = orc.layer_forward(x, p, al, xm, heads)
+    orc.layer_backward(x, p, saved, heads)
+    return time.perf_counter() - t0
+
+
+def cpu_head_seconds_per_token(np, orc, rng, tokens=2):
+    H, V = FT["hidden"], FT["vocab"]
+    block = rng.standard_normal((1024, H), dtype=np.float32) * np.float32(0.02)
+    w = np.tile(block, (V // 1024 + 1, 1))[:V]                 # cheap to build; the arithmetic does not care
+    x = rng.standard_normal((1, tokens + 1, H), dtype=np.float32)
+    ids = rng.integers(0, V, (1, tokens + 1)).astype(np.int32)
+    mask = np.ones((1, tokens + 1), np.int32)
+    wg = np.zeros_like(w)
+    t0 = time.perf_counter()
+    orc.loss_backward(x, ids, mask, w, w_g=wg)
+    return (time.perf_counter() - t0) / tokens
+
+
+def cpu_baseline_finetune():
+    import numpy as np
+    from oracle import oracle as orc
+    rng = np.random.default_rng(FT["seed"])
+    parts = cpu_finetune_parts(np, orc, FT_CPU_LAYER_TOKENS, rng)
+    t_layer = min(cpu_layer_seconds(orc, parts) for _ in range(2))
+    t_head = cpu_head_seconds_per_token(np, orc, rng)
+    per_token = FT["n_layers"] * t_layer / FT_CPU_LAYER_TOKENS + t_head
+    return {"value": round(1.0 / per_token, 4), "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port",
+            "sample": f"fp32 CPU oracle (OpenMP): one 7b1-shaped decoder layer fwd+bwd on {FT_CPU_LAYER_TOKENS} tokens "
+                      f"({t_layer:.2f} s) and LM head + loss fwd+bwd on 2 tokens ({t_head:.2f} s/token); "
+                      "extrapolated to 30 layers + head per token, no optimizer"}
 
 
 def run_case(args):
@@ -360,6 +584,24 @@ def run_case(args):
             y, _, var = ops.layernorm(x, gamma, beta)
         for _ in range(reps):
             ops.layernorm_backward(dy, gamma, beta, var, y)
+    elif args.case == "gemm":
+        m, n, k = 2048, 16384, 4096          # the h -> 4h projection of one micro-batch
+        a = torch.randn(m, k, generator=g, device=dev).half()
+        b = torch.randn(n, k, generator=g, device=dev).half()
+        c = torch.empty(m, n, device=dev).half()
+        for _ in range(reps * 2):
+            ops.gemm_f16(a, b, c, m, n, k, 0, 1, k, k, n)
+    elif args.case == "attn":
+        from blackriver_b200 import brk
+        B, T, heads, d = 2, 1024, 32, 128
+        H = heads * d
+        qkv = torch.randn(B * T, 3 * H, generator=g, device=dev).half()
+        out = torch.empty(B * T, H, device=dev).half()
+        lse = torch.empty(B, heads, T, device=dev)
+        base = qkv.data_ptr()
+        for _ in range(reps):
+            brk.call("brk_flash_attn_fwd", base, base + 2 * H, base + 4 * H, 3 * H, out.data_ptr(), H, lse.data_ptr(), 0, 0,
+                     B, T, heads, d, ops.stream())
     else:
         x = torch.randn(TOKENS, HIDDEN4, generator=g, device=dev).half()
         dy = torch.randn(TOKENS, HIDDEN4, generator=g, device=dev).half()
@@ -430,29 +672,47 @@ def cpu_baseline(steps=3):
 
 
 def run_reference(args):
+    """Reference arm: the reference has no CPU implementation of this path (its cpu_tensor is storage
+    only), so this times the fp32 CPU restatement of its operator semantics on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
     import numpy as np
     from oracle import oracle as orc
-    rng = np.random.default_rng(SEED)
-    inputs = cpu_inputs(np, CPU_SAMPLE_TOKENS, rng)
-    for _ in range(max(1, min(args.warmup, 3))):
-        cpu_pass(orc, inputs)
-    ts = [cpu_pass(orc, inputs) for _ in range(args.steps)]
-    t = sum(ts) / len(ts)
-    value = CPU_SAMPLE_TOKENS / t
+    if args.workload == "ops":
+        rng = np.random.default_rng(SEED)
+        inputs = cpu_inputs(np, CPU_SAMPLE_TOKENS, rng)
+        for _ in range(max(1, min(args.warmup, 3))):
+            cpu_pass(orc, inputs)
+        ts = [cpu_pass(orc, inputs) for _ in range(args.steps)]
+        t = sum(ts) / len(ts)
+        value, workload, sample = CPU_SAMPLE_TOKENS / t, WORKLOAD, f"{CPU_SAMPLE_TOKENS} of the 8192 tokens per step"
+    else:
+        # each timed step = one 7b1-shaped decoder layer fwd+bwd on S tokens, S sized from --steps so that the
+        # run ends within a few minutes; the LM head + loss cost per token is measured once before the timed steps
+        rng = np.random.default_rng(FT["seed"])
+        budget = 150.0 / (args.steps + max(1, min(args.warmup, 3)))
+        layer_tokens = int(max(8, min(256, budget / 0.08)))
+        parts = cpu_finetune_parts(np, orc, layer_tokens, rng)
+        t_head = cpu_head_seconds_per_token(np, orc, rng)
+        for _ in range(max(1, min(args.warmup, 3))):
+            cpu_layer_seconds(orc, parts)
+        ts = [cpu_layer_seconds(orc, parts) for _ in range(args.steps)]
+        t = sum(ts) / len(ts)
+        value = 1.0 / (FT["n_layers"] * t / layer_tokens + t_head)
+        workload = FT_WORKLOAD
+        sample = (f"per step one decoder layer fwd+bwd on {layer_tokens} tokens ({t:.2f} s); LM head + loss {t_head:.2f} s/token "
+                  "measured once; tokens/s extrapolated to 30 layers + head, no optimizer")
     out = {
-        "impl": "reference", "metric": "tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
+        "impl": "reference", "metric": "tokens/s", "value": round(value, 4), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(t * 1e3, 3), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "the reference has no CPU implementation of these operators "
-                   "(its cpu_tensor is storage only); this arm times the fp32 CPU restatement of its operator "
-                   "semantics on the host cores, each step a bounded sample of the pass"},
-        "cpu_baseline": {"value": round(value, 1), "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port",
-                         "sample": f"{CPU_SAMPLE_TOKENS} of the 8192 tokens per step"},
-        "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "scaling": "strong" if args.workload != "ops" else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "note": "the reference has no CPU implementation of these operators (its cpu_tensor "
+                   "is storage only); this arm times the fp32 CPU restatement of its operator semantics on the host cores, "
+                   "each step a bounded sample of the workload"},
+        "cpu_baseline": {"value": round(value, 4), "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(out), flush=True)
 
@@ -460,21 +720,29 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu"],
+    ap.add_argument("--workload", default="finetune", choices=["finetune", "ops"])
+    ap.add_argument("--layers", type=int, default=0, help="fine-tune workload with fewer layers (development aid)")
+    ap.add_argument("--micro", type=int, default=0, help="fine-tune workload with fewer micro-batches (development aid)")
+    ap.add_argument("--skip-ops", action="store_true", help="do not run the operator microbench before the fine-tune step")
+    ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "attn"],
                     help="profiling aid: run a few launches of one kernel family on a small case and exit")
     ap.add_argument("--rows", type=int, default=1024, help="rows of the --case run")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 5 if args.workload == "finetune" else 200
     if args.case:
         return run_case(args)
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "ops":
+        run_ops(args)
     else:
-        run_ours(args)
+        run_finetune(args)
 
 
 if __name__ == "__main__":

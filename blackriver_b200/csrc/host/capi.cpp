@@ -135,6 +135,15 @@ int brh_env_tensor_read(void* env, const char* name, void* host, size_t bytes) {
     });
 }
 
+int brh_profile_start(void) { return guarded([] { Profiler::start(); }); }
+int brh_profile_stop(char* out, size_t cap) {
+    return guarded([&] {
+        std::string j = Profiler::report_json();
+        br_assert(j.size() + 1 <= cap, "profile buffer too small");
+        std::memcpy(out, j.c_str(), j.size() + 1);
+    });
+}
+
 float brh_last_loss(void) { return last_loss(); }
 
 }  // extern "C"

@@ -5,6 +5,8 @@
 #include <chrono>
 #include <cstring>
 #include <fstream>
+#include <map>
+#include <vector>
 #include <thread>
 
 namespace br {
@@ -19,6 +21,7 @@ void* ComputingContext::local_workspace = nullptr;
 size_t ComputingContext::workspace_size = 0;
 int ComputingContext::grad_accumulate = 0;
 float ComputingContext::loss_scale = 1.0f;
+int ComputingContext::verbose = 1;
 bool ComputingContext::booted = false;
 static bool g_owns_compute_stream = false;
 
@@ -63,6 +66,72 @@ void ComputingContext::shutdown() {
     cuda_stream = comm_stream = nullptr;
     workspace_size = 0;
     booted = false;
+}
+
+// ------------------------------------------------------------------------------------------
+bool Profiler::enabled = false;
+namespace {
+struct ProfRec {
+    const char* family;
+    cudaEvent_t e0, e1;
+};
+std::vector<ProfRec> g_prof;
+std::vector<cudaEvent_t> g_prof_pool;
+cudaEvent_t prof_event() {
+    if (!g_prof_pool.empty()) {
+        cudaEvent_t e = g_prof_pool.back();
+        g_prof_pool.pop_back();
+        return e;
+    }
+    cudaEvent_t e;
+    BR_CUDA_CHECK(cudaEventCreate(&e));
+    return e;
+}
+}  // namespace
+
+void Profiler::start() {
+    for (auto& r : g_prof) {
+        g_prof_pool.push_back(r.e0);
+        g_prof_pool.push_back(r.e1);
+    }
+    g_prof.clear();
+    enabled = true;
+}
+
+void Profiler::begin(const char* family) {
+    if (!enabled) return;
+    ProfRec r{family, prof_event(), prof_event()};
+    BR_CUDA_CHECK(cudaEventRecord(r.e0, ComputingContext::cuda_stream));
+    g_prof.push_back(r);
+}
+
+void Profiler::end() {
+    if (!enabled || g_prof.empty()) return;
+    BR_CUDA_CHECK(cudaEventRecord(g_prof.back().e1, ComputingContext::cuda_stream));
+}
+
+std::string Profiler::report_json() {
+    enabled = false;
+    if (ComputingContext::booted) BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::cuda_stream));
+    std::map<std::string, std::pair<double, long>> agg;
+    for (auto& r : g_prof) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, r.e0, r.e1) == cudaSuccess) {
+            auto& a = agg[r.family];
+            a.first += ms;
+            a.second += 1;
+        }
+    }
+    std::ostringstream ss;
+    ss << "{";
+    bool first = true;
+    for (auto& kv : agg) {
+        if (!first) ss << ", ";
+        first = false;
+        ss << "\"" << kv.first << "\": {\"ms\": " << kv.second.first << ", \"calls\": " << kv.second.second << "}";
+    }
+    ss << "}";
+    return ss.str();
 }
 
 // ------------------------------------------------------------------------------------------

@@ -34,11 +34,24 @@ struct ComputingContext {
     static int grad_accumulate;        // 1: op_linear_backward / op_layernorm_backward add into W_g, b_g (micro-batches)
     static float loss_scale;           // multiplies the loss gradient (fp16 gradients); Adam divides it out
 
+    static int verbose;                // 1: op_loss_backward prints its "#### items loss" line like the reference
+
     static bool booted;
     static void boot(int device, size_t workspace_bytes = (size_t)256 << 20);
     // adopt a stream owned by an embedding process (e.g. torch's current stream)
     static void boot_with_stream(int device, cudaStream_t compute, size_t workspace_bytes = (size_t)256 << 20);
     static void shutdown();
+};
+
+// Optional per-kernel-family timing of the device backend: when enabled, every kernel-library call
+// made by the backend is bracketed by CUDA events on the compute stream; report() waits for the
+// stream and returns the accumulated device time and call count per family.
+struct Profiler {
+    static bool enabled;
+    static void start();                       // clears previous records
+    static std::string report_json();          // {"family": {"ms": .., "calls": ..}, ...}; disables
+    static void begin(const char* family);
+    static void end();
 };
 
 struct CollectiveContext {

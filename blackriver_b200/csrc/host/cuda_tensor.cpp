@@ -30,6 +30,11 @@ inline ComputingReturn ret(int st) {
     return (ComputingReturn)st;
 }
 
+struct ProfScope {
+    explicit ProfScope(const char* family) { Profiler::begin(family); }
+    ~ProfScope() { Profiler::end(); }
+};
+
 // all operands of a math op must be device tensors of the op's element type
 template <DataType DT>
 inline bool dev_ok(std::initializer_list<tensor_t> ts) {
@@ -63,6 +68,7 @@ struct Scratch {
 template <DataType DT>
 inline int gemm_any(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int ta, int tb, int64_t lda,
                     int64_t ldb, int64_t ldc, float beta, const void* bias) {
+    ProfScope prof(DT == DataType::F16 ? "gemm_f16" : "gemm_f32");
     if (DT == DataType::F16 && (beta == 0.0f || beta == 1.0f) && brk_gemm_f16_supported(m, n, k, ta, tb, lda, ldb, a, b))
         return brk_gemm_f16(a, b, c, m, n, k, ta, tb, lda, ldb, ldc, bias, nullptr, 0, nullptr, 0, beta == 1.0f ? 1 : 0, sptr());
     return brk_gemm(a, b, c, m, n, k, ta, tb, lda, ldb, ldc, 1, 0, 0, 0, 1.0f, beta, bias, brk_dtype<DT>(), sptr());
@@ -187,6 +193,7 @@ ViewReturn CUDATensor<DT>::op_view(tensor_t self, size_t offset, const std::vect
 // ---- forward math ----------------------------------------------------------------------------------
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_add(tensor_t self, tensor_t b, tensor_t c) {
+    ProfScope prof("add");
     if (DT == DataType::Int) return OP_TODO_ERROR;
     if (!dev_ok<DT>({b})) return OP_INPUT_ERROR;
     if (!dev_ok<DT>({c}) || c->items() != self->items()) return OP_OUTPUT_ERROR;
@@ -213,6 +220,7 @@ ComputingReturn CUDATensor<DT>::op_linear(tensor_t self, tensor_t w, tensor_t bi
 
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_layernorm(tensor_t self, tensor_t mean, tensor_t var, tensor_t scale, tensor_t bias, tensor_t y, float eps) {
+    ProfScope prof("layernorm_fwd");
     if (DT == DataType::Int) return OP_TODO_ERROR;
     if (!dev_ok<DT>({scale, bias})) return OP_INPUT_ERROR;
     if (!dev_ok<DT>({y}) || !dev_ok<DataType::Float>({mean, var})) return OP_OUTPUT_ERROR;
@@ -268,6 +276,7 @@ ComputingReturn CUDATensor<DT>::op_attn(tensor_t self, tensor_t v, tensor_t attn
 
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_gelu(tensor_t self, tensor_t dst) {
+    ProfScope prof("gelu_fwd");
     if (DT == DataType::Int) return OP_TODO_ERROR;
     if (!dev_ok<DT>({dst}) || dst->items() != self->items()) return OP_OUTPUT_ERROR;
     return ret(brk_gelu_fwd(mem_, dst->data(), (int64_t)self->items(), brk_dtype<DT>(), sptr()));
@@ -361,7 +370,7 @@ LossReturn CUDATensor<DT>::op_loss_backward(tensor_t self, tensor_t ids_, tensor
         // logits = x W^T
         st = gemm_any<DT>(x, lm_head->data(), logits, rows, vocab, hidden, 0, 1, hidden, hidden, vocab, 0.0f, nullptr);
         // row losses and dlogits (in place)
-        if (st == BRK_OK) st = brk_logsoftmax_nll_fwd_bwd(logits, d_target + r0, d_rowloss + r0, logits, rows, vocab, scale, dt, sptr());
+        if (st == BRK_OK) { ProfScope prof("nll_fwd_bwd"); st = brk_logsoftmax_nll_fwd_bwd(logits, d_target + r0, d_rowloss + r0, logits, rows, vocab, scale, dt, sptr()); }
         // x_g = dlogits W
         if (st == BRK_OK) st = gemm_any<DT>(logits, lm_head->data(), dx, rows, hidden, vocab, 0, 0, vocab, hidden, hidden, 0.0f, nullptr);
         // W_g += dlogits^T x
@@ -377,7 +386,7 @@ LossReturn CUDATensor<DT>::op_loss_backward(tensor_t self, tensor_t ids_, tensor
     if (twin) cudaFree(twin);
     if (st != BRK_OK) return ret(st);
     float loss = total / (float)items;
-    std::cout << "#################  " << items << " " << loss << std::endl;
+    if (ComputingContext::verbose) std::cout << "#################  " << items << " " << loss << std::endl;
     return loss;
 }
 
@@ -385,6 +394,7 @@ LossReturn CUDATensor<DT>::op_loss_backward(tensor_t self, tensor_t ids_, tensor
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_layernorm_backward(tensor_t self, tensor_t scale, tensor_t bias, tensor_t var, tensor_t y,
                                                       tensor_t dscale, tensor_t dbias, tensor_t din, float eps) {
+    ProfScope prof("layernorm_bwd");
     if (DT == DataType::Int) return OP_TODO_ERROR;
     if (!dev_ok<DT>({scale, bias, y}) || !dev_ok<DataType::Float>({var})) return OP_INPUT_ERROR;
     if (!dev_ok<DT>({dscale, dbias, din}) || din->items() != self->items()) return OP_OUTPUT_ERROR;
@@ -412,7 +422,8 @@ ComputingReturn CUDATensor<DT>::op_linear_backward(tensor_t self, tensor_t x, te
     if (x_g->items() != x->items() || weight_g->items() != weight->items() || (int64_t)bias_g->items() != out) return OP_OUTPUT_ERROR;
     constexpr int dt = brk_dtype<DT>();
     const int acc = ComputingContext::grad_accumulate;
-    int st = brk_colsum(mem_, bias_g->data(), n, out, acc, dt, sptr());
+    int st;
+    { ProfScope prof("colsum"); st = brk_colsum(mem_, bias_g->data(), n, out, acc, dt, sptr()); }
     if (st == BRK_OK) st = gemm_any<DT>(mem_, x->data(), weight_g->data(), out, in, n, 1, 0, out, in, in, acc ? 1.0f : 0.0f, nullptr);
     if (st == BRK_OK) st = gemm_any<DT>(mem_, weight->data(), x_g->data(), n, in, out, 0, 0, out, in, in, 0.0f, nullptr);
     return ret(st);
@@ -420,6 +431,7 @@ ComputingReturn CUDATensor<DT>::op_linear_backward(tensor_t self, tensor_t x, te
 
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_gelu_backward(tensor_t self, tensor_t x, tensor_t x_g) {
+    ProfScope prof("gelu_bwd");
     if (DT == DataType::Int) return OP_TODO_ERROR;
     if (!dev_ok<DT>({x}) || x->items() != self->items()) return OP_INPUT_ERROR;
     if (!dev_ok<DT>({x_g}) || x_g->items() != self->items()) return OP_OUTPUT_ERROR;
@@ -526,6 +538,7 @@ const int32_t* int_on_device(const tensor_t& t, Scratch& sc) {
 
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_flash_attn(tensor_t self, tensor_t lens, tensor_t out, tensor_t lse, int heads) {
+    ProfScope prof("attention_fwd");
     if (DT != DataType::F16) return OP_TODO_ERROR;   // the fp32 parity path keeps the unfused operator chain
     if (self->shape().dim() != 3 || heads <= 0) return OP_INPUT_ERROR;
     const int batch = (int)self->shape()[0], tokens = (int)self->shape()[1];
@@ -546,6 +559,7 @@ ComputingReturn CUDATensor<DT>::op_flash_attn(tensor_t self, tensor_t lens, tens
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_flash_attn_backward(tensor_t self, tensor_t qkv, tensor_t out, tensor_t lse, tensor_t lens,
                                                        tensor_t dqkv, int heads) {
+    ProfScope prof("attention_bwd");
     if (DT != DataType::F16) return OP_TODO_ERROR;
     if (!dev_ok<DT>({qkv, out}) || qkv->shape().dim() != 3 || heads <= 0 || !dev_ok<DataType::Float>({lse})) return OP_INPUT_ERROR;
     const int batch = (int)qkv->shape()[0], tokens = (int)qkv->shape()[1];
@@ -574,6 +588,7 @@ ComputingReturn CUDATensor<DT>::op_linear_residual(tensor_t self, tensor_t w, te
     int64_t n = (int64_t)self->items() / in;
     if ((int64_t)w->shape()[1] != in || (int64_t)bias->items() != out || (int64_t)residual->items() != n * out) return OP_INPUT_ERROR;
     if ((int64_t)y->items() != n * out) return OP_OUTPUT_ERROR;
+    ProfScope prof(DT == DataType::F16 ? "gemm_f16" : "gemm_f32");
     if (DT == DataType::F16 && brk_gemm_f16_supported(n, out, in, 0, 1, in, in, mem_, w->data()))
         return ret(brk_gemm_f16(mem_, w->data(), y->data(), n, out, in, 0, 1, in, in, out, bias->data(), residual->data(), out,
                                 nullptr, 0, 0, sptr()));
@@ -592,6 +607,7 @@ ComputingReturn CUDATensor<DT>::op_linear_gelu(tensor_t self, tensor_t w, tensor
     int64_t n = (int64_t)self->items() / in;
     if ((int64_t)w->shape()[1] != in || (int64_t)bias->items() != out) return OP_INPUT_ERROR;
     if ((int64_t)y->items() != n * out || y_gelu->items() != y->items()) return OP_OUTPUT_ERROR;
+    ProfScope prof(DT == DataType::F16 ? "gemm_f16" : "gemm_f32");
     if (DT == DataType::F16 && brk_gemm_f16_supported(n, out, in, 0, 1, in, in, mem_, w->data()))
         return ret(brk_gemm_f16(mem_, w->data(), y->data(), n, out, in, 0, 1, in, in, out, bias->data(), nullptr, 0, y_gelu->data(), out,
                                 0, sptr()));
@@ -603,6 +619,7 @@ ComputingReturn CUDATensor<DT>::op_linear_gelu(tensor_t self, tensor_t w, tensor
 // self = ids; the call is routed here through the TABLE's backend, so DT is the table's type
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_embed(tensor_t self, tensor_t table, tensor_t out) {
+    ProfScope prof("embedding");
     if (DT == DataType::Int) return OP_TODO_ERROR;
     if (self->dtype() != DataType::Int || table->shape().dim() != 2) return OP_INPUT_ERROR;
     const int64_t n = (int64_t)self->items(), vocab = (int64_t)table->shape()[0], hidden = (int64_t)table->shape()[1];
@@ -614,6 +631,7 @@ ComputingReturn CUDATensor<DT>::op_embed(tensor_t self, tensor_t table, tensor_t
 
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_embed_backward(tensor_t self, tensor_t ids_, tensor_t table_g) {
+    ProfScope prof("embedding");
     if (DT == DataType::Int) return OP_TODO_ERROR;
     if (!ids_ || ids_->dtype() != DataType::Int) return OP_INPUT_ERROR;
     if (!dev_ok<DT>({table_g}) || table_g->shape().dim() != 2) return OP_OUTPUT_ERROR;
@@ -627,6 +645,7 @@ ComputingReturn CUDATensor<DT>::op_embed_backward(tensor_t self, tensor_t ids_, 
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_adam(tensor_t self, tensor_t grad, tensor_t master, tensor_t m, tensor_t v, float lr, float beta1,
                                         float beta2, float eps, int step, float grad_scale) {
+    ProfScope prof("adam");
     if (DT == DataType::Int) return OP_TODO_ERROR;
     if (!dev_ok<DT>({grad}) || !dev_ok<DataType::Float>({master, m, v})) return OP_INPUT_ERROR;
     const int64_t n = (int64_t)self->items();
@@ -638,6 +657,17 @@ ComputingReturn CUDATensor<DT>::op_adam(tensor_t self, tensor_t grad, tensor_t m
     if (st == BRK_OK && DT == DataType::Float && master->data() != mem_)
         BR_CUDA_CHECK(cudaMemcpyAsync(mem_, master->data(), self->bytes(), cudaMemcpyDeviceToDevice, stream()));
     return ret(st);
+}
+
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) {
+    if (!CollectiveContext::has_comm) return OP_ATTR_ERROR;
+    if (!recv || !recv->is_cuda()) return OP_OUTPUT_ERROR;
+    BR_NCCL_CHECK(ncclGroupStart());
+    BR_NCCL_CHECK(ncclSend(mem_, self->bytes(), ncclChar, peer, CollectiveContext::nccl_comm, stream()));
+    BR_NCCL_CHECK(ncclRecv(recv->data(), recv->bytes(), ncclChar, peer, CollectiveContext::nccl_comm, stream()));
+    BR_NCCL_CHECK(ncclGroupEnd());
+    return OP_OK;
 }
 
 template <DataType DT>

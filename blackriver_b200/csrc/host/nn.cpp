@@ -239,10 +239,18 @@ BR_WORD(Randn, {
     tensor_t t = stack.pop_tensor();
     t->op_randn(t, mean, std, seed);
 })
+// ( send_t recv_t peer -- )  grouped send + receive with one peer
+BR_WORD(IoNcclSendRecv, {
+    int peer = (int)stack.pop_number();
+    auto t = pop_tensors<2>(stack);
+    t[0]->io_nccl_sendrecv(t[0], t[1], peer);
+})
 // ( flag -- )  1: weight / bias gradients are added to, 0: overwritten (the reference behaviour)
 BR_WORD(Accumulate, { ComputingContext::grad_accumulate = stack.pop_number() != 0.0 ? 1 : 0; })
 // ( value -- )  factor applied to the loss gradient
 BR_WORD(LossScale, { ComputingContext::loss_scale = (float)stack.pop_number(); })
+// ( flag -- )  0 silences the per-call loss line of op.loss_backward
+BR_WORD(Verbose, { ComputingContext::verbose = stack.pop_number() != 0.0 ? 1 : 0; })
 // ( -- loss )  value of the most recent op.loss_backward
 BR_WORD(LastLoss, { stack.push_number((double)g_last_loss); })
 
@@ -305,6 +313,7 @@ void load_nn_words(Enviroment& env) {
     env.insert_native_word("io.nccl.send", IoNcclSend::creator);
     env.insert_native_word("io.nccl.recv", IoNcclRecv::creator);
 
+    env.insert_native_word("io.nccl.sendrecv", IoNcclSendRecv::creator);
     env.insert_native_word("op.flash_attn", FlashAttn::creator);
     env.insert_native_word("op.flash_attn_backward", FlashAttnBackward::creator);
     env.insert_native_word("op.linear_residual", LinearResidual::creator);
@@ -316,6 +325,7 @@ void load_nn_words(Enviroment& env) {
     env.insert_native_word("op.accumulate", Accumulate::creator);
     env.insert_native_word("op.loss_scale", LossScale::creator);
     env.insert_native_word("op.last_loss", LastLoss::creator);
+    env.insert_native_word("op.verbose", Verbose::creator);
 
     env.insert_native_word("op.sync", Sync::creator);
     env.insert_native_word("op.create", Create::creator);

@@ -97,6 +97,9 @@ struct TransformerComputing {
     // self = working weights (fp16 or fp32) ; Adam on fp32 master / m / v, gradient multiplied by grad_scale
     virtual ComputingReturn op_adam(tensor_t self, tensor_t grad, tensor_t master, tensor_t m, tensor_t v, float lr, float beta1,
                                     float beta2, float eps, int step, float grad_scale) { return OP_TODO_ERROR; }
+    // simultaneous exchange with one peer: send self, receive into `recv` (one NCCL group, so two ranks
+    // that both call it towards each other cannot block one another)
+    virtual ComputingReturn io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) { return OP_TODO_ERROR; }
     // self[i] ~ N(mean, std), seeded
     virtual ComputingReturn op_randn(tensor_t self, float mean, float std, uint64_t seed) { return OP_TODO_ERROR; }
 };

@@ -221,6 +221,12 @@ ComputingReturn TensorType::op_randn(tensor_t self, float mean, float std, uint6
     op_check(r, "randn");
 }
 
+ComputingReturn TensorType::io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) {
+    SELF_CHECK();
+    auto r = impl_->io_nccl_sendrecv(self, recv, peer);
+    op_check(r, "nccl_sendrecv");
+}
+
 ComputingReturn TensorType::io_load(tensor_t self, const char* fileName) {
     SELF_CHECK();
     auto r = impl_->io_load(self, fileName);

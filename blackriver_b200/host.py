@@ -40,6 +40,8 @@ SIGNATURES = {
     "brh_env_tensor_write": (i32, [p, cstr, p, sz]),
     "brh_env_tensor_read": (i32, [p, cstr, p, sz]),
     "brh_last_loss": (f32, []),
+    "brh_profile_start": (i32, []),
+    "brh_profile_stop": (i32, [C.c_char_p, sz]),
 }
 
 _lib = None
@@ -184,6 +186,18 @@ class Env:
         a = np.empty(info["shape"], dtype=_NP[info["dtype"]])
         _check(lib().brh_env_tensor_read(self._h, name.encode(), a.ctypes.data_as(p), a.nbytes))
         return a
+
+
+def profile_start():
+    _check(lib().brh_profile_start())
+
+
+def profile_stop():
+    """Returns {family: {"ms": device milliseconds, "calls": launches}} and switches profiling off."""
+    import json
+    buf = C.create_string_buffer(1 << 16)
+    _check(lib().brh_profile_stop(buf, 1 << 16))
+    return json.loads(buf.value.decode())
 
 
 def last_loss():

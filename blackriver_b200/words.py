@@ -241,14 +241,21 @@ def layer_param_elements(hidden):
 
 
 def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps=1e-5, first_stage=True, last_stage=True,
-                logits_rows=None, init_std=0.02, seed=0, layer_offset=0):
+                logits_rows=None, init_std=0.02, seed=0, layer_offset=0, n_slots=1, prev_rank=None, next_rank=None):
     """Script text defining the whole stage.  After executing it:
          build_model            allocates everything (call once)
          init_model             seeded random initialisation (weights N(0, init_std), biases 0, LN 1/0)
          model_forward / model_backward / zero_grads / ( lr step grad_scale -- ) optimizer_step
        Inputs are written to "ids_", "mask_", "lens_" (host int tensors) in hash 0; on a stage that is
        not the first the incoming activations go to "stage_in" and the outgoing gradient is
-       "stage_in_g"; on a stage that is not the last "stage_out" / "stage_out_g" play the same roles."""
+       "stage_in_g"; on a stage that is not the last "stage_out" / "stage_out_g" play the same roles.
+       Pipeline use: n_slots > 1 keeps that many micro-batches' saved activations at once; `slot_k`
+       selects the set the next forward / backward works on, and stage_forward / stage_backward add the
+       NCCL receive from / send to prev_rank and next_rank around model_forward / model_backward."""
+    SLOTTED = ("xattn_in", "qkv", "attn_out", "xb", "x4a", "x4b", "lse", "input_ln_var", "post_ln_var")
+
+    def slot_names(name):
+        return [name] if n_slots == 1 else [f"{name}@{k}" for k in range(n_slots)]
     assert hidden % heads == 0 and hidden % 8 == 0
     layout, flat = _layer_param_layout(hidden)
     n = batch * tokens
@@ -272,10 +279,14 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
             dims = " ".join(str(d) for d in shape)
             w(f'    "_flat{suffix}" @ {off} {dims} {len(shape)} op.view "{name}{suffix}" !')
     for name, cols in (("xattn_in", 1), ("qkv", 3), ("attn_out", 1), ("xa", 1), ("xb", 1), ("x4a", 4), ("x4b", 4), ("xout", 1)):
-        w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "{dtype}" op.create "{name}" !')
-    w(f'    {batch} {heads} {tokens} 3 "cuda" "float" op.create "lse" !')
-    for name in ("ln_mean", "input_ln_var", "post_ln_var"):
-        w(f'    {n} 1 "cuda" "float" op.create "{name}" !')
+        for nm in (slot_names(name) if name in SLOTTED else [name]):
+            w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "{dtype}" op.create "{nm}" !')
+    for nm in slot_names("lse"):
+        w(f'    {batch} {heads} {tokens} 3 "cuda" "float" op.create "{nm}" !')
+    w(f'    {n} 1 "cuda" "float" op.create "ln_mean" !')
+    for name in ("input_ln_var", "post_ln_var"):
+        for nm in slot_names(name):
+            w(f'    {n} 1 "cuda" "float" op.create "{nm}" !')
     w("%end")
 
     # ---- layer math (run inside the layer's hash; xinput / yout_g / xin_g and the scratch are bound there) ----
@@ -324,24 +335,32 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w(f'    {batch} {tokens} 2 "cpu" "int" op.create "ids_" !  {batch} {tokens} 2 "cpu" "int" op.create "mask_" !  {batch} 1 "cpu" "int" op.create "lens_" !')
     for name, cols in (("d4", 4), ("dqkv", 3), ("dh1", 1), ("dh2", 1), ("dh3", 1), ("gA", 1), ("gB", 1)):
         w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "DTYPE" @ op.create "{name}" !')
-    w(f'    {n} 1 "cuda" "float" op.create "ln_mean" !  {n} 1 "cuda" "float" op.create "emb_ln_var" !  {n} 1 "cuda" "float" op.create "ln_f_var" !')
+    w(f'    {n} 1 "cuda" "float" op.create "ln_mean" !')
+    for nm in slot_names("emb_ln_var") + slot_names("ln_f_var"):
+        w(f'    {n} 1 "cuda" "float" op.create "{nm}" !')
     main_params = []
     if first_stage:
         main_params += [("word_embeddings.weight", (vocab, hidden)), ("word_embeddings_layernorm.weight", (hidden,)),
                         ("word_embeddings_layernorm.bias", (hidden,))]
-        w(f'    {BTH} "cuda" "DTYPE" @ op.create "emb_raw" !  {BTH} "cuda" "DTYPE" @ op.create "emb_out" !')
+        w(f'    {BTH} "cuda" "DTYPE" @ op.create "emb_raw" !')
+        for nm in slot_names("emb_out"):
+            w(f'    {BTH} "cuda" "DTYPE" @ op.create "{nm}" !')
     else:
         w(f'    {BTH} "cuda" "DTYPE" @ op.create "stage_in" !')
     if last_stage:
         if not first_stage:
             main_params += [("word_embeddings.weight", (vocab, hidden))]       # the tied LM head lives on this stage too
         main_params += [("ln_f.weight", (hidden,)), ("ln_f.bias", (hidden,))]
-        w(f'    {BTH} "cuda" "DTYPE" @ op.create "xf" !  {BTH} "cuda" "DTYPE" @ op.create "xf_g" !')
+        w(f'    {BTH} "cuda" "DTYPE" @ op.create "xf_g" !')
+        for nm in slot_names("xf"):
+            w(f'    {BTH} "cuda" "DTYPE" @ op.create "{nm}" !')
         w(f'    {logits_rows} "VOCAB_SIZE" @ 2 "cuda" "DTYPE" @ op.create "all_logits" !')
     for name, shape in main_params:
         dims = " ".join(str(d) for d in shape)
         for suffix, dt in (("", '"DTYPE" @'), ("_g", '"DTYPE" @'), (".master", '"float"'), (".m", '"float"'), (".v", '"float"')):
             w(f'    {dims} {len(shape)} "cuda" {dt} op.create "{name}{suffix}" !')
+    if (first_stage != last_stage) and (prev_rank is not None or next_rank is not None):
+        w(f'    "VOCAB_SIZE" @ "HIDDEN_SIZE" @ 2 "cuda" "DTYPE" @ op.create "tied_recv" !')
     for i in range(1, n_layers + 1):
         w(f"    {i} # create_layer_fused")
     # bindings: scratch and inputs into every layer hash; activations chained layer to layer
@@ -350,13 +369,28 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         for name in shared:
             w(f'    0 # "{name}" @ {i} # "{name}" !')
         src = (f'{i - 1} # "xout" @' if i > 1 else ('0 # "emb_out" @' if first_stage else '0 # "stage_in" @'))
-        w(f'    {src} {i} # "xinput" !')
+        if not (i == 1 and first_stage and n_slots > 1):      # with slots the embedding output is bound by slot_k
+            w(f'    {src} {i} # "xinput" !')
         # gradient buffers alternate so a layer never reads and writes the same one
         gin, gout = ("gA", "gB") if (n_layers - i) % 2 == 0 else ("gB", "gA")
         w(f'    0 # "{gin}" @ {i} # "yout_g" !  0 # "{gout}" @ {i} # "xin_g" !')
     w("    0 #")
     w(f'    {n_layers} # "xout" @ 0 # "stage_out" !  {n_layers} # "yout_g" @ 0 # "stage_out_g" !  1 # "xin_g" @ 0 # "stage_in_g" !  0 #')
     w("%end")
+
+    # ---- slot selection: which micro-batch's saved activations the layer words see ----
+    for k in range(n_slots):
+        w(f"%def slot_{k}")
+        if n_slots > 1:
+            w("    0 #")
+            for name in (["emb_out", "emb_ln_var"] if first_stage else []) + (["xf", "ln_f_var"] if last_stage else []):
+                w(f'    "{name}@{k}" @ "{name}" !')
+            if first_stage:
+                w(f'    "emb_out" @ 1 # "xinput" ! 0 #')
+            for i in range(1, n_layers + 1):
+                w(f"    {i} #  " + "  ".join(f'"{name}@{k}" @ "{name}" !' for name in SLOTTED))
+        w("    0 #")
+        w("%end")
 
     w("%def init_model")
     w("    0 #")
@@ -418,4 +452,28 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         w(f'    0 # "lr_" @ "step_" @ "gs_" @  {i} # "gs_" ! "step_" ! "lr_" !  {g("_flat", "_flat_g", "_flat.master", "_flat.m", "_flat.v")} {adam}')
     w('    0 #  "gs_" !! "step_" !! "lr_" !!')
     w("%end")
+
+    # ---- pipeline hand-offs around the stage's forward / backward ----
+    w("%def stage_forward")
+    if prev_rank is not None:
+        w(f'    0 # "stage_in" @ {prev_rank} io.nccl.recv')
+    w("    model_forward")
+    if next_rank is not None:
+        w(f'    0 # "stage_out" @ {next_rank} io.nccl.send')
+    w("%end")
+    w("%def stage_backward")
+    if next_rank is not None:
+        w(f'    0 # "stage_out_g" @ {next_rank} io.nccl.recv')
+    w("    model_backward")
+    if prev_rank is not None:
+        w(f'    0 # "stage_in_g" @ {prev_rank} io.nccl.send')
+    w("%end")
+    # ( peer -- )  both holders of the tied embedding / LM-head table sum their gradients
+    w("%def sync_tied_grads")
+    w('    0 # "peer_" !')
+    w('    "word_embeddings.weight_g" @ "tied_recv" @ "peer_" @ io.nccl.sendrecv')
+    w('    "word_embeddings.weight_g" @ "tied_recv" @ "word_embeddings.weight_g" @ op.add')
+    w('    "peer_" !!')
+    w("%end")
+
     return "\n".join(L) + "\n"

@@ -65,6 +65,12 @@ BRH_API int brh_env_tensor_info(void* env, const char* name, void** data, int* i
 BRH_API int brh_env_tensor_write(void* env, const char* name, const void* host, size_t bytes);
 BRH_API int brh_env_tensor_read(void* env, const char* name, void* host, size_t bytes);
 
+/* Per-kernel-family device timing of the backend (CUDA events around every kernel-library call).
+ * brh_profile_stop waits for the stream, writes a JSON object {"family": {"ms":..,"calls":..}} into
+ * `out` and switches profiling off. */
+BRH_API int brh_profile_start(void);
+BRH_API int brh_profile_stop(char* out, size_t cap);
+
 /* Value returned by the most recent op.loss_backward word. */
 BRH_API float brh_last_loss(void);
 
