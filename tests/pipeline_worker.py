@@ -1,0 +1,97 @@
+"""Worker for the pipeline tests: run under torchrun with WORLD_SIZE ranks.
+
+backend nccl (GPU): trains a small model for two steps as a WORLD_SIZE-stage pipeline, then rank 0
+trains the same model on one GPU and compares losses and updated weights.
+backend gloo (CPU): checks the host-side logic only -- stage partition, identical micro-batches on
+every rank, stage scripts compile in the words machine."""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from blackriver_b200 import finetune, host, words  # noqa: E402
+
+CFG = dict(hidden=128, heads=2, vocab=512, n_layers=4, batch=2, tokens=64, n_micro=4)
+
+
+def main():
+    backend = sys.argv[1]
+    out_path = sys.argv[2]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    mbs = finetune.make_microbatches(CFG["n_micro"], CFG["batch"], CFG["tokens"], CFG["vocab"], 20, seed=5)
+    counts = finetune.partition_layers(CFG["n_layers"], world, head_cost=0.5)
+    if backend == "gloo":
+        dist.init_process_group("gloo")
+        gathered = [None] * world
+        digest = [int(np.sum([m[0].astype(np.int64).sum() for m in mbs])), counts]
+        dist.all_gather_object(gathered, digest)
+        assert all(g == gathered[0] for g in gathered), "ranks disagree on inputs or partition"
+        assert sum(counts) == CFG["n_layers"] and all(c >= 1 for c in counts)
+        first, last = rank == 0, rank == world - 1
+        env = host.Env(counts[rank] + 1)
+        env.execute(words.fused_words(hidden=CFG["hidden"], heads=CFG["heads"], vocab=CFG["vocab"], n_layers=counts[rank],
+                                      batch=CFG["batch"], tokens=CFG["tokens"], first_stage=first, last_stage=last,
+                                      n_slots=CFG["n_micro"], prev_rank=None if first else rank - 1,
+                                      next_rank=None if last else rank + 1, layer_offset=sum(counts[:rank])))
+        prog = env.build("slot_1 stage_forward slot_1 stage_backward")     # links every word of the stage
+        env.free_program(prog)
+        env.close()
+        dist.barrier()
+        if rank == 0:
+            json.dump({"ok": True, "counts": counts}, open(out_path, "w"))
+        dist.destroy_process_group()
+        return
+
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    host.context_boot(local, torch.cuda.current_stream().cuda_stream, 128 << 20)
+    box = [host.collective_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    host.collective_boot(rank, world, box[0])
+    orig = finetune.partition_layers
+    finetune.partition_layers = lambda n, w, head_cost=0.5: orig(n, w, 0.5)
+    tr = finetune.Trainer(CFG["hidden"], CFG["heads"], CFG["vocab"], CFG["n_layers"], CFG["batch"], CFG["tokens"], CFG["n_micro"],
+                          rank=rank, world=world, seed=9, lr=1e-3, init_std=0.05)
+    losses = [tr.step(mbs) for _ in range(2)]
+    tr.sync()
+    tr.env.change(1)
+    w_first = tr.env.read("_flat.master").copy()          # first layer of this stage
+    tr.env.change(0)
+    table = tr.env.read("word_embeddings.weight.master").copy() if (rank == 0 or rank == world - 1) else None
+    box = [losses]
+    dist.broadcast_object_list(box, src=world - 1)
+    pipe_losses = box[0]
+    tables = [None] * world
+    dist.all_gather_object(tables, None if table is None else float(np.abs(table).sum()))
+    tr.close()
+    if rank == 0:
+        single = finetune.Trainer(CFG["hidden"], CFG["heads"], CFG["vocab"], CFG["n_layers"], CFG["batch"], CFG["tokens"],
+                                  CFG["n_micro"], rank=0, world=1, seed=9, lr=1e-3, init_std=0.05)
+        ref_losses = [single.step(mbs) for _ in range(2)]
+        single.sync()
+        single.env.change(1)
+        ref_w = single.env.read("_flat.master").copy()
+        single.env.change(0)
+        ref_table = single.env.read("word_embeddings.weight.master").copy()
+        single.close()
+        res = {
+            "pipe_losses": pipe_losses, "ref_losses": ref_losses,
+            "w_err": float(np.abs(w_first - ref_w).max() / np.abs(ref_w).max()),
+            "table_err": float(np.abs(table - ref_table).max() / np.abs(ref_table).max()),
+            "tables_agree": abs(tables[0] - tables[-1]) <= 1e-6 * abs(tables[0]),
+            "counts": tr.counts,
+        }
+        json.dump(res, open(out_path, "w"))
+    dist.barrier()
+    host.collective_shutdown()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
