@@ -489,7 +489,7 @@ def run_finetune(args):
             "kernels": None if ops_line is None else ops_line.get("kernels"),
             "ops_microbench": None if ops_line is None else {"value": ops_line["value"], "unit": "tokens/s",
                                                              "roofline": ops_line["roofline"]},
-            "cpu_baseline": cpu_baseline_finetune(), "loss": None if loss is None else round(loss, 4),
+            "cpu_baseline": cpu_baseline_finetune() if world == 1 else None, "loss": None if loss is None else round(loss, 4),
         }
         print(json.dumps(out), flush=True)
     tr.close()

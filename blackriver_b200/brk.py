@@ -45,6 +45,8 @@ SIGNATURES = {
     "brk_cast": (i32, [p, i32, p, i32, i64, p]),
     "brk_transpose_0213": (i32, [p, p, i64, i64, i64, i64, i32, p]),
     "brk_colsum": (i32, [p, p, i64, i64, i32, i32, p]),
+    "brk_colsum_workspace_bytes": (sz, [i64, i64]),
+    "brk_colsum_ws": (i32, [p, p, i64, i64, i32, i32, p, sz, p]),
     "brk_softmax_fwd": (i32, [p, p, i64, i64, i32, p]),
     "brk_softmax_bwd": (i32, [p, p, p, i64, i64, i32, p]),
     "brk_embedding_gather": (i32, [p, p, p, i64, i64, i64, i32, p]),
@@ -58,6 +60,7 @@ SIGNATURES = {
     "brk_gemm_f16_supported": (i32, [i64, i64, i64, i32, i32, i64, i64, p, p]),
     "brk_gemm_f16": (i32, [p, p, p, i64, i64, i64, i32, i32, i64, i64, i64, p, p, i64, p, i64, i32, p]),
     "brk_gemm_f16_status": (i32, []),
+    "brk_gemm_f16_set_mode": (None, [i32]),
     "brk_flash_attn_fwd": (i32, [p, p, p, i64, p, i64, p, p, p, i32, i32, i32, i32, p]),
     "brk_flash_attn_bwd_workspace_bytes": (sz, [i32, i32, i32]),
     "brk_flash_attn_bwd": (i32, [p, p, p, i64, p, p, i64, p, p, p, p, i64, p, p, i32, i32, i32, i32, p, sz, p]),

@@ -423,7 +423,7 @@ ComputingReturn CUDATensor<DT>::op_linear_backward(tensor_t self, tensor_t x, te
     constexpr int dt = brk_dtype<DT>();
     const int acc = ComputingContext::grad_accumulate;
     int st;
-    { ProfScope prof("colsum"); st = brk_colsum(mem_, bias_g->data(), n, out, acc, dt, sptr()); }
+    { ProfScope prof("colsum"); st = brk_colsum_ws(mem_, bias_g->data(), n, out, acc, dt, ComputingContext::cuda_workspace, ComputingContext::workspace_size, sptr()); }
     if (st == BRK_OK) st = gemm_any<DT>(mem_, x->data(), weight_g->data(), out, in, n, 1, 0, out, in, in, acc ? 1.0f : 0.0f, nullptr);
     if (st == BRK_OK) st = gemm_any<DT>(mem_, weight->data(), x_g->data(), n, in, out, 0, 0, out, in, in, 0.0f, nullptr);
     return ret(st);

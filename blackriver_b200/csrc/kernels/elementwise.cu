@@ -166,6 +166,81 @@ colsum_kernel(const T* x, T* out, int64_t rows, int64_t cols, int accumulate) {
     }
 }
 
+// Two-stage form for large inputs: stage 1 CTAs own 64 columns x a slice of rows (128-bit loads,
+// 32 row lanes) and write fp32 partial sums [slices, cols] to scratch; stage 2 adds the slices in a
+// fixed order.  Deterministic, and enough CTAs in flight to stream at HBM speed.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const T* x, float* partial, int64_t rows, int64_t cols, int64_t rows_per_slice) {
+    constexpr int VN = Vec<T>::N;
+    constexpr int CV = 64 / VN;                 // 16-byte packets across the 64 columns of this CTA
+    constexpr int RL = 256 / CV;                // row lanes
+    __shared__ float red[RL][65];
+    const int cv = threadIdx.x % CV, rl = threadIdx.x / CV;
+    const int64_t c0 = (int64_t)blockIdx.x * 64 + cv * VN;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_slice;
+    const int64_t r1 = min(rows, r0 + rows_per_slice);
+    float acc[VN];
+#pragma unroll
+    for (int e = 0; e < VN; e++) acc[e] = 0.0f;
+    if (c0 < cols) {
+        int64_t r = r0 + rl;
+        for (; r + 3 * RL < r1; r += 4 * RL) {
+            Vec<T> v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u].load_stream(x + (r + u * RL) * cols + c0);
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int e = 0; e < VN; e++) acc[e] += v[u].v[e];
+        }
+        for (; r < r1; r += RL) {
+            Vec<T> v;
+            v.load_stream(x + r * cols + c0);
+#pragma unroll
+            for (int e = 0; e < VN; e++) acc[e] += v.v[e];
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < VN; e++) red[rl][cv * VN + e] = acc[e];
+    __syncthreads();
+    if (threadIdx.x < 64) {
+        float t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < RL; k++) t += red[k][threadIdx.x];
+        const int64_t c = (int64_t)blockIdx.x * 64 + threadIdx.x;
+        if (c < cols) partial[(int64_t)blockIdx.y * cols + c] = t;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_final_kernel(const float* partial, T* out, int slices, int64_t cols, int accumulate) {
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= cols) return;
+    float t = 0.0f;
+    for (int s = 0; s < slices; s++) t += partial[(int64_t)s * cols + j];
+    if (accumulate) t += to_f32(out[j]);
+    out[j] = from_f32<T>(t);
+}
+
+template <typename T>
+static int colsum_ws_dispatch(const void* x, void* out, int64_t rows, int64_t cols, int accumulate, void* ws, size_t ws_bytes,
+                              cudaStream_t st) {
+    int64_t col_ctas = (cols + 63) / 64;
+    int64_t slices = ((int64_t)sm_count() * 4 + col_ctas - 1) / col_ctas;
+    if (slices > rows / 32) slices = rows / 32 > 0 ? rows / 32 : 1;
+    if (slices > 64) slices = 64;
+    if ((size_t)(slices * cols) * sizeof(float) > ws_bytes) return BRK_ATTR_ERROR;
+    int64_t rps = (rows + slices - 1) / slices;
+    dim3 grid((unsigned)col_ctas, (unsigned)slices);
+    colsum_partial_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (float*)ws, rows, cols, rps);
+    int rc = launch_status("colsum_partial_kernel");
+    if (rc) return rc;
+    colsum_final_kernel<T><<<(unsigned)((cols + 255) / 256), 256, 0, st>>>((const float*)ws, (T*)out, (int)slices, cols, accumulate);
+    return launch_status("colsum_final_kernel");
+}
+
 // ------------------------------------------------------------------------------------------
 // row softmax forward / backward (one CTA per row; rows are attention score rows, T <= 2048)
 // ------------------------------------------------------------------------------------------
@@ -367,6 +442,26 @@ extern "C" int brk_colsum(const void* x, void* out, int64_t rows, int64_t cols, 
     else
         return BRK_ATTR_ERROR;
     return launch_status("colsum_kernel");
+}
+
+extern "C" size_t brk_colsum_workspace_bytes(int64_t rows, int64_t cols) {
+    (void)rows;
+    return cols > 0 ? (size_t)64 * (size_t)cols * sizeof(float) : 0;
+}
+
+extern "C" int brk_colsum_ws(const void* x, void* out, int64_t rows, int64_t cols, int accumulate, int dtype, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+    if (!x) return BRK_INPUT_ERROR;
+    if (!out) return BRK_OUTPUT_ERROR;
+    if (rows < 0 || cols < 0) return BRK_ATTR_ERROR;
+    if (cols == 0) return BRK_OK;
+    const int64_t vn = dtype == BRK_F16 ? 8 : 4;
+    const bool fast = workspace && rows >= 256 && cols % vn == 0 && aligned16(x) && aligned16(workspace) &&
+                      (dtype == BRK_F16 || dtype == BRK_F32);
+    if (!fast) return brk_colsum(x, out, rows, cols, accumulate, dtype, stream);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == BRK_F16) return colsum_ws_dispatch<__half>(x, out, rows, cols, accumulate, workspace, workspace_bytes, st);
+    return colsum_ws_dispatch<float>(x, out, rows, cols, accumulate, workspace, workspace_bytes, st);
 }
 
 extern "C" int brk_softmax_fwd(const void* x, void* y, int64_t rows, int64_t cols, int dtype, void* stream) {

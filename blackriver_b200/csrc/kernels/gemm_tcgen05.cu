@@ -46,6 +46,64 @@ __device__ __forceinline__ float tc_gelu(float x) {
     return x * 0.5f * (1.0f + t);
 }
 
+// Epilogue of one accumulator chunk: 32 consecutive columns of one output row held by this thread.
+__device__ __forceinline__ void tc_store_chunk(const TcParams& p, const uint32_t (&v)[32], int row, bool row_ok, int col0, bool vec_ok) {
+    if (!(row_ok && col0 < p.n)) return;
+    __half* crow = p.c + (int64_t)row * p.ldc + col0;
+    const __half* rrow = p.residual ? p.residual + (int64_t)row * p.ldr + col0 : nullptr;
+    __half* grow = p.gelu_out ? p.gelu_out + (int64_t)row * p.ldg + col0 : nullptr;
+    if (vec_ok && col0 + 32 <= p.n) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) f[e] = __uint_as_float(v[q * 8 + e]);
+            if (p.bias) {
+                Vec<__half> b;
+                b.load(p.bias + col0 + q * 8);
+#pragma unroll
+                for (int e = 0; e < 8; e++) f[e] += b.v[e];
+            }
+            if (rrow) {
+                Vec<__half> r;
+                r.load(rrow + q * 8);
+#pragma unroll
+                for (int e = 0; e < 8; e++) f[e] += r.v[e];
+            }
+            if (p.accumulate) {
+                Vec<__half> o;
+                o.load(crow + q * 8);
+#pragma unroll
+                for (int e = 0; e < 8; e++) f[e] += o.v[e];
+            }
+            Vec<__half> out;
+#pragma unroll
+            for (int e = 0; e < 8; e++) out.v[e] = f[e];
+            out.store(crow + q * 8);
+            if (grow) {
+#pragma unroll
+                for (int e = 0; e < 8; e++) out.v[e] = tc_gelu(f[e]);
+                out.store(grow + q * 8);
+            }
+        }
+    } else {
+        for (int e = 0; e < 32 && col0 + e < p.n; e++) {
+            float f = __uint_as_float(v[e]);
+            if (p.bias) f += __half2float(p.bias[col0 + e]);
+            if (rrow) f += __half2float(rrow[e]);
+            if (p.accumulate) f += __half2float(crow[e]);
+            crow[e] = __float2half_rn(f);
+            if (grow) grow[e] = __float2half_rn(tc_gelu(f));
+        }
+    }
+}
+
+__device__ __forceinline__ bool tc_vec_ok(const TcParams& p) {
+    return (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) &&
+           (!p.residual || ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0))) &&
+           (!p.gelu_out || ((p.ldg % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.gelu_out) & 15) == 0)));
+}
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, TcParams p) {
@@ -176,56 +234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, v);
                 tmem_ld_wait();
-                const int col0 = tn * BN + c0;
-                if (row_ok && col0 < p.n) {
-                    __half* crow = p.c + (int64_t)row * p.ldc + col0;
-                    const __half* rrow = p.residual ? p.residual + (int64_t)row * p.ldr + col0 : nullptr;
-                    __half* grow = p.gelu_out ? p.gelu_out + (int64_t)row * p.ldg + col0 : nullptr;
-                    if (vec_ok && col0 + 32 <= p.n) {
-#pragma unroll
-                        for (int q = 0; q < 4; q++) {
-                            float f[8];
-#pragma unroll
-                            for (int e = 0; e < 8; e++) f[e] = __uint_as_float(v[q * 8 + e]);
-                            if (p.bias) {
-                                Vec<__half> b;
-                                b.load(p.bias + col0 + q * 8);
-#pragma unroll
-                                for (int e = 0; e < 8; e++) f[e] += b.v[e];
-                            }
-                            if (rrow) {
-                                Vec<__half> r;
-                                r.load(rrow + q * 8);
-#pragma unroll
-                                for (int e = 0; e < 8; e++) f[e] += r.v[e];
-                            }
-                            if (p.accumulate) {
-                                Vec<__half> o;
-                                o.load(crow + q * 8);
-#pragma unroll
-                                for (int e = 0; e < 8; e++) f[e] += o.v[e];
-                            }
-                            Vec<__half> out;
-#pragma unroll
-                            for (int e = 0; e < 8; e++) out.v[e] = f[e];
-                            out.store(crow + q * 8);
-                            if (grow) {
-#pragma unroll
-                                for (int e = 0; e < 8; e++) out.v[e] = tc_gelu(f[e]);
-                                out.store(grow + q * 8);
-                            }
-                        }
-                    } else {
-                        for (int e = 0; e < 32 && col0 + e < p.n; e++) {
-                            float f = __uint_as_float(v[e]);
-                            if (p.bias) f += __half2float(p.bias[col0 + e]);
-                            if (rrow) f += __half2float(rrow[e]);
-                            if (p.accumulate) f += __half2float(crow[e]);
-                            crow[e] = __float2half_rn(f);
-                            if (grow) grow[e] = __float2half_rn(tc_gelu(f));
-                        }
-                    }
-                }
+                tc_store_chunk(p, v, row, row_ok, tn * BN + c0, vec_ok);
             }
             tcgen05_fence_before();
             __syncwarp();
@@ -239,6 +248,164 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs owns a 256 x 256 output tile.  Each CTA stages its own
+// 128 rows of A and its own 128 of the 256 B rows (so a stage is 32 KB and six stages fit), the
+// leader's single thread issues tcgen05.mma.cta_group::2 with M = 256, which reads both CTAs'
+// shared memory and writes 128 accumulator rows into each CTA's tensor memory.  Per FLOP the pair
+// moves two thirds of the operand bytes of the single-CTA kernel through L2 and shared memory.
+// Barrier protocol: every TMA load credits the LEADER's full barrier (the leader's producer posts
+// the expected byte count of both CTAs); tcgen05.commit multicasts stage-free and accumulator-ready
+// arrivals to both CTAs; both CTAs' epilogue warps release the accumulator on the leader's barrier.
+// ------------------------------------------------------------------------------------------
+constexpr int TC2_STAGES = 6;
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, TcParams p) {
+    constexpr int BN = 256;                              // pair tile: 256 (M) x 256 (N)
+    constexpr uint32_t A_BYTES = 128 * TC_BK * 2;        // this CTA's 128 rows of A
+    constexpr uint32_t B_BYTES = 128 * TC_BK * 2;        // this CTA's 128 of the 256 B rows
+    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = 512;                  // two accumulators of 256 columns
+    constexpr uint32_t IDESC = make_idesc_f16_f32(256, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + TC2_STAGES * STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + TC2_STAGES;
+    uint64_t* tmem_full = empty_bar + TC2_STAGES;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();             // 0 = leader
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int num_tiles = p.tiles_m * p.tiles_n;         // pair tiles
+    const int kblocks = (p.k + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC2_STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 8);                // four epilogue warps in each CTA of the pair
+        }
+        fence_barrier_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_base_smem, TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tcgen05_fence_before();
+    cluster_sync_all();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_base_smem;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
+                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                const int row_a = tm * 256 + (int)rank * 128;
+                const int row_b = tn * BN + (int)rank * 128;
+                for (int kb = 0; kb < kblocks && ok; kb++, it++) {
+                    const int s = it % TC2_STAGES;
+                    ok = mbar_wait(&empty_bar[s], ((it / TC2_STAGES) & 1) ^ 1);
+                    if (!ok) break;
+                    unsigned char* sa = tiles + s * STAGE_BYTES;
+                    unsigned char* sb = sa + A_BYTES;
+                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+                    if (!A_MN) {
+                        tma_load_2d_pair(sa, &tmap_a, &full_bar[s], kb * TC_BK, row_a);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; j++) tma_load_2d_pair(sa + j * 8192, &tmap_a, &full_bar[s], row_a + j * 64, kb * TC_BK);
+                    }
+                    if (!B_MN) {
+                        tma_load_2d_pair(sb, &tmap_b, &full_bar[s], kb * TC_BK, row_b);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; j++) tma_load_2d_pair(sb + j * 8192, &tmap_b, &full_bar[s], row_b + j * 64, kb * TC_BK);
+                    }
+                }
+            }
+            if (!ok) atomicExch(&g_tc_error, 4);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && rank == 0) {
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs, tcount++) {
+                const int buf = tcount & 1;
+                ok = mbar_wait(&tmem_empty[buf], ((tcount >> 1) & 1) ^ 1);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < kblocks && ok; kb++, it++) {
+                    const int s = it % TC2_STAGES;
+                    ok = mbar_wait(&full_bar[s], (it / TC2_STAGES) & 1);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t sa = smem_u32(tiles + s * STAGE_BYTES);
+                    const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < TC_BK / 16; kk++) {
+                        const uint64_t da = A_MN ? make_smem_desc_sw128(sa + kk * 2048, 8192, 1024)
+                                                 : make_smem_desc_sw128(sa + kk * 32, 16, 1024);
+                        const uint64_t db = B_MN ? make_smem_desc_sw128(sb + kk * 2048, 8192, 1024)
+                                                 : make_smem_desc_sw128(sb + kk * 32, 16, 1024);
+                        umma_f16_ss_pair(d_tmem, da, db, IDESC, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_pair(&empty_bar[s], 3);      // frees the stage in both CTAs
+                }
+                if (ok) umma_commit_pair(&tmem_full[buf], 3);
+            }
+            if (!ok) atomicExch(&g_tc_error, 5);
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+        const int quarter = warp & 3;
+        uint32_t tcount = 0;
+        bool ok = true;
+        const bool vec_ok = tc_vec_ok(p);
+        for (int tile = pair; tile < num_tiles && ok; tile += npairs, tcount++) {
+            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            const int buf = tcount & 1;
+            ok = mbar_wait(&tmem_full[buf], (tcount >> 1) & 1);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const int row = tm * 256 + (int)rank * 128 + quarter * 32 + lane;
+            const bool row_ok = row < p.m;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, v);
+                tmem_ld_wait();
+                tc_store_chunk(p, v, row, row_ok, tn * BN + c0, vec_ok);
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(&tmem_empty[buf]);
+        }
+        if (!ok && lane == 0) atomicExch(&g_tc_error, 6);
+    }
+
+    tcgen05_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
     }
 }
 
@@ -297,7 +464,54 @@ static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUt
     return launch_tc<BN, true, true>(ta, tb, p, st);
 }
 
+template <bool A_MN, bool B_MN>
+static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p, cudaStream_t st) {
+    constexpr size_t smem = 1024 + (size_t)TC2_STAGES * (2 * 128 * TC_BK * 2) + 256;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(gemm_tc_pair_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    });
+    if (attr_err != cudaSuccess) {
+        set_cuda_error(attr_err, "gemm_tc_pair smem attribute");
+        return BRK_CUDA_ERROR;
+    }
+    int tiles = p.tiles_m * p.tiles_n;
+    int pairs = sm_count() / 2;
+    if (tiles < pairs) pairs = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(pairs * 2));
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<A_MN, B_MN>, ta, tb, p);
+    if (e != cudaSuccess) {
+        set_cuda_error(e, "gemm_tc_pair_kernel launch");
+        return BRK_CUDA_ERROR;
+    }
+    return launch_status("gemm_tc_pair_kernel");
+}
+
+static int dispatch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p, cudaStream_t st) {
+    if (!a_mn && !b_mn) return launch_tc_pair<false, false>(ta, tb, p, st);
+    if (!a_mn && b_mn) return launch_tc_pair<false, true>(ta, tb, p, st);
+    if (a_mn && !b_mn) return launch_tc_pair<true, false>(ta, tb, p, st);
+    return launch_tc_pair<true, true>(ta, tb, p, st);
+}
+
+// 0 = choose by shape, 1 = always the single-CTA kernel, 2 = the CTA-pair kernel whenever it applies
+static int g_tc_mode = 0;
+
 }  // namespace brk
+
+extern "C" void brk_gemm_f16_set_mode(int mode) { brk::g_tc_mode = mode; }
 
 extern "C" int brk_gemm_f16_supported(int64_t m, int64_t n, int64_t k, int trans_a, int trans_b, int64_t lda, int64_t ldb,
                                       const void* a, const void* b) {
@@ -320,13 +534,15 @@ extern "C" int brk_gemm_f16(const void* a, const void* b, void* c, int64_t m, in
     if (!brk_gemm_f16_supported(m, n, k, trans_a, trans_b, lda, ldb, a, b)) return BRK_ATTR_ERROR;
     const bool a_mn = trans_a != 0;   // A stored [k, m]
     const bool b_mn = trans_b == 0;   // B stored [k, n]
+    const bool use_pair = g_tc_mode != 1 && m > 128 && n > 128;
     const int bn = n > 128 ? 256 : 128;
+    const uint32_t box_b_rows = use_pair ? 128u : (uint32_t)bn;
     CUtensorMap ta, tb;
     bool ok;
     if (!a_mn) ok = make_tmap_2d_f16(&ta, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda, TC_BK, TC_BM);
     else ok = make_tmap_2d_f16(&ta, a, (uint64_t)k, (uint64_t)m, (uint64_t)lda, 64, TC_BK);
     if (ok) {
-        if (!b_mn) ok = make_tmap_2d_f16(&tb, b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb, TC_BK, (uint32_t)bn);
+        if (!b_mn) ok = make_tmap_2d_f16(&tb, b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb, TC_BK, box_b_rows);
         else ok = make_tmap_2d_f16(&tb, b, (uint64_t)k, (uint64_t)n, (uint64_t)ldb, 64, TC_BK);
     }
     if (!ok) {
@@ -348,6 +564,10 @@ extern "C" int brk_gemm_f16(const void* a, const void* b, void* c, int64_t m, in
     p.tiles_m = (int)((m + TC_BM - 1) / TC_BM);
     p.tiles_n = (int)((n + bn - 1) / bn);
     cudaStream_t st = (cudaStream_t)stream;
+    if (use_pair) {
+        p.tiles_m = (int)((m + 255) / 256);
+        return dispatch_pair(a_mn, b_mn, ta, tb, p, st);
+    }
     if (bn == 256) return dispatch_major<256>(a_mn, b_mn, ta, tb, p, st);
     return dispatch_major<128>(a_mn, b_mn, ta, tb, p, st);
 }

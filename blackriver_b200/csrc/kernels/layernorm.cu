@@ -289,25 +289,27 @@ ln_bwd_kernel(const T* dy, const T* gamma, const T* beta,
     }
 }
 
-// out[j] = sum_p partial[p][j], j over 2*hidden (dgamma then dbeta), fixed order.
+// out[j] = sum_p partial[p][j], j over 2*hidden (dgamma then dbeta).  32 columns x 8 partial lanes per
+// CTA; each lane adds every 8th partial, the lanes are combined in a fixed order (deterministic).
 template <typename T>
 __global__ void __launch_bounds__(256)
 ln_bwd_reduce_kernel(const float* partial, T* dgamma, T* dbeta, int nparts, int hidden, int accumulate) {
-    int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= 2 * hidden) return;
-    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-    int p = 0;
-    for (; p + 3 < nparts; p += 4) {
-        s0 += partial[(size_t)p * 2 * hidden + j];
-        s1 += partial[(size_t)(p + 1) * 2 * hidden + j];
-        s2 += partial[(size_t)(p + 2) * 2 * hidden + j];
-        s3 += partial[(size_t)(p + 3) * 2 * hidden + j];
+    __shared__ float red[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int j = blockIdx.x * 32 + tx;
+    float s = 0.0f;
+    if (j < 2 * hidden)
+        for (int p = ty; p < nparts; p += 8) s += partial[(size_t)p * 2 * hidden + j];
+    red[ty][tx] = s;
+    __syncthreads();
+    if (ty == 0 && j < 2 * hidden) {
+        float t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) t += red[k][tx];
+        T* out = j < hidden ? dgamma + j : dbeta + (j - hidden);
+        if (accumulate) t += to_f32(*out);
+        *out = from_f32<T>(t);
     }
-    for (; p < nparts; p++) s0 += partial[(size_t)p * 2 * hidden + j];
-    float s = (s0 + s1) + (s2 + s3);
-    T* out = j < hidden ? dgamma + j : dbeta + (j - hidden);
-    if (accumulate) s += to_f32(*out);
-    *out = from_f32<T>(s);
 }
 
 // Generic path: one CTA per row for dx; column sums by a thread-per-column kernel.
@@ -396,7 +398,7 @@ static int ln_bwd_dispatch(const void* dy_, const void* gamma_, const void* beta
             ln_bwd_kernel<T, 4><<<grid, threads, 0, st>>>(dy, gamma, beta, var, y, dx, partial, rows, h, eps);
         int rc = launch_status("ln_bwd_kernel");
         if (rc) return rc;
-        ln_bwd_reduce_kernel<T><<<(2 * h + 255) / 256, 256, 0, st>>>(partial, dgamma, dbeta, grid, h, accumulate);
+        ln_bwd_reduce_kernel<T><<<(2 * h + 31) / 32, 256, 0, st>>>(partial, dgamma, dbeta, grid, h, accumulate);
         return launch_status("ln_bwd_reduce_kernel");
     }
     // column sums first: dx may alias dy or y

@@ -126,6 +126,11 @@ BRK_API int brk_transpose_0213(const void* x, void* y, int64_t a, int64_t b, int
 /* Column sums, out[j] = sum_i x[i,j] (overwrite or accumulate): the bias gradient that the
  * reference takes with cudnnReduceTensor (blackriver/cuda_tensor.cpp:738-761). */
 BRK_API int brk_colsum(const void* x, void* out, int64_t rows, int64_t cols, int accumulate, int dtype, void* stream);
+/* Same result through a two-stage reduction that streams at HBM speed; `workspace` holds fp32 partial
+ * sums (brk_colsum_workspace_bytes).  Falls back to brk_colsum for small or unaligned inputs. */
+BRK_API size_t brk_colsum_workspace_bytes(int64_t rows, int64_t cols);
+BRK_API int brk_colsum_ws(const void* x, void* out, int64_t rows, int64_t cols, int accumulate, int dtype, void* workspace,
+                  size_t workspace_bytes, void* stream);
 /* Row softmax and its backward on [rows,cols]: CUDATensor::op_softmax / op_softmax_backward
  * (blackriver/cuda_tensor.cpp:333-356, 891-918).  In-place allowed. */
 BRK_API int brk_softmax_fwd(const void* x, void* y, int64_t rows, int64_t cols, int dtype, void* stream);
@@ -180,6 +185,9 @@ BRK_API int brk_gemm_f16(const void* a, const void* b, void* c, int64_t m, int64
                  int64_t lda, int64_t ldb, int64_t ldc, const void* bias, const void* residual, int64_t ldr,
                  void* gelu_out, int64_t ldg, int accumulate, void* stream);
 BRK_API int brk_gemm_f16_status(void);
+/* Kernel selection for measurements: 0 = by shape (default), 1 = single-CTA tiles only, 2 = CTA-pair
+ * (cta_group::2, 256 x 256 tiles) whenever m, n > 128. */
+BRK_API void brk_gemm_f16_set_mode(int mode);
 
 /* ---- fused attention (fp16, tcgen05) ------------------------------------------------------------
  * Replaces the op_qk -> op_add(alibi) -> op_add(xmask) -> op_softmax -> op_attn chain of layer_forward

@@ -309,3 +309,16 @@ def test_error_codes_on_device(ops):
     assert st == brk.ATTR_ERROR
     a = (brk.i64 * 4)(1, 1, 2, 8); b = (brk.i64 * 4)(1, 1, 3, 8)
     assert brk.raw("brk_add_bcast", x.data_ptr(), x.data_ptr(), x.data_ptr(), a, b, brk.F32, 0) == brk.INPUT_ERROR
+
+
+def test_colsum_two_stage(ops):
+    from blackriver_b200 import brk
+    rng = np.random.default_rng(21)
+    for dtype, tdt, tol in ((np.float32, brk.F32, TOL32), (np.float16, brk.F16, TOL16)):
+        for rows, cols in ((2048, 4096), (300, 72), (1000, 16384)):
+            x = rng.standard_normal((rows, cols)).astype(dtype)
+            dx = torch.from_numpy(x).cuda()
+            out = torch.from_numpy(np.full(cols, 2.0, dtype)).cuda()
+            ws = torch.empty(brk.lib().brk_colsum_workspace_bytes(rows, cols), dtype=torch.uint8, device="cuda")
+            brk.call("brk_colsum_ws", dx.data_ptr(), out.data_ptr(), rows, cols, 1, tdt, ws.data_ptr(), ws.numel(), ops.stream())
+            assert relerr(host(out), x.astype(np.float64).sum(0) + 2.0) <= tol

@@ -43,4 +43,7 @@ def test_two_stage_pipeline_matches_single_gpu(tmp_path):
     res = launch(2, "nccl", str(tmp_path / "out.json"), 29531)
     for a, b in zip(res["pipe_losses"], res["ref_losses"]):
         assert abs(a - b) <= 1e-3 * abs(b)
-    assert res["w_err"] <= 2e-3 and res["table_err"] <= 2e-3 and res["tables_agree"]
+    # two Adam steps of size lr = 1e-3: a weight whose tiny gradient rounds differently in fp16 may move the
+    # other way, so the bound is a few update steps relative to the largest weight
+    assert res["w_err"] <= 1e-2 and res["table_err"] <= 1e-2
+    assert res["tables_agree"]          # both holders of the tied table applied the same summed gradient
