@@ -35,8 +35,9 @@ def gelu_ref(x):
     return x * 0.5 * (1 + np.tanh(0.79788456 * x * (1 + 0.044715 * x * x)))
 
 
-def run(ops, m, n, k, ta, tb, seed, bias=False, res=False, acc=False, gelu=False):
+def run(ops, m, n, k, ta, tb, seed, bias=False, res=False, acc=False, gelu=False, mode=0):
     from blackriver_b200 import brk
+    brk.lib().brk_gemm_f16_set_mode(mode)      # 1 = single-CTA tiles, 2 = CTA-pair (cta_group::2) tiles
     rng = np.random.default_rng(seed)
     A = h16(rng.standard_normal((k, m) if ta else (m, k)))
     B = h16(rng.standard_normal((n, k) if tb else (k, n)))
@@ -48,6 +49,7 @@ def run(ops, m, n, k, ta, tb, seed, bias=False, res=False, acc=False, gelu=False
     ops.gemm_f16(dev(A), dev(B), C, m, n, k, ta, tb, A.shape[1], B.shape[1], n, bias=dev(bs), residual=dev(R), ldr=n,
                  gelu_out=G, ldg=n, accumulate=acc)
     torch.cuda.synchronize()
+    brk.lib().brk_gemm_f16_set_mode(0)
     assert brk.lib().brk_gemm_f16_status() == 0
     a = (A.T if ta else A).astype(np.float64); b = (B.T if tb else B).astype(np.float64)
     ref = a @ b
@@ -59,12 +61,14 @@ def run(ops, m, n, k, ta, tb, seed, bias=False, res=False, acc=False, gelu=False
         assert relerr(G.float().cpu().numpy(), gelu_ref(ref)) <= TOL16
 
 
+@pytest.mark.parametrize("mode", [1, 2])
 @pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 1), (1, 0)])
-@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 512, 128), (200, 328, 136), (130, 72, 40), (1, 8, 8), (384, 1000, 264)])
-def test_all_layouts_and_tails(ops, m, n, k, ta, tb):
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 512, 128), (200, 328, 136), (130, 72, 40), (1, 8, 8), (384, 1000, 264),
+                                   (520, 264, 72)])
+def test_all_layouts_and_tails(ops, m, n, k, ta, tb, mode):
     if (ta and m % 8) or (not tb and n % 8):
         pytest.skip("this storage order needs a leading dimension that is a multiple of 8")
-    run(ops, m, n, k, ta, tb, seed=m + n + k)
+    run(ops, m, n, k, ta, tb, seed=m + n + k, mode=mode)
 
 
 def test_epilogues(ops):
@@ -72,6 +76,7 @@ def test_epilogues(ops):
     run(ops, 256, 512, 128, 0, 1, 2, bias=True, res=True)
     run(ops, 256, 512, 128, 1, 0, 3, acc=True)
     run(ops, 200, 328, 136, 0, 1, 4, bias=True, res=True, acc=True, gelu=True)
+    run(ops, 200, 328, 136, 0, 1, 4, bias=True, res=True, acc=True, gelu=True, mode=1)
 
 
 def test_matches_oracle_linear_and_backward(ops):
