@@ -348,6 +348,10 @@ FT_WORKLOAD = ("BLOOM-7b1-architecture fine-tune step, random init: 30 layers, h
                "stages over the GPUs")
 
 
+# virtual stages per rank by GPU count (breadth-first interleaved schedule); 1 = plain all-forward-all-backward
+DEFAULT_INTERLEAVE = {1: 1, 2: 1, 4: 1, 8: 1}
+
+
 def load_tensor_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -393,8 +397,9 @@ def run_finetune(args):
     else:
         host.collective_boot_local(0, 1)
 
+    interleave = args.interleave if args.interleave > 0 else DEFAULT_INTERLEAVE.get(world, 1)
     tr = finetune.Trainer(cfg["hidden"], cfg["heads"], cfg["vocab"], cfg["n_layers"], cfg["batch"], cfg["tokens"], cfg["n_micro"],
-                          rank=rank, world=world, seed=cfg["seed"], logits_rows=cfg["batch"] * cfg["tokens"])
+                          rank=rank, world=world, seed=cfg["seed"], logits_rows=cfg["batch"] * cfg["tokens"], interleave=interleave)
     mbs = finetune.make_microbatches(cfg["n_micro"], cfg["batch"], cfg["tokens"], cfg["vocab"], cfg["min_len"], cfg["seed"])
     tokens_per_step = cfg["n_micro"] * cfg["batch"] * cfg["tokens"]
     valid_per_step = int(sum(int(m[2].sum()) for m in mbs))
@@ -462,7 +467,7 @@ def run_finetune(args):
         h2d = feeds * sum(m[0].nbytes + m[1].nbytes + m[2].nbytes for m in mbs)
         d2h = cfg["n_micro"] * 8
         peak_tf, peak_src = load_tensor_peak()
-        my_layers = tr.counts[0]
+        my_layers = tr.counts[0]          # rank 0 never holds the head when world > 1
         flops = cfg["n_micro"] * finetune.gemm_flops_per_microbatch(cfg["hidden"], cfg["vocab"], my_layers, cfg["batch"] * cfg["tokens"],
                                                                   with_head=(world == 1))
         gemm_ms = prof.get("gemm_f16", {}).get("ms", 0.0)
@@ -476,7 +481,9 @@ def run_finetune(args):
             "data": "synthetic",
             "config": {"workload": FT_WORKLOAD, "layers": cfg["n_layers"], "micro_batches": cfg["n_micro"],
                        "tokens_per_step": tokens_per_step, "valid_tokens_per_step": valid_per_step,
-                       "parallelism": "pp%d" % world, "stage_layers": tr.counts, "schedule": "all-forward-all-backward over micro-batch slots",
+                       "parallelism": "pp%d" % world, "stage_layers": tr.counts,
+                       "virtual_stages_per_rank": interleave, "stage_chunks": [[c["n_layers"] for c in ch] for ch in tr.plan],
+                       "schedule": "all-forward-all-backward over micro-batch slots, breadth-first over the chunks of a rank",
                        "l2": "inputs larger than L2: per step every kernel streams >= 14 GB of weights and activations between re-uses"},
             "clocks": clocks, "gpu_launches": launches * args.steps,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -726,6 +733,8 @@ def main():
     ap.add_argument("--workload", default="finetune", choices=["finetune", "ops"])
     ap.add_argument("--layers", type=int, default=0, help="fine-tune workload with fewer layers (development aid)")
     ap.add_argument("--micro", type=int, default=0, help="fine-tune workload with fewer micro-batches (development aid)")
+    ap.add_argument("--interleave", type=int, default=0,
+                    help="virtual pipeline stages per rank (breadth-first schedule); 0 = choose from the number of GPUs")
     ap.add_argument("--skip-ops", action="store_true", help="do not run the operator microbench before the fine-tune step")
     ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "attn"],
                     help="profiling aid: run a few launches of one kernel family on a small case and exit")

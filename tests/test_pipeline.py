@@ -11,10 +11,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "pipeline_worker.py")
 
 
-def launch(world, backend, out_path, port):
+def launch(world, backend, out_path, port, interleave=1, head_cost="0.5"):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), WORKER, backend, out_path]
-    env = dict(os.environ, OMP_NUM_THREADS="2")
+           "--master-port", str(port), WORKER, backend, out_path, str(interleave)]
+    env = dict(os.environ, OMP_NUM_THREADS="2", BR_TEST_HEAD_COST=head_cost)
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return json.load(open(out_path))
@@ -27,12 +27,27 @@ def test_stage_logic_on_cpu_ranks(tmp_path, world):
 
 
 def test_partition_balances_head():
-    from blackriver_b200.finetune import partition_layers
-    for world in (1, 2, 4, 8):
+    from blackriver_b200.finetune import partition_layers, plan_stages
+    assert partition_layers(30, 1) == [30]
+    assert partition_layers(30, 2) == [17, 13]
+    assert partition_layers(30, 4) == [9, 9, 8, 4]
+    assert partition_layers(30, 8) == [5, 5, 4, 4, 4, 4, 4, 0]      # the head alone fills the last stage
+    for world in (2, 4, 8):
         c = partition_layers(30, world)
-        assert sum(c) == 30 and len(c) == world and min(c) >= 1
-        if world > 1:
-            assert c[-1] + 4.9 <= max(c[:-1]) + 1.0 + 1e-9      # the head-carrying stage is not the bottleneck by more than a layer
+        assert sum(c) == 30 and max(max(c[:-1]), c[-1] + 4.9) <= (30 + 4.9) / world + 1.0
+    for world, v in ((2, 2), (4, 2), (8, 2), (8, 4), (4, 3)):
+        plan, partner = plan_stages(30, world, v)
+        flat = sorted((c["layer_offset"], c["n_layers"]) for ch in plan for c in ch)
+        assert sum(n for _, n in flat) == 30
+        pos = 0
+        for off, n in flat:              # chunks tile the layer range without gaps
+            assert off == pos
+            pos += n
+        assert sum(c["first"] for ch in plan for c in ch) == 1 and sum(c["last"] for ch in plan for c in ch) == 1
+        outs = [c["out"] for ch in plan for c in ch]
+        ins = [c["in"] for ch in plan for c in ch]
+        assert sum(o == ("wrap",) for o in outs) == sum(i == ("wrap",) for i in ins) == v - 1
+        assert partner == (world - 1 if plan[-1][0]["n_layers"] or len(plan[-1]) > 1 else world - 2)
 
 
 @pytest.mark.gpu
@@ -47,3 +62,30 @@ def test_two_stage_pipeline_matches_single_gpu(tmp_path):
     # other way, so the bound is a few update steps relative to the largest weight
     assert res["w_err"] <= 1e-2 and res["table_err"] <= 1e-2
     assert res["tables_agree"]          # both holders of the tied table applied the same summed gradient
+
+
+def check_against_single(res):
+    for a, b in zip(res["pipe_losses"], res["ref_losses"]):
+        assert abs(a - b) <= 1e-3 * abs(b)
+    assert res["w_err"] <= 1e-2 and res["table_err"] <= 1e-2 and res["tables_agree"]
+
+
+@pytest.mark.gpu
+def test_interleaved_two_rank_pipeline(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    res = launch(2, "nccl", str(tmp_path / "out.json"), 29541, interleave=2)
+    assert [len(p) for p in res["plan"]] == [2, 2]
+    check_against_single(res)
+
+
+@pytest.mark.gpu
+def test_interleaved_pipeline_with_head_only_last_rank(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 3:
+        pytest.skip("needs three GPUs")
+    # a head as expensive as the whole layer share of a rank: the last rank keeps the head only
+    res = launch(3, "nccl", str(tmp_path / "out.json"), 29551, interleave=2, head_cost="2.5")
+    assert res["plan"][-1] == [0] and [len(p) for p in res["plan"]] == [2, 2, 1]
+    check_against_single(res)
