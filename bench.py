@@ -328,7 +328,7 @@ def run_ops(args, emit=True):
             "roofline": roofline, "kernels": kern, "cpu_baseline": cpu, "loss": round(loss_val, 5),
         }
         if emit:
-            print(json.dumps(out), flush=True)
+            emit_line(out)
     if world > 1 and emit:
         dist.destroy_process_group()
     result = out if rank == 0 else None
@@ -346,10 +346,6 @@ FT_WORKLOAD = ("BLOOM-7b1-architecture fine-tune step, random init: 30 layers, h
                "tied, embedding LayerNorm, ALiBi; fp16 weights/activations, fp32 master weights + Adam; 16 micro-batches of "
                "batch 2 x seq 1024 (32768 tokens/step), right padding with lengths U[512,1024], seed 3; contiguous pipeline "
                "stages over the GPUs")
-
-
-# virtual stages per rank by GPU count (breadth-first interleaved schedule); 1 = plain all-forward-all-backward
-DEFAULT_INTERLEAVE = {1: 1, 2: 1, 4: 1, 8: 1}
 
 
 def load_tensor_peak():
@@ -397,9 +393,8 @@ def run_finetune(args):
     else:
         host.collective_boot_local(0, 1)
 
-    interleave = args.interleave if args.interleave > 0 else DEFAULT_INTERLEAVE.get(world, 1)
     tr = finetune.Trainer(cfg["hidden"], cfg["heads"], cfg["vocab"], cfg["n_layers"], cfg["batch"], cfg["tokens"], cfg["n_micro"],
-                          rank=rank, world=world, seed=cfg["seed"], logits_rows=cfg["batch"] * cfg["tokens"], interleave=interleave)
+                          rank=rank, world=world, seed=cfg["seed"], logits_rows=cfg["batch"] * cfg["tokens"])
     mbs = finetune.make_microbatches(cfg["n_micro"], cfg["batch"], cfg["tokens"], cfg["vocab"], cfg["min_len"], cfg["seed"])
     tokens_per_step = cfg["n_micro"] * cfg["batch"] * cfg["tokens"]
     valid_per_step = int(sum(int(m[2].sum()) for m in mbs))
@@ -467,7 +462,7 @@ def run_finetune(args):
         h2d = feeds * sum(m[0].nbytes + m[1].nbytes + m[2].nbytes for m in mbs)
         d2h = cfg["n_micro"] * 8
         peak_tf, peak_src = load_tensor_peak()
-        my_layers = tr.counts[0]          # rank 0 never holds the head when world > 1
+        my_layers = tr.counts[0]
         flops = cfg["n_micro"] * finetune.gemm_flops_per_microbatch(cfg["hidden"], cfg["vocab"], my_layers, cfg["batch"] * cfg["tokens"],
                                                                   with_head=(world == 1))
         gemm_ms = prof.get("gemm_f16", {}).get("ms", 0.0)
@@ -481,9 +476,7 @@ def run_finetune(args):
             "data": "synthetic",
             "config": {"workload": FT_WORKLOAD, "layers": cfg["n_layers"], "micro_batches": cfg["n_micro"],
                        "tokens_per_step": tokens_per_step, "valid_tokens_per_step": valid_per_step,
-                       "parallelism": "pp%d" % world, "stage_layers": tr.counts,
-                       "virtual_stages_per_rank": interleave, "stage_chunks": [[c["n_layers"] for c in ch] for ch in tr.plan],
-                       "schedule": "all-forward-all-backward over micro-batch slots, breadth-first over the chunks of a rank",
+                       "parallelism": "pp%d" % world, "stage_layers": tr.counts, "schedule": "all-forward-all-backward over micro-batch slots",
                        "l2": "inputs larger than L2: per step every kernel streams >= 14 GB of weights and activations between re-uses"},
             "clocks": clocks, "gpu_launches": launches * args.steps,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -498,7 +491,7 @@ def run_finetune(args):
                                                              "roofline": ops_line["roofline"]},
             "cpu_baseline": cpu_baseline_finetune() if world == 1 else None, "loss": None if loss is None else round(loss, 4),
         }
-        print(json.dumps(out), flush=True)
+        emit_line(out)
     tr.close()
     if world > 1:
         host.collective_shutdown()
@@ -618,7 +611,7 @@ def run_case(args):
         for _ in range(reps):
             ops.gelu_backward(dy, x, out=out)
     torch.cuda.synchronize()
-    print(json.dumps({"case": args.case, "rows": rows, "launch_groups": 2, "reps": reps}))
+    emit_line({"case": args.case, "rows": rows, "launch_groups": 2, "reps": reps})
 
 
 def load_traffic():
@@ -721,10 +714,30 @@ def run_reference(args):
         "cpu_baseline": {"value": round(value, 4), "unit": "tokens/s", "cores": orc.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": round(value, 4), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(out), flush=True)
+    emit_line(out)
+
+
+RESULT_OUT = None      # the process's original stdout; everything else written to fd 1 goes to stderr
+
+
+def emit_line(obj):
+    """The one JSON line of a run."""
+    out = RESULT_OUT or sys.stdout
+    out.write(json.dumps(obj) + "\n")
+    out.flush()
+
+
+def keep_stdout_clean():
+    """Libraries (NCCL's version banner, for one) print to fd 1; the run's stdout must carry the JSON
+    line only, so fd 1 is pointed at stderr and the result is written to a private copy of the old fd 1."""
+    global RESULT_OUT
+    sys.stdout.flush()
+    RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
 
 
 def main():
+    keep_stdout_clean()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
@@ -733,8 +746,6 @@ def main():
     ap.add_argument("--workload", default="finetune", choices=["finetune", "ops"])
     ap.add_argument("--layers", type=int, default=0, help="fine-tune workload with fewer layers (development aid)")
     ap.add_argument("--micro", type=int, default=0, help="fine-tune workload with fewer micro-batches (development aid)")
-    ap.add_argument("--interleave", type=int, default=0,
-                    help="virtual pipeline stages per rank (breadth-first schedule); 0 = choose from the number of GPUs")
     ap.add_argument("--skip-ops", action="store_true", help="do not run the operator microbench before the fine-tune step")
     ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "attn"],
                     help="profiling aid: run a few launches of one kernel family on a small case and exit")

@@ -54,7 +54,6 @@ int brh_collective_boot(int rank, int world, const char id_bytes[128]) {
         CollectiveContext::boot(rank, world, id);
     });
 }
-int brh_collective_boot_wrap(int partner) { return guarded([&] { CollectiveContext::boot_wrap(partner); }); }
 int brh_collective_shutdown(void) { return guarded([] { CollectiveContext::shutdown(); }); }
 
 int brh_memory_boot(size_t total_bytes, int pinned) { return guarded([&] { MemoryContext::boot(total_bytes, pinned != 0); }); }

@@ -142,10 +142,6 @@ int CollectiveContext::nccl_rank = 0;
 ncclComm_t CollectiveContext::nccl_comm = nullptr;
 ncclUniqueId CollectiveContext::nccl_id;
 bool CollectiveContext::has_comm = false;
-ncclComm_t CollectiveContext::wrap_comm[2] = {nullptr, nullptr};
-int CollectiveContext::wrap_peer = -1;
-cudaStream_t CollectiveContext::wrap_stream = nullptr;
-cudaEvent_t CollectiveContext::wrap_event = nullptr;
 static std::chrono::steady_clock::time_point g_boot_time = std::chrono::steady_clock::now();
 
 void CollectiveContext::boot_local(int rank, int world) {
@@ -196,39 +192,7 @@ void CollectiveContext::boot_from_file(int rank, int world, const std::string& p
     boot(rank, world, id);
 }
 
-void CollectiveContext::boot_wrap(int partner) {
-    br_assert(has_comm, "the wrap link needs the world communicator");
-    br_assert(partner > 0 && partner < nccl_world, "wrap partner out of range");
-    const bool member = nccl_rank == 0 || nccl_rank == partner;
-    for (int i = 0; i < 2; i++) {
-        ncclComm_t c = nullptr;
-        ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
-        cfg.minCTAs = 1;
-        cfg.maxCTAs = 2;        // a queued send may wait long for its receive: keep it off the compute SMs
-        BR_NCCL_CHECK(ncclCommSplit(nccl_comm, member ? 0 : NCCL_SPLIT_NOCOLOR, nccl_rank, &c, &cfg));
-        wrap_comm[i] = c;
-    }
-    if (member) {
-        wrap_peer = nccl_rank == 0 ? 1 : 0;      // ranks inside the pair are ordered by world rank
-        BR_CUDA_CHECK(cudaStreamCreateWithFlags(&wrap_stream, cudaStreamNonBlocking));
-        BR_CUDA_CHECK(cudaEventCreateWithFlags(&wrap_event, cudaEventDisableTiming));
-    }
-}
-
 void CollectiveContext::shutdown() {
-    for (int i = 0; i < 2; i++)
-        if (wrap_comm[i]) {
-            ncclCommDestroy(wrap_comm[i]);
-            wrap_comm[i] = nullptr;
-        }
-    if (wrap_stream) {
-        cudaStreamSynchronize(wrap_stream);
-        cudaStreamDestroy(wrap_stream);
-        cudaEventDestroy(wrap_event);
-        wrap_stream = nullptr;
-        wrap_event = nullptr;
-    }
-    wrap_peer = -1;
     if (has_comm) {
         ncclCommDestroy(nccl_comm);
         has_comm = false;

@@ -63,18 +63,6 @@ struct CollectiveContext {
     static ncclUniqueId nccl_id;
     static bool has_comm;
 
-    // "Wrap" link of an interleaved pipeline: the rank that ends a round of stages hands over to rank 0,
-    // which starts the next round much later, so these transfers are asynchronous (own stream) and use
-    // their own two-rank communicators: [0] activations (partner -> rank 0), [1] gradients (rank 0 ->
-    // partner).  wrap_peer is the other rank's index INSIDE the two-rank communicator, -1 if this rank
-    // is not on the link.
-    static ncclComm_t wrap_comm[2];
-    static int wrap_peer;
-    static cudaStream_t wrap_stream;
-    static cudaEvent_t wrap_event;
-    // collective over all ranks: creates the two wrap communicators between rank 0 and `partner`
-    static void boot_wrap(int partner);
-
     // Rank layout only (no communicator): what host-only tools and tests need.
     static void boot_local(int rank, int world);
     // Creates the communicator from a unique id produced by make_unique_id() on rank 0.

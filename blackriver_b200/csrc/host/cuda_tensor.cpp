@@ -660,25 +660,6 @@ ComputingReturn CUDATensor<DT>::op_adam(tensor_t self, tensor_t grad, tensor_t m
 }
 
 template <DataType DT>
-ComputingReturn CUDATensor<DT>::io_wrap_isend(tensor_t self, int dir) {
-    if (dir < 0 || dir > 1 || CollectiveContext::wrap_peer < 0 || !CollectiveContext::wrap_comm[dir]) return OP_ATTR_ERROR;
-    // the wrap stream picks the tensor up once the compute stream has written it; the caller keeps
-    // the tensor untouched until the matching receive has happened (per-micro-batch buffers)
-    BR_CUDA_CHECK(cudaEventRecord(CollectiveContext::wrap_event, stream()));
-    BR_CUDA_CHECK(cudaStreamWaitEvent(CollectiveContext::wrap_stream, CollectiveContext::wrap_event, 0));
-    BR_NCCL_CHECK(ncclSend(mem_, self->bytes(), ncclChar, CollectiveContext::wrap_peer, CollectiveContext::wrap_comm[dir],
-                           CollectiveContext::wrap_stream));
-    return OP_OK;
-}
-
-template <DataType DT>
-ComputingReturn CUDATensor<DT>::io_wrap_recv(tensor_t self, int dir) {
-    if (dir < 0 || dir > 1 || CollectiveContext::wrap_peer < 0 || !CollectiveContext::wrap_comm[dir]) return OP_ATTR_ERROR;
-    BR_NCCL_CHECK(ncclRecv(mem_, self->bytes(), ncclChar, CollectiveContext::wrap_peer, CollectiveContext::wrap_comm[dir], stream()));
-    return OP_OK;
-}
-
-template <DataType DT>
 ComputingReturn CUDATensor<DT>::io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) {
     if (!CollectiveContext::has_comm) return OP_ATTR_ERROR;
     if (!recv || !recv->is_cuda()) return OP_OUTPUT_ERROR;

@@ -55,8 +55,6 @@ struct CUDATensor : public TransformerComputing {
     ComputingReturn op_adam(tensor_t self, tensor_t grad, tensor_t master, tensor_t m, tensor_t v, float lr, float beta1, float beta2, float eps, int step, float grad_scale) override;
     ComputingReturn op_randn(tensor_t self, float mean, float std, uint64_t seed) override;
     ComputingReturn io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) override;
-    ComputingReturn io_wrap_isend(tensor_t self, int dir) override;
-    ComputingReturn io_wrap_recv(tensor_t self, int dir) override;
 
 private:
     void* mem_;

@@ -34,7 +34,6 @@ BR_WORD(Sync, {
     if (ComputingContext::booted) {
         BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::cuda_stream));
         BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::comm_stream));
-        if (CollectiveContext::wrap_stream) BR_CUDA_CHECK(cudaStreamSynchronize(CollectiveContext::wrap_stream));
     }
 })
 
@@ -246,17 +245,6 @@ BR_WORD(IoNcclSendRecv, {
     auto t = pop_tensors<2>(stack);
     t[0]->io_nccl_sendrecv(t[0], t[1], peer);
 })
-// ( t dir -- )  wrap link: dir 0 activations, 1 gradients
-BR_WORD(IoWrapISend, {
-    int dir = (int)stack.pop_number();
-    tensor_t t = stack.pop_tensor();
-    t->io_wrap_isend(t, dir);
-})
-BR_WORD(IoWrapRecv, {
-    int dir = (int)stack.pop_number();
-    tensor_t t = stack.pop_tensor();
-    t->io_wrap_recv(t, dir);
-})
 // ( flag -- )  1: weight / bias gradients are added to, 0: overwritten (the reference behaviour)
 BR_WORD(Accumulate, { ComputingContext::grad_accumulate = stack.pop_number() != 0.0 ? 1 : 0; })
 // ( value -- )  factor applied to the loss gradient
@@ -326,8 +314,6 @@ void load_nn_words(Enviroment& env) {
     env.insert_native_word("io.nccl.recv", IoNcclRecv::creator);
 
     env.insert_native_word("io.nccl.sendrecv", IoNcclSendRecv::creator);
-    env.insert_native_word("io.wrap.isend", IoWrapISend::creator);
-    env.insert_native_word("io.wrap.recv", IoWrapRecv::creator);
     env.insert_native_word("op.flash_attn", FlashAttn::creator);
     env.insert_native_word("op.flash_attn_backward", FlashAttnBackward::creator);
     env.insert_native_word("op.linear_residual", LinearResidual::creator);

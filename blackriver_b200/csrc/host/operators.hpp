@@ -100,11 +100,6 @@ struct TransformerComputing {
     // simultaneous exchange with one peer: send self, receive into `recv` (one NCCL group, so two ranks
     // that both call it towards each other cannot block one another)
     virtual ComputingReturn io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) { return OP_TODO_ERROR; }
-    // wrap link of an interleaved pipeline (see CollectiveContext): asynchronous send of self on the wrap
-    // stream once the compute stream has produced it; receive into self on the compute stream.
-    // dir 0 = activations, 1 = gradients.
-    virtual ComputingReturn io_wrap_isend(tensor_t self, int dir) { return OP_TODO_ERROR; }
-    virtual ComputingReturn io_wrap_recv(tensor_t self, int dir) { return OP_TODO_ERROR; }
     // self[i] ~ N(mean, std), seeded
     virtual ComputingReturn op_randn(tensor_t self, float mean, float std, uint64_t seed) { return OP_TODO_ERROR; }
 };

@@ -221,16 +221,6 @@ ComputingReturn TensorType::op_randn(tensor_t self, float mean, float std, uint6
     op_check(r, "randn");
 }
 
-ComputingReturn TensorType::io_wrap_isend(tensor_t self, int dir) {
-    SELF_CHECK();
-    auto r = impl_->io_wrap_isend(self, dir);
-    op_check(r, "wrap_isend");
-}
-ComputingReturn TensorType::io_wrap_recv(tensor_t self, int dir) {
-    SELF_CHECK();
-    auto r = impl_->io_wrap_recv(self, dir);
-    op_check(r, "wrap_recv");
-}
 ComputingReturn TensorType::io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) {
     SELF_CHECK();
     auto r = impl_->io_nccl_sendrecv(self, recv, peer);

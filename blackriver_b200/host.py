@@ -17,7 +17,6 @@ SIGNATURES = {
     "brh_collective_boot_local": (i32, [i32, i32]),
     "brh_collective_unique_id": (i32, [C.c_char * 128]),
     "brh_collective_boot": (i32, [i32, i32, C.c_char * 128]),
-    "brh_collective_boot_wrap": (i32, [i32]),
     "brh_collective_shutdown": (i32, []),
     "brh_memory_boot": (i32, [sz, i32]),
     "brh_memory_shutdown": (i32, []),
@@ -93,10 +92,6 @@ def collective_unique_id():
 def collective_boot(rank, world, id_bytes):
     buf = (C.c_char * 128)(*id_bytes)
     _check(lib().brh_collective_boot(rank, world, buf))
-
-
-def collective_boot_wrap(partner):
-    _check(lib().brh_collective_boot_wrap(partner))
 
 
 def collective_shutdown():

@@ -241,8 +241,7 @@ def layer_param_elements(hidden):
 
 
 def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps=1e-5, first_stage=True, last_stage=True,
-                logits_rows=None, init_std=0.02, seed=0, layer_offset=0, n_slots=1, prev_rank=None, next_rank=None,
-                in_wrap=False, out_wrap=False, hash_base=0, word_suffix=""):
+                logits_rows=None, init_std=0.02, seed=0, layer_offset=0, n_slots=1, prev_rank=None, next_rank=None):
     """Script text defining the whole stage.  After executing it:
          build_model            allocates everything (call once)
          init_model             seeded random initialisation (weights N(0, init_std), biases 0, LN 1/0)
@@ -253,14 +252,8 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
        Pipeline use: n_slots > 1 keeps that many micro-batches' saved activations at once; `slot_k`
        selects the set the next forward / backward works on, and stage_forward / stage_backward add the
        NCCL receive from / send to prev_rank and next_rank around model_forward / model_backward.
-       Interleaved pipelines put several such chunks on one rank: hash_base shifts the chunk's hash
-       tables, word_suffix is appended to every word it defines, in_wrap / out_wrap route the chunk's input /
-       output over the asynchronous wrap link (io.wrap.*) instead of a neighbour rank.  A chunk with
-       n_layers == 0 is allowed on the last stage (final LayerNorm + LM head only)."""
+       A last stage that is not also the first may have n_layers == 0 (final LayerNorm + LM head only)."""
     assert n_layers >= 1 or (last_stage and not first_stage)
-    assert not (in_wrap and first_stage) and not (out_wrap and last_stage)
-    if in_wrap or out_wrap:
-        assert n_slots > 1
     SLOTTED = ("xattn_in", "qkv", "attn_out", "xb", "x4a", "x4b", "lse", "input_ln_var", "post_ln_var")
 
     def slot_names(name):
@@ -386,14 +379,8 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w("    0 #")
     if n_layers >= 1:
         w(f'    {n_layers} # "xout" @ 0 # "stage_out" !  {n_layers} # "yout_g" @ 0 # "stage_out_g" !  1 # "xin_g" @ 0 # "stage_in_g" !  0 #')
-    else:
+    else:             # head-only stage: what arrives is what the final LayerNorm reads
         w('    "stage_in" @ "stage_out" !  "gA" @ "stage_out_g" !  "gA" @ "stage_in_g" !')
-    if out_wrap:      # the sent activations must survive until rank 0 receives them: one buffer per micro-batch
-        for k in range(n_slots):
-            w(f'    {BTH} "cuda" "DTYPE" @ op.create {n_layers} # "xout@{k}" ! 0 #')
-    if in_wrap:       # same for the gradients sent back over the wrap link
-        for k in range(n_slots):
-            w(f'    {BTH} "cuda" "DTYPE" @ op.create "gsend@{k}" !')
     w("%end")
 
     # ---- slot selection: which micro-batch's saved activations the layer words see ----
@@ -407,10 +394,6 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
                 w(f'    "emb_out" @ 1 # "xinput" ! 0 #')
             for i in range(1, n_layers + 1):
                 w(f"    {i} #  " + "  ".join(f'"{name}@{k}" @ "{name}" !' for name in SLOTTED))
-            if out_wrap:
-                w(f'    {n_layers} # "xout@{k}" @ "xout" !  "xout" @ 0 # "stage_out" !')
-            if in_wrap:
-                w(f'    0 # "gsend@{k}" @ "gsend" !')
         w("    0 #")
         w("%end")
 
@@ -477,25 +460,17 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
 
     # ---- pipeline hand-offs around the stage's forward / backward ----
     w("%def stage_forward")
-    if in_wrap:
-        w('    0 # "stage_in" @ 0 io.wrap.recv')
-    elif prev_rank is not None:
+    if prev_rank is not None:
         w(f'    0 # "stage_in" @ {prev_rank} io.nccl.recv')
     w("    model_forward")
-    if out_wrap:
-        w('    0 # "stage_out" @ 0 io.wrap.isend')
-    elif next_rank is not None:
+    if next_rank is not None:
         w(f'    0 # "stage_out" @ {next_rank} io.nccl.send')
     w("%end")
     w("%def stage_backward")
-    if out_wrap:
-        w('    0 # "stage_out_g" @ 1 io.wrap.recv')
-    elif next_rank is not None:
+    if next_rank is not None:
         w(f'    0 # "stage_out_g" @ {next_rank} io.nccl.recv')
     w("    model_backward")
-    if in_wrap:
-        w('    0 # "gsend" @ "stage_in_g" @ op.copy  "gsend" @ 1 io.wrap.isend')
-    elif prev_rank is not None:
+    if prev_rank is not None:
         w(f'    0 # "stage_in_g" @ {prev_rank} io.nccl.send')
     w("%end")
     # ( peer -- )  both holders of the tied embedding / LM-head table sum their gradients
@@ -506,14 +481,4 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w('    "peer_" !!')
     w("%end")
 
-    text = "\n".join(L) + "\n"
-    if hash_base or word_suffix:
-        import re
-        defined = set(re.findall(r"^%def (\w+)", text, flags=re.M))
-        if hash_base:
-            text = re.sub(r"(?<![\w.@\"])(\d+) #(?!#)", lambda m: f"{int(m.group(1)) + hash_base} #", text)
-        if word_suffix:
-            text = re.sub(r"(?<![\w.@\"$])([A-Za-z_]\w*)(?![\w.@\"])",
-                          lambda m: m.group(1) + word_suffix if m.group(1) in defined else m.group(1), text)
-        text = f"{hash_base} #\n" + text
-    return text
+    return "\n".join(L) + "\n"

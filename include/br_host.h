@@ -32,9 +32,6 @@ BRH_API void* brh_context_stream(void);
 BRH_API int brh_collective_boot_local(int rank, int world);
 BRH_API int brh_collective_unique_id(char out[128]);
 BRH_API int brh_collective_boot(int rank, int world, const char id[128]);
-/* Collective over all ranks: the asynchronous wrap link of an interleaved pipeline between rank 0 and
- * `partner` (see CollectiveContext::boot_wrap). */
-BRH_API int brh_collective_boot_wrap(int partner);
 BRH_API int brh_collective_shutdown(void);
 
 /* Host arena: blackriver/context.cpp:96-121 (MemoryContext). */

@@ -11,51 +11,38 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "pipeline_worker.py")
 
 
-def launch(world, backend, out_path, port, interleave=1, head_cost="0.5"):
+def launch(world, backend, out_path, port, head_cost=0.5):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), WORKER, backend, out_path, str(interleave)]
-    env = dict(os.environ, OMP_NUM_THREADS="2", BR_TEST_HEAD_COST=head_cost)
+           "--master-port", str(port), WORKER, backend, out_path]
+    env = dict(os.environ, OMP_NUM_THREADS="2", BR_TEST_HEAD_COST=str(head_cost))
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return json.load(open(out_path))
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_stage_logic_on_cpu_ranks(tmp_path, world):
-    res = launch(world, "gloo", str(tmp_path / "out.json"), 29510 + world)
+@pytest.mark.parametrize("world,head_cost", [(2, 0.5), (3, 0.5), (3, 2.5)])
+def test_stage_logic_on_cpu_ranks(tmp_path, world, head_cost):
+    res = launch(world, "gloo", str(tmp_path / "out.json"), 29510 + world + int(head_cost), head_cost)
     assert res["ok"] and sum(res["counts"]) == 4 and len(res["counts"]) == world
+    assert (res["counts"][-1] == 0) == (head_cost > 2)
 
 
 def test_partition_balances_head():
-    from blackriver_b200.finetune import partition_layers, plan_stages
-    assert partition_layers(30, 1) == [30]
-    assert partition_layers(30, 2) == [17, 13]
-    assert partition_layers(30, 4) == [9, 9, 8, 4]
-    assert partition_layers(30, 8) == [5, 5, 4, 4, 4, 4, 4, 0]      # the head alone fills the last stage
-    for world in (2, 4, 8):
+    from blackriver_b200.finetune import LM_HEAD_COST_IN_LAYERS, partition_layers
+    expect = {1: [30], 2: [18, 12], 4: [9, 9, 9, 3], 8: [5, 5, 4, 4, 4, 4, 4, 0]}
+    for world in (1, 2, 4, 8):
         c = partition_layers(30, world)
-        assert sum(c) == 30 and max(max(c[:-1]), c[-1] + 4.9) <= (30 + 4.9) / world + 1.0
-    for world, v in ((2, 2), (4, 2), (8, 2), (8, 4), (4, 3)):
-        plan, partner = plan_stages(30, world, v)
-        flat = sorted((c["layer_offset"], c["n_layers"]) for ch in plan for c in ch)
-        assert sum(n for _, n in flat) == 30
-        pos = 0
-        for off, n in flat:              # chunks tile the layer range without gaps
-            assert off == pos
-            pos += n
-        assert sum(c["first"] for ch in plan for c in ch) == 1 and sum(c["last"] for ch in plan for c in ch) == 1
-        outs = [c["out"] for ch in plan for c in ch]
-        ins = [c["in"] for ch in plan for c in ch]
-        assert sum(o == ("wrap",) for o in outs) == sum(i == ("wrap",) for i in ins) == v - 1
-        assert partner == (world - 1 if plan[-1][0]["n_layers"] or len(plan[-1]) > 1 else world - 2)
+        assert c == expect[world]
+        assert min(c[:-1] or [1]) >= 1 and c[-1] >= 0
+        if world > 1:      # no other contiguous split has a lighter heaviest stage
+            heaviest = max(max(c[:-1]), c[-1] + LM_HEAD_COST_IN_LAYERS)
+            for last in range(0, 30 - (world - 1) + 1):
+                rest = 30 - last
+                assert max(-(-rest // (world - 1)), last + LM_HEAD_COST_IN_LAYERS) >= heaviest - 1e-9
+    assert partition_layers(4, 3, 2.5) == [2, 2, 0]        # a head heavier than a stage's share stands alone
 
 
-@pytest.mark.gpu
-def test_two_stage_pipeline_matches_single_gpu(tmp_path):
-    import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    res = launch(2, "nccl", str(tmp_path / "out.json"), 29531)
+def check_against_single(res):
     for a, b in zip(res["pipe_losses"], res["ref_losses"]):
         assert abs(a - b) <= 1e-3 * abs(b)
     # two Adam steps of size lr = 1e-3: a weight whose tiny gradient rounds differently in fp16 may move the
@@ -64,28 +51,19 @@ def test_two_stage_pipeline_matches_single_gpu(tmp_path):
     assert res["tables_agree"]          # both holders of the tied table applied the same summed gradient
 
 
-def check_against_single(res):
-    for a, b in zip(res["pipe_losses"], res["ref_losses"]):
-        assert abs(a - b) <= 1e-3 * abs(b)
-    assert res["w_err"] <= 1e-2 and res["table_err"] <= 1e-2 and res["tables_agree"]
-
-
 @pytest.mark.gpu
-def test_interleaved_two_rank_pipeline(tmp_path):
+def test_two_stage_pipeline_matches_single_gpu(tmp_path):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    res = launch(2, "nccl", str(tmp_path / "out.json"), 29541, interleave=2)
-    assert [len(p) for p in res["plan"]] == [2, 2]
-    check_against_single(res)
+    check_against_single(launch(2, "nccl", str(tmp_path / "out.json"), 29531))
 
 
 @pytest.mark.gpu
-def test_interleaved_pipeline_with_head_only_last_rank(tmp_path):
+def test_pipeline_with_head_only_last_stage(tmp_path):
     import torch
     if torch.cuda.device_count() < 3:
         pytest.skip("needs three GPUs")
-    # a head as expensive as the whole layer share of a rank: the last rank keeps the head only
-    res = launch(3, "nccl", str(tmp_path / "out.json"), 29551, interleave=2, head_cost="2.5")
-    assert res["plan"][-1] == [0] and [len(p) for p in res["plan"]] == [2, 2, 1]
+    res = launch(3, "nccl", str(tmp_path / "out.json"), 29533, head_cost=2.5)
+    assert res["counts"] == [2, 2, 0]
     check_against_single(res)
