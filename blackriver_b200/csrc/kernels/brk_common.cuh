@@ -42,6 +42,9 @@ struct Vec<float> {
     __device__ __forceinline__ void unpack(const uint4& t) {
         v[0] = __uint_as_float(t.x); v[1] = __uint_as_float(t.y); v[2] = __uint_as_float(t.z); v[3] = __uint_as_float(t.w);
     }
+    __device__ __forceinline__ uint4 pack() const {
+        return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+    }
     __device__ __forceinline__ void load(const float* p) {
         float4 t = *reinterpret_cast<const float4*>(p);
         v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;

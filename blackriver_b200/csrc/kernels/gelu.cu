@@ -4,23 +4,50 @@
 
 namespace brk {
 
-// tanh(u) = 1 - 2/(1+exp(2u)), exp through ex2.approx and the division through rcp.approx:
-// absolute error ~1e-7, saturates correctly for |u| large (exp -> inf gives 1, exp -> 0 gives -1).
+// Two tanh flavours.  PRECISE: tanh(u) = 1 - 2/(1+exp(2u)), exp through ex2.approx and the division
+// through rcp.approx: absolute error ~1e-7, saturates correctly for |u| large (exp -> inf gives 1,
+// exp -> 0 gives -1); used for fp32 tensors.  Otherwise the hardware tanh.approx.f32 (one SFU
+// operation, relative error 2^-11, i.e. below half precision's own rounding); used for fp16 tensors,
+// where two SFU operations and the longer instruction sequence per element would cost as much time as
+// the memory traffic.
+template <bool PRECISE>
 __device__ __forceinline__ float fast_tanh(float u) {
-    float e = __expf(2.0f * u);
-    return 1.0f - __fdividef(2.0f, e + 1.0f);
+    if (PRECISE) {
+        float e = __expf(2.0f * u);
+        return 1.0f - __fdividef(2.0f, e + 1.0f);
+    } else {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+        return t;
+    }
 }
 
+template <bool PRECISE>
 __device__ __forceinline__ float gelu_f(float x) {
-    float t = fast_tanh(0.79788456f * x * (1.0f + 0.044715f * x * x));
-    return x * 0.5f * (1.0f + t);
+    const float x2 = x * x;
+    const float t = fast_tanh<PRECISE>(x * fmaf(0.79788456f * 0.044715f, x2, 0.79788456f));
+    const float hx = 0.5f * x;
+    return fmaf(hx, t, hx);
 }
 
+template <bool PRECISE>
 __device__ __forceinline__ float gelu_grad_f(float g, float x) {
-    float t = fast_tanh(0.79788456f * x * (1.0f + 0.044715f * x * x));
-    float ff = 0.5f * x * ((1.0f - t * t) * (0.79788456f + 0.1070322243f * x * x)) + 0.5f * (1.0f + t);
+    const float x2 = x * x;
+    const float t = fast_tanh<PRECISE>(x * fmaf(0.79788456f * 0.044715f, x2, 0.79788456f));
+    const float sech2 = fmaf(-t, t, 1.0f);
+    const float dpoly = fmaf(0.1070322243f, x2, 0.79788456f);
+    const float ff = fmaf(0.5f * x * sech2, dpoly, fmaf(0.5f, t, 0.5f));
     return ff * g;
 }
+
+template <typename T>
+struct GeluPrecise {
+    static constexpr bool value = true;
+};
+template <>
+struct GeluPrecise<__half> {
+    static constexpr bool value = false;
+};
 
 constexpr int GELU_UNROLL = 4;
 constexpr int GELU_THREADS = 256;
@@ -31,22 +58,26 @@ gelu_vec_kernel(const T* dy, const T* x, T* out, int64_t nvec) {
     constexpr int VN = Vec<T>::N;
     const int64_t stride = (int64_t)gridDim.x * GELU_THREADS;
     for (int64_t base = (int64_t)blockIdx.x * GELU_THREADS + threadIdx.x; base < nvec; base += stride * GELU_UNROLL) {
-        Vec<T> vx[GELU_UNROLL], vg[GELU_UNROLL];
+        // the packets stay packed (4 registers each) until their turn: more loads in flight per register
+        uint4 rx[GELU_UNROLL], rg[GELU_UNROLL];
 #pragma unroll
         for (int u = 0; u < GELU_UNROLL; u++) {
             int64_t i = base + u * stride;
             if (i < nvec) {
-                vx[u].load_stream(x + i * VN);
-                if (BWD) vg[u].load_stream(dy + i * VN);
+                rx[u] = ld_raw_stream(x + i * VN);
+                if (BWD) rg[u] = ld_raw_stream(dy + i * VN);
             }
         }
 #pragma unroll
         for (int u = 0; u < GELU_UNROLL; u++) {
             int64_t i = base + u * stride;
             if (i < nvec) {
-                Vec<T> o;
+                Vec<T> vx, vg, o;
+                vx.unpack(rx[u]);
+                if (BWD) vg.unpack(rg[u]);
 #pragma unroll
-                for (int e = 0; e < VN; e++) o.v[e] = BWD ? gelu_grad_f(vg[u].v[e], vx[u].v[e]) : gelu_f(vx[u].v[e]);
+                for (int e = 0; e < VN; e++)
+                    o.v[e] = BWD ? gelu_grad_f<GeluPrecise<T>::value>(vg.v[e], vx.v[e]) : gelu_f<GeluPrecise<T>::value>(vx.v[e]);
                 o.store_stream(out + i * VN);
             }
         }
@@ -58,7 +89,7 @@ __global__ void gelu_scalar_kernel(const T* dy, const T* x, T* out, int64_t begi
     int64_t i = begin + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         float xv = to_f32(x[i]);
-        out[i] = from_f32<T>(BWD ? gelu_grad_f(to_f32(dy[i]), xv) : gelu_f(xv));
+        out[i] = from_f32<T>(BWD ? gelu_grad_f<GeluPrecise<T>::value>(to_f32(dy[i]), xv) : gelu_f<GeluPrecise<T>::value>(xv));
     }
 }
 

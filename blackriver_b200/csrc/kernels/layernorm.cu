@@ -14,8 +14,12 @@
 #include <string>
 
 #include "brk_common.cuh"
+#include "layernorm_ring.cuh"
 
 namespace brk {
+
+// 0: shared-memory ring kernels where the row size allows them; 1: register-resident kernels only
+static int g_ln_mode = 0;
 
 // ------------------------------------------------------------------------------------------
 // forward
@@ -27,7 +31,7 @@ __global__ void __launch_bounds__(LN_FWD_WARPS * 32)
 ln_fwd_kernel(const T* x, const T* gamma, const T* beta, T* y,
               float* mean, float* var, int64_t rows, int hidden, float eps) {
     constexpr int VN = Vec<T>::N;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     T* s_gamma = reinterpret_cast<T*>(smem_raw);
     T* s_beta = s_gamma + hidden;
     const int nvec = hidden / VN;
@@ -152,6 +156,12 @@ static int ln_fwd_dispatch(const void* x_, const void* gamma_, const void* beta_
     if (fast) {
         int nv = (int)((hidden / VN + 31) / 32);
         int h = (int)hidden;
+        if (g_ln_mode == 0 && nv >= 4 && nv * VN <= 128 && lnr_fwd_stages((size_t)hidden * sizeof(T)) >= 4) {
+            if (nv <= 4) return launch_ln_fwd_ring<T, 4>(x, gamma, beta, y, mean, var, rows, h, eps, st);
+            if (nv <= 8) return launch_ln_fwd_ring<T, 8>(x, gamma, beta, y, mean, var, rows, h, eps, st);
+            if (nv <= 16) return launch_ln_fwd_ring<T, 16>(x, gamma, beta, y, mean, var, rows, h, eps, st);
+            if (VN * 32 <= 128) return launch_ln_fwd_ring<T, (VN * 32 <= 128 ? 32 : 16)>(x, gamma, beta, y, mean, var, rows, h, eps, st);
+        }
         if (nv <= 1) return launch_ln_fwd<T, 1>(x, gamma, beta, y, mean, var, rows, h, eps, st);
         if (nv <= 2) return launch_ln_fwd<T, 2>(x, gamma, beta, y, mean, var, rows, h, eps, st);
         if (nv <= 4) return launch_ln_fwd<T, 4>(x, gamma, beta, y, mean, var, rows, h, eps, st);
@@ -385,11 +395,29 @@ static int ln_bwd_dispatch(const void* dy_, const void* gamma_, const void* beta
                 aligned16(gamma) && aligned16(beta) && aligned16(workspace);
     if (fast) {
         if (workspace == nullptr || workspace_bytes < brk_layernorm_bwd_workspace_bytes(rows, hidden)) return BRK_ATTR_ERROR;
+        float* partial = (float*)workspace;
+        int h = (int)hidden;
+        const size_t row_bytes = (size_t)hidden * sizeof(T);
+        // packets per thread: 1, 2 or 4 with at most 512 threads and 16 floats per per-column register array
+        int rnvt = nvec <= LNR_BWD_MAX_THREADS ? 1 : (nvec <= 2 * LNR_BWD_MAX_THREADS ? 2 : 4);
+        bool ring = nvec <= 4 * LNR_BWD_MAX_THREADS && rnvt * VN <= 16 &&
+                    (rnvt == 1 ? lnr_bwd_stages<T, 1>(row_bytes) : rnvt == 2 ? lnr_bwd_stages<T, 2>(row_bytes) : lnr_bwd_stages<T, 4>(row_bytes)) >= 2;
+        if (g_ln_mode == 0 && ring) {
+            int rgrid = 0;      // at most one CTA per SM: never more partial rows than the workspace was sized for
+            int rc;
+            if (rnvt == 1)
+                rc = launch_ln_bwd_ring<T, 1>(dy, gamma, beta, var, y, dx, partial, rows, h, eps, &rgrid, st);
+            else if (rnvt == 2)
+                rc = launch_ln_bwd_ring<T, 2>(dy, gamma, beta, var, y, dx, partial, rows, h, eps, &rgrid, st);
+            else
+                rc = launch_ln_bwd_ring<T, (Vec<T>::N == 4 ? 4 : 2)>(dy, gamma, beta, var, y, dx, partial, rows, h, eps, &rgrid, st);
+            if (rc) return rc;
+            ln_bwd_reduce_kernel<T><<<(2 * h + 31) / 32, 256, 0, st>>>(partial, dgamma, dbeta, rgrid, h, accumulate);
+            return launch_status("ln_bwd_reduce_kernel");
+        }
         int grid = ln_bwd_grid(rows);
         int nvt = nvec <= 512 ? 1 : (nvec <= 1024 ? 2 : 4);
         int threads = (int)(((nvec + nvt - 1) / nvt + 31) / 32 * 32);
-        float* partial = (float*)workspace;
-        int h = (int)hidden;
         if (nvt == 1)
             ln_bwd_kernel<T, 1><<<grid, threads, 0, st>>>(dy, gamma, beta, var, y, dx, partial, rows, h, eps);
         else if (nvt == 2)
@@ -424,9 +452,26 @@ extern "C" int brk_layernorm_fwd(const void* x, const void* gamma, const void* b
     return BRK_ATTR_ERROR;
 }
 
+extern "C" int brk_layernorm_set_mode(int mode) {
+    if (mode != 0 && mode != 1) return BRK_ATTR_ERROR;
+    brk::g_ln_mode = mode;
+    return BRK_OK;
+}
+
+// Synchronous: reads (and clears) the flag the ring kernels raise when a bounded wait gave up.
+// 0 = healthy; 1 / 2 = forward producer / consumer, 3 / 4 = backward producer / consumer timed out.
+extern "C" int brk_layernorm_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, brk::g_ln_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(brk::g_ln_error, &zero, sizeof(int));
+    return v;
+}
+
 extern "C" size_t brk_layernorm_bwd_workspace_bytes(int64_t rows, int64_t hidden) {
     if (rows <= 0 || hidden <= 0) return 0;
-    return (size_t)brk::ln_bwd_grid(rows) * 2 * (size_t)hidden * sizeof(float);
+    // one partial row (dgamma then dbeta, fp32) per CTA; no kernel variant launches more than min(rows, 2 x SMs) CTAs
+    const int64_t cap = (int64_t)brk::sm_count() * 2;
+    return (size_t)(rows < cap ? rows : cap) * 2 * (size_t)hidden * sizeof(float);
 }
 
 extern "C" int brk_layernorm_bwd(const void* dy, const void* gamma, const void* beta, const float* var, const void* y,

@@ -85,6 +85,42 @@ def test_layernorm_fwd_bwd_f16(ops, rows, hidden):
     assert relerr(host(db), db_ref) <= TOL16
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("rows,hidden,dtype", [(6001, 4096, "f16"), (300, 2056, "f16"), (2500, 1024, "f32"), (151, 4096, "f32"),
+                                                (297, 8192, "f16"), (1, 4096, "f16")])
+def test_layernorm_ring_and_register_kernels(ops, mode, rows, hidden, dtype):
+    """Rows of 2 KiB and more go through the shared-memory ring (mode 0) or the register-resident kernels
+    (mode 1); row counts that wrap the ring several times per CTA, odd counts, packet counts that are not
+    a multiple of the warp size, in-place outputs."""
+    from blackriver_b200 import brk
+    rng = np.random.default_rng(rows + hidden)
+    rnd = h16 if dtype == "f16" else (lambda a: np.asarray(a, np.float32))
+    td = torch.float16 if dtype == "f16" else torch.float32
+    tol = TOL16 if dtype == "f16" else TOL32
+    x = rnd(rng.standard_normal((rows, hidden)) * 1.3 + 0.2)
+    gamma = rnd(1.0 + 0.1 * rng.standard_normal(hidden))
+    beta = rnd(0.1 * rng.standard_normal(hidden))
+    dy = rnd(rng.standard_normal((rows, hidden)))
+    y_ref, mean_ref, var_ref = orc.layernorm(x, gamma, beta, 1e-5)
+    assert brk.raw("brk_layernorm_set_mode", mode) == 0
+    try:
+        xd = dev(x, td)
+        y, mean, var = ops.layernorm(xd, dev(gamma, td), dev(beta, td), 1e-5, out=xd)      # in place
+        assert relerr(host(y), y_ref) <= tol
+        assert relerr(host(mean), mean_ref) <= 1e-3 and relerr(host(var), var_ref) <= 1e-3
+        yin = host(y)
+        dg_ref, db_ref, dx_ref = orc.layernorm_backward(dy, gamma, beta, var_ref, yin, 1e-5)
+        dyd = dev(dy, td)
+        dg, db, dx = ops.layernorm_backward(dyd, dev(gamma, td), dev(beta, td), dev(var_ref), y, 1e-5, dx=dyd)      # dx over dy
+        assert relerr(host(dx), dx_ref) <= tol
+        # column sums over thousands of rows, rounded to the tensor's type at the end
+        assert relerr(host(dg), dg_ref) <= tol and relerr(host(db), db_ref) <= tol
+        torch.cuda.synchronize()
+        assert brk.raw("brk_layernorm_status") == 0
+    finally:
+        brk.raw("brk_layernorm_set_mode", 0)
+
+
 def test_layernorm_unaligned_views_and_inplace(ops):
     rng = np.random.default_rng(5)
     rows, hidden = 6, 256
