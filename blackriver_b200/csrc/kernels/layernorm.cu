@@ -18,7 +18,7 @@
 
 namespace brk {
 
-// 0: shared-memory ring kernels where the row size allows them; 1: register-resident kernels only
+// 0: kernels that prefetch the rows through shared memory where the row size allows them; 1: register-resident kernels only
 static int g_ln_mode = 0;
 
 // ------------------------------------------------------------------------------------------
@@ -156,7 +156,7 @@ static int ln_fwd_dispatch(const void* x_, const void* gamma_, const void* beta_
     if (fast) {
         int nv = (int)((hidden / VN + 31) / 32);
         int h = (int)hidden;
-        if (g_ln_mode == 0 && nv >= 4 && nv * VN <= 128 && lnr_fwd_stages((size_t)hidden * sizeof(T)) >= 4) {
+        if (g_ln_mode == 0 && nv >= 4 && nv * VN <= 128 && lnr_fwd_depth((size_t)hidden * sizeof(T)) > 0) {
             if (nv <= 4) return launch_ln_fwd_ring<T, 4>(x, gamma, beta, y, mean, var, rows, h, eps, st);
             if (nv <= 8) return launch_ln_fwd_ring<T, 8>(x, gamma, beta, y, mean, var, rows, h, eps, st);
             if (nv <= 16) return launch_ln_fwd_ring<T, 16>(x, gamma, beta, y, mean, var, rows, h, eps, st);
@@ -401,7 +401,7 @@ static int ln_bwd_dispatch(const void* dy_, const void* gamma_, const void* beta
         // packets per thread: 1, 2 or 4 with at most 512 threads and 16 floats per per-column register array
         int rnvt = nvec <= LNR_BWD_MAX_THREADS ? 1 : (nvec <= 2 * LNR_BWD_MAX_THREADS ? 2 : 4);
         bool ring = nvec <= 4 * LNR_BWD_MAX_THREADS && rnvt * VN <= 16 &&
-                    (rnvt == 1 ? lnr_bwd_stages<T, 1>(row_bytes) : rnvt == 2 ? lnr_bwd_stages<T, 2>(row_bytes) : lnr_bwd_stages<T, 4>(row_bytes)) >= 2;
+                    (rnvt == 1 ? lnr_bwd_depth<T, 1>(row_bytes) : rnvt == 2 ? lnr_bwd_depth<T, 2>(row_bytes) : lnr_bwd_depth<T, 4>(row_bytes)) > 0;
         if (g_ln_mode == 0 && ring) {
             int rgrid = 0;      // at most one CTA per SM: never more partial rows than the workspace was sized for
             int rc;
@@ -456,15 +456,6 @@ extern "C" int brk_layernorm_set_mode(int mode) {
     if (mode != 0 && mode != 1) return BRK_ATTR_ERROR;
     brk::g_ln_mode = mode;
     return BRK_OK;
-}
-
-// Synchronous: reads (and clears) the flag the ring kernels raise when a bounded wait gave up.
-// 0 = healthy; 1 / 2 = forward producer / consumer, 3 / 4 = backward producer / consumer timed out.
-extern "C" int brk_layernorm_status(void) {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, brk::g_ln_error, sizeof(int)) != cudaSuccess) return -1;
-    if (v != 0) cudaMemcpyToSymbol(brk::g_ln_error, &zero, sizeof(int));
-    return v;
 }
 
 extern "C" size_t brk_layernorm_bwd_workspace_bytes(int64_t rows, int64_t hidden) {

@@ -1,24 +1,34 @@
-// LayerNorm forward / backward with the rows staged through a shared-memory ring.
+// LayerNorm forward / backward with the rows prefetched through shared memory.
 //
-// One persistent CTA per SM.  One thread streams the CTA's rows into a ring of stages with
-// untiled bulk-asynchronous copies (cp.async.bulk, completion counted on an mbarrier per stage);
-// the consumer warps read the rows from shared memory, so the amount of data in flight per SM is
-// the size of the ring (100-200 KB) instead of what the consumers' registers can hold, and the
-// load latency is hidden behind the rows that are being worked on.  Results go straight from
-// registers to global memory with 128-bit stores.
+// One persistent CTA per SM.  Every thread copies the 16-byte packets it is going to work on
+// itself, several rows ahead, with asynchronous 16-byte copies (cp.async, the load/store-unit
+// path) into its own slots of a shared-memory ring, and picks them up with cp.async.wait_group.
+// The data in flight per SM is the size of the ring (130-200 KB) instead of what the registers
+// can hold, and since a thread only ever reads slots it filled itself the ring needs no barrier
+// of its own: nothing in these kernels waits on another thread except the block-wide row sums of
+// the backward pass.
 //
-// Stage protocol of the forward kernel (k = how many times the stage has been used before):
-//   producer: wait empty[s] for use k-1 (skipped for k = 0), arrive.expect_tx on full[s], copies
-//   consumer: wait full[s] with parity k & 1, move the data to registers, arrive on empty[s]
-// Every wait is bounded; a wait that gives up raises g_ln_error and the thread stops using the ring.
+// (An earlier version filled the ring with untiled bulk copies, cp.async.bulk + mbarrier.  With
+// all of a stage's bytes behind one bulk request per row it streamed at most ~17 GB/s per SM from
+// DRAM, 2.6 TB/s over the chip, however many stages were in flight; the per-thread 16-byte copies
+// keep many more requests outstanding.)
+//
+// Results go straight from registers to global memory with 128-bit streaming stores.
 #pragma once
 
 #include "brk_common.cuh"
-#include "brk_ptx.cuh"
 
 namespace brk {
 
-__device__ int g_ln_error = 0;
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {      // at most N of this thread's groups still pending
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 __device__ __forceinline__ float ln_guard_gamma(float g, float eps) { return g >= 0.0f ? g + eps : g - eps; }
 
@@ -56,88 +66,79 @@ __device__ __forceinline__ uint4 ln_affine_packet<__half>(const Vec<__half>& x, 
 }
 
 // ------------------------------------------------------------------------------------------
-// forward: a stage is one row; consumer warp w takes the CTA's rows w, w + 8, ...
+// forward: a team of WPR warps per row (each lane holds NV packets of it); every team owns DEPTH row
+// slots and keeps DEPTH rows in flight.  With WPR = 2 the two warps of a team exchange their partial
+// sums through shared memory around a 64-thread named barrier; twice the warps per SM at half the
+// registers each keep the instruction issue busier than one warp per row does.
 // ------------------------------------------------------------------------------------------
-constexpr int LNR_FWD_WARPS = 8;
-constexpr int LNR_FWD_THREADS = (LNR_FWD_WARPS + 1) * 32;
-constexpr int LNR_FWD_MAX_STAGES = 16;
+constexpr int LNR_FWD_TEAMS = 8;      // rows in work per CTA
 
-template <typename T, int NV>
-__global__ void __launch_bounds__(LNR_FWD_THREADS, 1)
+template <int WPR>
+__device__ __forceinline__ float lnr_team_sum(float v, float* xch, int team, int member, int lane, int slot) {
+    v = warp_sum(v);
+    if (WPR == 1) return v;
+    // xch[slot][team][member]; the slot alternates between the two sums of a row, so a value is never
+    // overwritten before the partner has read it (see the barrier order in the kernel)
+    float* mine = xch + (slot * LNR_FWD_TEAMS + team) * WPR;
+    if (lane == 0) mine[member] = v;
+    asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(32 * WPR) : "memory");
+    float t = 0.0f;
+#pragma unroll
+    for (int m = 0; m < WPR; m++) t += mine[m];      // same order in every member: identical totals
+    return t;
+}
+
+template <typename T, int NV, int DEPTH, int WPR>
+__global__ void __launch_bounds__(LNR_FWD_TEAMS * WPR * 32, 1)
 ln_fwd_ring_kernel(const T* x, const T* gamma, const T* beta, T* y, float* mean, float* var, int64_t rows, int hidden,
-                   float eps, int stages) {
+                   float eps) {
     constexpr int VN = Vec<T>::N;
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ float xch[2 * LNR_FWD_TEAMS * WPR];
     const int nvec = hidden / VN;
-    const uint32_t row_bytes = (uint32_t)nvec * 16u;
-    unsigned char* ring = smem_raw;
-    uint4* s_gamma = reinterpret_cast<uint4*>(ring + (size_t)stages * row_bytes);
-    uint4* s_beta = s_gamma + nvec;
-    uint64_t* full = reinterpret_cast<uint64_t*>(s_beta + nvec);
-    uint64_t* empty = full + stages;
+    const size_t row_bytes = (size_t)nvec * 16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int team = warp / WPR, member = warp % WPR;
+    uint4* s_gamma = reinterpret_cast<uint4*>(smem_raw);
+    uint4* s_beta = s_gamma + nvec;
+    unsigned char* my_ring = smem_raw + 2 * row_bytes + (size_t)team * DEPTH * row_bytes;      // this team's DEPTH row slots
 
-    // rows of this CTA: blockIdx.x + j * gridDim.x, j = 0 .. nj-1
-    const int64_t nj = rows > (int64_t)blockIdx.x ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const bool producer = warp == LNR_FWD_WARPS && lane == 0;
+    // rows of this team: first + n * step, n = 0 .. nrows-1 (rows interleaved over all teams of the grid)
+    const int64_t first = (int64_t)blockIdx.x * LNR_FWD_TEAMS + team;
+    const int64_t step = (int64_t)gridDim.x * LNR_FWD_TEAMS;
+    const int64_t nrows = rows > first ? (rows - first + step - 1) / step : 0;
+    // packets of this lane: (i * WPR + member) * 32 + lane, i = 0 .. NV-1
 
-    if (producer) {      // barriers, then the first fill of every stage, before anything else is waited for
-        for (int s = 0; s < stages; s++) {
-            ptx::mbar_init(&full[s], 1);
-            ptx::mbar_init(&empty[s], 1);
+    auto prefetch = [&](int64_t n, int slot) {      // one commit group per call, empty past the end
+        if (n < nrows) {
+            const uint4* src = reinterpret_cast<const uint4*>(x + (first + n * step) * hidden);
+            uint4* dst = reinterpret_cast<uint4*>(my_ring + (size_t)slot * row_bytes);
+#pragma unroll
+            for (int i = 0; i < NV; i++) {
+                const int idx = (i * WPR + member) * 32 + lane;
+                if (idx < nvec) cp_async_16(dst + idx, src + idx);
+            }
         }
-        ptx::fence_barrier_init();
-        for (int64_t j = 0; j < nj && j < stages; j++) {
-            ptx::mbar_arrive_expect_tx(&full[j], row_bytes);
-            ptx::bulk_load_1d(ring + (size_t)j * row_bytes, x + ((int64_t)blockIdx.x + j * gridDim.x) * hidden, row_bytes, &full[j]);
-        }
-    }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int d = 0; d < DEPTH; d++) prefetch(d, d);
+
     for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
         s_gamma[i] = reinterpret_cast<const uint4*>(gamma)[i];
         s_beta[i] = reinterpret_cast<const uint4*>(beta)[i];
     }
-    __syncthreads();      // barriers initialised, gamma and beta staged
-
-    if (warp == LNR_FWD_WARPS) {
-        if (lane == 0) {
-            int s = 0;            // stage of row j; k = how often it has been used before (j = k * stages + s)
-            uint32_t k = 1;
-            for (int64_t j = stages; j < nj; j++) {
-                if (!ptx::mbar_wait(&empty[s], (k - 1) & 1)) {
-                    atomicExch(&g_ln_error, 1);
-                    break;
-                }
-                const int64_t row = (int64_t)blockIdx.x + j * gridDim.x;
-                ptx::mbar_arrive_expect_tx(&full[s], row_bytes);
-                ptx::bulk_load_1d(ring + (size_t)s * row_bytes, x + row * hidden, row_bytes, &full[s]);
-                if (++s == stages) {
-                    s = 0;
-                    k++;
-                }
-            }
-        }
-        return;
-    }
+    __syncthreads();
 
     const float inv_h = 1.0f / (float)hidden;
-    int s = warp % stages;      // stage of row j and how often it has been used before, kept without 64-bit divisions
-    uint32_t k = (uint32_t)(warp / stages);
-    for (int64_t j = warp; j < nj; j += LNR_FWD_WARPS, s += LNR_FWD_WARPS) {
-        while (s >= stages) {
-            s -= stages;
-            k++;
-        }
-        bool ok = ptx::mbar_wait(&full[s], k & 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-            if (lane == 0) atomicExch(&g_ln_error, 2);
-            break;
-        }
-        const uint4* sp = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
+    int slot = 0;
+    for (int64_t n = 0; n < nrows; n++) {
+        cp_async_wait<DEPTH - 1>();      // row n has landed (each lane waits for, and then reads, its own packets)
+        const uint4* sp = reinterpret_cast<const uint4*>(my_ring + (size_t)slot * row_bytes);
         Vec<T> xv[NV];
 #pragma unroll
         for (int i = 0; i < NV; i++) {
-            const int idx = i * 32 + lane;
+            const int idx = (i * WPR + member) * 32 + lane;
             if (idx < nvec) {
                 xv[i].unpack(sp[idx]);
             } else {
@@ -145,10 +146,7 @@ ln_fwd_ring_kernel(const T* x, const T* gamma, const T* beta, T* y, float* mean,
                 for (int e = 0; e < VN; e++) xv[i].v[e] = 0.0f;
             }
         }
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&empty[s]);      // the row is in registers: the stage may be refilled
-
-        const int64_t row = (int64_t)blockIdx.x + j * gridDim.x;
+        const int64_t row = first + n * step;
         T* yr = y + row * hidden;
         // four partial sums each: the additions of one lane do not form a single dependent chain
         float sm[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -156,11 +154,14 @@ ln_fwd_ring_kernel(const T* x, const T* gamma, const T* beta, T* y, float* mean,
         for (int i = 0; i < NV; i++)
 #pragma unroll
             for (int e = 0; e < VN; e++) sm[e & 3] += xv[i].v[e];
-        const float mu = warp_sum((sm[0] + sm[1]) + (sm[2] + sm[3])) * inv_h;
+        const float mu = lnr_team_sum<WPR>((sm[0] + sm[1]) + (sm[2] + sm[3]), xch, team, member, lane, 0) * inv_h;
+        // every packet of the slot has been read and used by now: refill it with the row DEPTH ahead
+        prefetch(n + DEPTH, slot);
+        if (++slot == DEPTH) slot = 0;
         float qs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
         for (int i = 0; i < NV; i++) {
-            if (i * 32 + lane < nvec) {
+            if ((i * WPR + member) * 32 + lane < nvec) {
 #pragma unroll
                 for (int e = 0; e < VN; e++) {
                     const float d = xv[i].v[e] - mu;
@@ -168,59 +169,67 @@ ln_fwd_ring_kernel(const T* x, const T* gamma, const T* beta, T* y, float* mean,
                 }
             }
         }
-        const float v = warp_sum((qs[0] + qs[1]) + (qs[2] + qs[3])) * inv_h + eps;
+        const float v = lnr_team_sum<WPR>((qs[0] + qs[1]) + (qs[2] + qs[3]), xch, team, member, lane, 1) * inv_h + eps;
         const float rstd = rsqrtf(v);
         const float shift = -mu * rstd;      // xhat = x * rstd + shift
 #pragma unroll
         for (int i = 0; i < NV; i++) {
-            const int idx = i * 32 + lane;
+            const int idx = (i * WPR + member) * 32 + lane;
             if (idx < nvec) __stcs(reinterpret_cast<uint4*>(yr + idx * VN), ln_affine_packet<T>(xv[i], rstd, shift, s_gamma[idx], s_beta[idx]));
         }
-        if (lane == 0) {
+        if (lane == 0 && member == 0) {
             if (mean) mean[row] = mu;
             if (var) var[row] = v;
         }
     }
+    cp_async_wait<0>();
 }
 
-// Stages that fit next to gamma and beta; 0 = the ring does not fit this row size.
-static int lnr_fwd_stages(size_t row_bytes) {
-    const size_t budget = 200 * 1024;
-    if (row_bytes < 2048 || 2 * row_bytes + 4 * row_bytes > budget) return 0;
-    size_t s = (budget - 2 * row_bytes) / row_bytes;
-    return (int)(s > LNR_FWD_MAX_STAGES ? LNR_FWD_MAX_STAGES : s);
+// Row slots per team that fit next to gamma and beta: 3, 2 or 0 (= rows too large or too small for this kernel).
+static int lnr_fwd_depth(size_t row_bytes) {
+    const size_t budget = 208 * 1024;
+    if (row_bytes < 2048) return 0;
+    if ((2 + 3 * LNR_FWD_TEAMS) * row_bytes <= budget) return 3;
+    if ((2 + 2 * LNR_FWD_TEAMS) * row_bytes <= budget) return 2;
+    return 0;
 }
 
-template <typename T, int NV>
-static int launch_ln_fwd_ring(const T* x, const T* gamma, const T* beta, T* y, float* mean, float* var, int64_t rows,
-                              int hidden, float eps, cudaStream_t st) {
+template <typename T, int NV, int DEPTH, int WPR>
+static int launch_ln_fwd_ring_d(const T* x, const T* gamma, const T* beta, T* y, float* mean, float* var, int64_t rows,
+                                int hidden, float eps, cudaStream_t st) {
     const size_t row_bytes = (size_t)hidden * sizeof(T);
-    const int stages = lnr_fwd_stages(row_bytes);
-    const size_t smem = (size_t)(stages + 2) * row_bytes + 2 * (size_t)stages * sizeof(uint64_t);
+    const size_t smem = (2 + (size_t)DEPTH * LNR_FWD_TEAMS) * row_bytes;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(ln_fwd_ring_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
+        attr_err = cudaFuncSetAttribute(ln_fwd_ring_kernel<T, NV, DEPTH, WPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
     });
     if (attr_err != cudaSuccess) {
         set_cuda_error(attr_err, "ln_fwd_ring smem attribute");
         return BRK_CUDA_ERROR;
     }
+    const int64_t want = (rows + LNR_FWD_TEAMS - 1) / LNR_FWD_TEAMS;
     const int64_t cap = sm_count();
-    const int grid = (int)(rows < cap ? rows : cap);
-    ln_fwd_ring_kernel<T, NV><<<grid, LNR_FWD_THREADS, smem, st>>>(x, gamma, beta, y, mean, var, rows, hidden, eps, stages);
+    const int grid = (int)(want < cap ? want : cap);
+    ln_fwd_ring_kernel<T, NV, DEPTH, WPR><<<grid, LNR_FWD_TEAMS * WPR * 32, smem, st>>>(x, gamma, beta, y, mean, var, rows, hidden, eps);
     return launch_status("ln_fwd_ring_kernel");
 }
 
+// NV = 16-byte packets per lane with one warp per row; rows of 8 and more packets per lane are shared by two warps.
+template <typename T, int NV>
+static int launch_ln_fwd_ring(const T* x, const T* gamma, const T* beta, T* y, float* mean, float* var, int64_t rows,
+                              int hidden, float eps, cudaStream_t st) {
+    constexpr int WPR = NV >= 8 ? 2 : 1;
+    if (lnr_fwd_depth((size_t)hidden * sizeof(T)) == 3)
+        return launch_ln_fwd_ring_d<T, NV / WPR, 3, WPR>(x, gamma, beta, y, mean, var, rows, hidden, eps, st);
+    return launch_ln_fwd_ring_d<T, NV / WPR, 2, WPR>(x, gamma, beta, y, mean, var, rows, hidden, eps, st);
+}
+
 // ------------------------------------------------------------------------------------------
-// backward: a stage is R rows of (dy, y); every thread owns NVT 16-byte column groups.
-// All threads meet at one barrier per stage (the row sums are block-wide), and at that point every
-// thread has moved its part of the stage to registers, so thread 0 refills the stage right there:
-// no producer warp and no "empty" barriers are needed.
+// backward: every thread owns NVT 16-byte column groups of every row; a stage is R rows of (dy, y).
+// All threads meet at one barrier per stage for the block-wide row sums.
 // ------------------------------------------------------------------------------------------
-constexpr int LNR_BWD_MAX_THREADS = 512;
-constexpr int LNR_BWD_MAX_STAGES = 6;
-constexpr int LNR_BWD_CTAS_PER_SM = 1;      // (two CTAs of 256 threads with twice the columns per thread measured 30 % slower)
+constexpr int LNR_BWD_MAX_THREADS = 512;      // (two CTAs of 256 threads with twice the columns per thread measured 30 % slower)
 
 // Block-wide sums of Q values per thread in two steps around one barrier.
 // Step 1 (before the barrier): every warp reduces its Q values and stores them at rp[q * 32 + warp].
@@ -287,35 +296,20 @@ __device__ __forceinline__ void lnr_block_totals<4>(float (&v)[4], const float* 
 template <typename T, int NVT>
 struct LnrBwdRows {      // rows per stage: two while a thread's columns fit 8 floats per array, else one
     static constexpr int R = (NVT * Vec<T>::N <= 8) ? 2 : 1;
-    static constexpr bool fits = NVT * Vec<T>::N <= 16;      // floats per per-column array in registers
 };
 
-template <typename T, int NVT>
-__device__ __forceinline__ void lnr_bwd_fill(unsigned char* stage, uint64_t* full, const T* dy, const T* y, int64_t r0,
-                                             int64_t rows, int hidden, uint32_t row_bytes) {
-    constexpr int R = LnrBwdRows<T, NVT>::R;
-    const int valid = (int)(rows - r0 < R ? rows - r0 : R);
-    ptx::fence_proxy_async();      // the stage's previous contents were read through the generic proxy
-    ptx::mbar_arrive_expect_tx(full, (uint32_t)valid * 2u * row_bytes);
-    for (int r = 0; r < valid; r++) {
-        ptx::bulk_load_1d(stage + (size_t)(2 * r) * row_bytes, dy + (r0 + r) * hidden, row_bytes, full);
-        ptx::bulk_load_1d(stage + (size_t)(2 * r + 1) * row_bytes, y + (r0 + r) * hidden, row_bytes, full);
-    }
-}
-
-template <typename T, int NVT>
-__global__ void __launch_bounds__(LNR_BWD_MAX_THREADS, LNR_BWD_CTAS_PER_SM)
+template <typename T, int NVT, int DEPTH>
+__global__ void __launch_bounds__(LNR_BWD_MAX_THREADS, 1)
 ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var, const T* y, T* dx, float* partial,
-                   int64_t rows, int hidden, float eps, int stages) {
+                   int64_t rows, int hidden, float eps) {
     constexpr int VN = Vec<T>::N;
     constexpr int R = LnrBwdRows<T, NVT>::R;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nvec = hidden / VN;
-    const uint32_t row_bytes = (uint32_t)nvec * 16u;
-    const size_t stage_bytes = (size_t)R * 2 * row_bytes;
+    const size_t row_bytes = (size_t)nvec * 16;
+    const size_t stage_bytes = (size_t)R * 2 * row_bytes;      // [R][dy, y][nvec packets]
     unsigned char* ring = smem_raw;
-    float* red = reinterpret_cast<float*>(ring + (size_t)stages * stage_bytes);      // [2][2R][32]
-    uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * 2 * R * 32);
+    float* red = reinterpret_cast<float*>(ring + (size_t)DEPTH * stage_bytes);      // [2][2R][32]
     const int nthreads = (int)blockDim.x;      // a multiple of 32
     const int nwarp = nthreads >> 5;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -324,22 +318,40 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
     const int64_t ngroups = (rows + R - 1) / R;
     const int64_t nj = ngroups > (int64_t)blockIdx.x ? (ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
-    if (tid == 0) {
-        for (int s = 0; s < stages; s++) ptx::mbar_init(&full[s], 1);
-        ptx::fence_barrier_init();
-        for (int64_t j = 0; j < nj && j < stages; j++)
-            lnr_bwd_fill<T, NVT>(ring + (size_t)j * stage_bytes, &full[j], dy, y, ((int64_t)blockIdx.x + j * gridDim.x) * R, rows,
-                                 hidden, row_bytes);
-    }
-    __syncthreads();      // the barriers are initialised before anybody waits on them
+    bool own[NVT];
+#pragma unroll
+    for (int i = 0; i < NVT; i++) own[i] = i * nthreads + tid < nvec;
+
+    auto prefetch = [&](int64_t j, int stage) {      // this thread's packets of group j; one commit group per call
+        if (j < nj) {
+            const int64_t r0 = ((int64_t)blockIdx.x + j * gridDim.x) * R;
+            uint4* dst = reinterpret_cast<uint4*>(ring + (size_t)stage * stage_bytes);
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                if (r0 + r < rows) {
+                    const uint4* sdy = reinterpret_cast<const uint4*>(dy + (r0 + r) * hidden);
+                    const uint4* sy = reinterpret_cast<const uint4*>(y + (r0 + r) * hidden);
+#pragma unroll
+                    for (int i = 0; i < NVT; i++) {
+                        const int idx = i * nthreads + tid;
+                        if (own[i]) {
+                            cp_async_16(dst + (size_t)(2 * r) * nvec + idx, sdy + idx);
+                            cp_async_16(dst + (size_t)(2 * r + 1) * nvec + idx, sy + idx);
+                        }
+                    }
+                }
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int d = 0; d < DEPTH; d++) prefetch(d, d);
 
     const float inv_h = 1.0f / (float)hidden;
     float gam[NVT][VN], cofs[NVT][VN], ginv[NVT][VN], acc_g[NVT][VN], acc_b[NVT][VN];
-    bool own[NVT];
 #pragma unroll
     for (int i = 0; i < NVT; i++) {
         const int idx = i * nthreads + tid;
-        own[i] = idx < nvec;
         Vec<T> g, b;
         if (own[i]) {
             g.load(gamma + idx * VN);
@@ -368,29 +380,19 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
     load_var(0, var0);
     load_var(1, var1);
 
-    int phase = 0;
-    bool dead = false;      // a wait gave up: keep meeting the others at the barrier, without data
-    int s = 0;            // stage of group j; k = how often it has been used before
-    uint32_t k = 0;
+    int phase = 0, stage = 0;
     for (int64_t j = 0; j < nj; j++, phase ^= 1) {
         load_var(j + 2, var2);
-        if (!dead) {
-            bool ok = ptx::mbar_wait(&full[s], k & 1);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) {
-                dead = true;
-                if (lane == 0) atomicExch(&g_ln_error, 4);
-            }
-        }
+        cp_async_wait<DEPTH - 1>();      // group j has landed (this thread's own packets)
         const int64_t r0 = ((int64_t)blockIdx.x + j * gridDim.x) * R;
-        const uint4* sp = reinterpret_cast<const uint4*>(ring + (size_t)s * stage_bytes);
+        const uint4* sp = reinterpret_cast<const uint4*>(ring + (size_t)stage * stage_bytes);
         Vec<T> vdy[R][NVT], vy[R][NVT];
 #pragma unroll
         for (int r = 0; r < R; r++) {
 #pragma unroll
             for (int i = 0; i < NVT; i++) {
                 const int idx = i * nthreads + tid;
-                if (own[i] && r0 + r < rows && !dead) {
+                if (own[i] && r0 + r < rows) {
                     vdy[r][i].unpack(sp[(size_t)(2 * r) * nvec + idx]);
                     vy[r][i].unpack(sp[(size_t)(2 * r + 1) * nvec + idx]);
                 } else {
@@ -402,7 +404,6 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
                 }
             }
         }
-
         float sums[2 * R];
 #pragma unroll
         for (int r = 0; r < R; r++) {
@@ -421,18 +422,17 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
             sums[2 * r] = a;
             sums[2 * r + 1] = b;
         }
+        // this thread's packets of the stage have been read and used by now: refill them with the group DEPTH ahead
+        prefetch(j + DEPTH, stage);
+        if (++stage == DEPTH) stage = 0;
         float* rp = red + phase * (2 * R * 32);
         lnr_warp_reduce_store<2 * R>(sums, rp, lane, warp);
         __syncthreads();
-        // every thread has its part of stage s in registers: refill it with the group `stages` ahead
-        if (tid == 0 && j + stages < nj && !dead)
-            lnr_bwd_fill<T, NVT>(ring + (size_t)s * stage_bytes, &full[s], dy, y, ((int64_t)blockIdx.x + (j + stages) * gridDim.x) * R,
-                                 rows, hidden, row_bytes);
         lnr_block_totals<2 * R>(sums, rp, lane, nwarp);
 #pragma unroll
         for (int r = 0; r < R; r++) {
             const int64_t row = r0 + r;
-            if (row >= rows || dead) continue;
+            if (row >= rows) continue;
             const float mg = sums[2 * r] * inv_h, mgx = sums[2 * r + 1] * inv_h;
             const float rstd = rsqrtf(var0[r]);
 #pragma unroll
@@ -456,11 +456,8 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
             var0[r] = var1[r];
             var1[r] = var2[r];
         }
-        if (++s == stages) {
-            s = 0;
-            k++;
-        }
     }
+    cp_async_wait<0>();
 
     float* pg = partial + (size_t)blockIdx.x * 2 * hidden;
     float* pb = pg + hidden;
@@ -476,47 +473,56 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
     }
 }
 
+// Stages in flight: 6, 3 or 0 (= rows too large or too small for this kernel).
 template <typename T, int NVT>
-static int lnr_bwd_stages(size_t row_bytes) {
+static int lnr_bwd_depth(size_t row_bytes) {
     const size_t budget = 200 * 1024;
     const size_t stage = (size_t)LnrBwdRows<T, NVT>::R * 2 * row_bytes;
-    if (row_bytes < 2048 || 2 * stage > budget) return 0;
-    size_t s = budget / stage;
-    return (int)(s > LNR_BWD_MAX_STAGES ? LNR_BWD_MAX_STAGES : s);
+    if (row_bytes < 2048) return 0;
+    if (6 * stage <= budget) return 6;
+    if (3 * stage <= budget) return 3;
+    return 0;
 }
 
 template <typename T, int NVT>
 static int lnr_bwd_grid(int64_t rows) {
     constexpr int R = LnrBwdRows<T, NVT>::R;
     const int64_t groups = (rows + R - 1) / R;
-    const int64_t cap = (int64_t)sm_count() * LNR_BWD_CTAS_PER_SM;
+    const int64_t cap = sm_count();
     return (int)(groups < cap ? groups : cap);
+}
+
+template <typename T, int NVT, int DEPTH>
+static int launch_ln_bwd_ring_d(const T* dy, const T* gamma, const T* beta, const float* var, const T* y, T* dx, float* partial,
+                                int64_t rows, int hidden, float eps, int grid, cudaStream_t st) {
+    constexpr int VN = Vec<T>::N;
+    constexpr int R = LnrBwdRows<T, NVT>::R;
+    const int nvec = hidden / VN;
+    const size_t row_bytes = (size_t)hidden * sizeof(T);
+    const int threads = ((nvec + NVT - 1) / NVT + 31) / 32 * 32;
+    const size_t smem = (size_t)DEPTH * R * 2 * row_bytes + 2 * 2 * R * 32 * sizeof(float);
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(ln_bwd_ring_kernel<T, NVT, DEPTH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
+    });
+    if (attr_err != cudaSuccess) {
+        set_cuda_error(attr_err, "ln_bwd_ring smem attribute");
+        return BRK_CUDA_ERROR;
+    }
+    ln_bwd_ring_kernel<T, NVT, DEPTH><<<grid, threads, smem, st>>>(dy, gamma, beta, var, y, dx, partial, rows, hidden, eps);
+    return launch_status("ln_bwd_ring_kernel");
 }
 
 // Returns the number of CTAs (= partial rows written) through *grid_out.
 template <typename T, int NVT>
 static int launch_ln_bwd_ring(const T* dy, const T* gamma, const T* beta, const float* var, const T* y, T* dx, float* partial,
                               int64_t rows, int hidden, float eps, int* grid_out, cudaStream_t st) {
-    constexpr int VN = Vec<T>::N;
-    constexpr int R = LnrBwdRows<T, NVT>::R;
-    const int nvec = hidden / VN;
-    const size_t row_bytes = (size_t)hidden * sizeof(T);
-    const int stages = lnr_bwd_stages<T, NVT>(row_bytes);
-    const int threads = ((nvec + NVT - 1) / NVT + 31) / 32 * 32;
-    const size_t smem = (size_t)stages * R * 2 * row_bytes + 2 * 2 * R * 32 * sizeof(float) + (size_t)stages * sizeof(uint64_t);
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(ln_bwd_ring_kernel<T, NVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
-    });
-    if (attr_err != cudaSuccess) {
-        set_cuda_error(attr_err, "ln_bwd_ring smem attribute");
-        return BRK_CUDA_ERROR;
-    }
     const int grid = lnr_bwd_grid<T, NVT>(rows);
     *grid_out = grid;
-    ln_bwd_ring_kernel<T, NVT><<<grid, threads, smem, st>>>(dy, gamma, beta, var, y, dx, partial, rows, hidden, eps, stages);
-    return launch_status("ln_bwd_ring_kernel");
+    if (lnr_bwd_depth<T, NVT>((size_t)hidden * sizeof(T)) == 6)
+        return launch_ln_bwd_ring_d<T, NVT, 6>(dy, gamma, beta, var, y, dx, partial, rows, hidden, eps, grid, st);
+    return launch_ln_bwd_ring_d<T, NVT, 3>(dy, gamma, beta, var, y, dx, partial, rows, hidden, eps, grid, st);
 }
 
 }  // namespace brk

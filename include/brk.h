@@ -61,13 +61,10 @@ BRK_API int brk_layernorm_bwd(const void* dy, const void* gamma, const void* bet
                       void* dgamma, void* dbeta, void* dx, int64_t rows, int64_t hidden, float eps,
                       void* workspace, size_t workspace_bytes, int accumulate, int dtype, void* stream);
 
-/* Kernel selection and health of the LayerNorm kernels (no counterpart in the reference).
- * Rows of 2 KiB and more are streamed through a shared-memory ring filled by bulk-asynchronous copies
- * (mode 0, default); mode 1 keeps to the register-resident kernels, for measurements.  The ring
- * kernels bound every internal wait; brk_layernorm_status() (synchronous) returns non-zero if one
- * of them gave up since the last query. */
+/* Kernel selection of the LayerNorm kernels, for measurements (no counterpart in the reference).
+ * Mode 0 (default): rows of 2 KiB and more are prefetched through shared memory with asynchronous
+ * copies, several rows ahead; mode 1 keeps to the register-resident kernels. */
 BRK_API int brk_layernorm_set_mode(int mode);
-BRK_API int brk_layernorm_status(void);
 
 /* LayerNorm backward for callers that cannot hand over a workspace.  It has no counterpart in the
  * reference.  Same arguments and results as brk_layernorm_bwd, but the partial column sums go to
