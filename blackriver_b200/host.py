@@ -52,11 +52,29 @@ class HostError(RuntimeError):
     pass
 
 
+def _preload_bundled_nccl():
+    """One NCCL per process: libbr_host.so asks for the soname libnccl.so.2, and a torch imported later needs the
+    (newer) build bundled with it under that same soname.  Loading the bundled library first lets both use it;
+    without the bundle the system library is used."""
+    try:
+        import importlib.util
+        spec = importlib.util.find_spec("nvidia.nccl")
+        if spec and spec.submodule_search_locations:
+            for d in spec.submodule_search_locations:
+                cand = os.path.join(d, "lib", "libnccl.so.2")
+                if os.path.exists(cand):
+                    C.CDLL(cand, mode=C.RTLD_GLOBAL)
+                    return
+    except (ImportError, OSError, ValueError):
+        pass
+
+
 def lib():
     global _lib
     if _lib is None:
         if not os.path.exists(LIB_PATH):
             raise ImportError(f"{LIB_PATH} is missing: run __graft_entry__.build()")
+        _preload_bundled_nccl()
         # libbr_host.so finds libbrk.so through its $ORIGIN rpath
         _lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
         for name, (res, args) in SIGNATURES.items():
