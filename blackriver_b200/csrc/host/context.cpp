@@ -26,6 +26,10 @@ bool ComputingContext::booted = false;
 static bool g_owns_compute_stream = false;
 
 static void boot_common(int device, size_t workspace_bytes) {
+    // training switches start from their defaults on every boot (a previous user of the process may have set them)
+    ComputingContext::grad_accumulate = 0;
+    ComputingContext::loss_scale = 1.0f;
+    ComputingContext::verbose = 1;
     ComputingContext::cuda_device = device;
     BR_CUDA_CHECK(cudaStreamCreateWithFlags(&ComputingContext::comm_stream, cudaStreamNonBlocking));
     BR_CUDA_CHECK(cudaEventCreateWithFlags(&ComputingContext::compute_done, cudaEventDisableTiming));

@@ -118,6 +118,8 @@ class Trainer:
         self.env.run(self.p_sync)
 
     def close(self):
+        # the training switches live in the process-wide computing context: hand them back at their defaults
+        self.env.execute("0 op.accumulate 1 op.loss_scale 1 op.verbose")
         for p in self.p_fwd + self.p_bwd + [self.p_begin, self.p_sync]:
             self.env.free_program(p)
         self.env.close()
