@@ -390,6 +390,50 @@ LossReturn CUDATensor<DT>::op_loss_backward(tensor_t self, tensor_t ids_, tensor
     return loss;
 }
 
+// Forward-only scoring over the LM head (no counterpart in the reference, whose only inference hook is op_last_logits):
+// the same banded logits GEMM and target rule as op_loss_backward, row losses only.
+template <DataType DT>
+LossReturn CUDATensor<DT>::op_token_nll(tensor_t self, tensor_t ids_, tensor_t mask_, tensor_t lm_head, tensor_t all_logits, tensor_t out) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (self->shape().dim() != 3 || !dev_ok<DT>({lm_head, all_logits})) return OP_INPUT_ERROR;
+    if (!ids_ || !mask_ || ids_->dtype() != DataType::Int || mask_->dtype() != DataType::Int) return OP_INPUT_ERROR;
+    const int batch = (int)self->shape()[0], tokens = (int)self->shape()[1];
+    const int64_t hidden = self->shape()[2], vocab = lm_head->shape()[0];
+    const int64_t n = (int64_t)batch * tokens;
+    if (!dev_ok<DataType::Float>({out}) || (int64_t)out->items() != n) return OP_OUTPUT_ERROR;
+    if ((int64_t)ids_->items() < n || (int64_t)mask_->items() < n) return OP_INPUT_ERROR;
+    const int64_t band = std::min<int64_t>((int64_t)all_logits->items() / vocab, n);
+    if (band < 1) return OP_ATTR_ERROR;
+    constexpr int dt = brk_dtype<DT>();
+    const size_t es = DataType_size(DT);
+
+    Scratch sc;
+    int32_t* d_ids = (int32_t*)sc.take(n * 4);
+    int32_t* d_mask = (int32_t*)sc.take(n * 4);
+    int32_t* d_target = (int32_t*)sc.take(n * 4);
+    int32_t* d_count = (int32_t*)sc.take(4);
+    float* d_total = (float*)sc.take(4);
+    auto kind = [](tensor_t& t) { return t->is_cpu() ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice; };
+    BR_CUDA_CHECK(cudaMemcpyAsync(d_ids, ids_->data(), n * 4, kind(ids_), stream()));
+    BR_CUDA_CHECK(cudaMemcpyAsync(d_mask, mask_->data(), n * 4, kind(mask_), stream()));
+    int st = brk_loss_targets(d_ids, d_mask, d_target, d_count, batch, tokens, sptr());
+    float* row_loss = (float*)out->data();
+    for (int64_t r0 = 0; r0 < n && st == BRK_OK; r0 += band) {
+        const int64_t rows = std::min(band, n - r0);
+        const unsigned char* x = (const unsigned char*)mem_ + r0 * hidden * es;
+        st = gemm_any<DT>(x, lm_head->data(), all_logits->data(), rows, vocab, hidden, 0, 1, hidden, hidden, vocab, 0.0f, nullptr);
+        if (st == BRK_OK) st = brk_logsoftmax_nll_fwd(all_logits->data(), d_target + r0, row_loss + r0, nullptr, rows, vocab, dt, sptr());
+    }
+    if (st == BRK_OK) st = brk_sum_f32(row_loss, d_total, n, sptr());
+    if (st != BRK_OK) return ret(st);
+    int items = 0;
+    float total = 0.0f;
+    BR_CUDA_CHECK(cudaMemcpyAsync(&items, d_count, 4, cudaMemcpyDeviceToHost, stream()));
+    BR_CUDA_CHECK(cudaMemcpyAsync(&total, d_total, 4, cudaMemcpyDeviceToHost, stream()));
+    BR_CUDA_CHECK(cudaStreamSynchronize(stream()));
+    return items > 0 ? total / (float)items : 0.0f;
+}
+
 // ---- backward math -----------------------------------------------------------------------------------
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_layernorm_backward(tensor_t self, tensor_t scale, tensor_t bias, tensor_t var, tensor_t y,

@@ -54,6 +54,7 @@ struct CUDATensor : public TransformerComputing {
     ComputingReturn op_embed_backward(tensor_t self, tensor_t ids, tensor_t table_g) override;
     ComputingReturn op_adam(tensor_t self, tensor_t grad, tensor_t master, tensor_t m, tensor_t v, float lr, float beta1, float beta2, float eps, int step, float grad_scale) override;
     ComputingReturn op_randn(tensor_t self, float mean, float std, uint64_t seed) override;
+    LossReturn op_token_nll(tensor_t self, tensor_t ids, tensor_t mask, tensor_t lm_head, tensor_t all_logits, tensor_t out) override;
     ComputingReturn io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) override;
 
 private:

@@ -144,6 +144,13 @@ BR_WORD(LossBackward, {
     if (r.index() == 1) g_last_loss = std::get<1>(r);
 })
 
+// ( x ids mask lm_head workspace out -- )   forward-only scoring; the mean is kept for last_loss()
+BR_WORD(TokenNll, {
+    auto t = pop_tensors<6>(stack);
+    auto r = t[0]->op_token_nll(t[0], t[1], t[2], t[3], t[4], t[5]);
+    if (r.index() == 1) g_last_loss = std::get<1>(r);
+})
+
 // ( dy scale bias var y dscale dbias din eps -- )
 BR_WORD(LayernormBackward, {
     float eps = (float)stack.pop_number();
@@ -321,6 +328,7 @@ void load_nn_words(Enviroment& env) {
     env.insert_native_word("op.embed", Embed::creator);
     env.insert_native_word("op.embed_backward", EmbedBackward::creator);
     env.insert_native_word("op.adam", Adam::creator);
+    env.insert_native_word("op.token_nll", TokenNll::creator);
     env.insert_native_word("op.randn", Randn::creator);
     env.insert_native_word("op.accumulate", Accumulate::creator);
     env.insert_native_word("op.loss_scale", LossScale::creator);

@@ -102,6 +102,11 @@ struct TransformerComputing {
     virtual ComputingReturn io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) { return OP_TODO_ERROR; }
     // self[i] ~ N(mean, std), seeded
     virtual ComputingReturn op_randn(tensor_t self, float mean, float std, uint64_t seed) { return OP_TODO_ERROR; }
+    // forward-only scoring: out[b, t] (fp32) = NLL of ids[b, t+1] given position t of self [batch, tokens, hidden], 0 where the
+    // pair (t, t+1) is not counted (same target rule as op_loss_backward); returns the mean over the counted positions
+    virtual LossReturn op_token_nll(tensor_t self, tensor_t ids, tensor_t mask, tensor_t lm_head, tensor_t all_logits, tensor_t out) {
+        return OP_TODO_ERROR;
+    }
 };
 
 }  // namespace br

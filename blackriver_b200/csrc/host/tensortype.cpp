@@ -143,6 +143,15 @@ LossReturn TensorType::op_loss_backward(tensor_t self, tensor_t ids, tensor_t ma
     }
     return r;
 }
+LossReturn TensorType::op_token_nll(tensor_t self, tensor_t ids, tensor_t mask, tensor_t lm_head, tensor_t all_logits, tensor_t out) {
+    SELF_CHECK();
+    auto r = impl_->op_token_nll(self, ids, mask, lm_head, all_logits, out);
+    if (r.index() == 0) {
+        ComputingReturn code = std::get<0>(r);
+        if (code != OP_OK) br_panic("token_nll returned " + std::to_string((int)code));
+    }
+    return r;
+}
 ComputingReturn TensorType::op_layernorm_backward(tensor_t self, tensor_t scale, tensor_t bias, tensor_t var, tensor_t y, tensor_t dscale, tensor_t dbias, tensor_t din, float eps) {
     SELF_CHECK();
     auto r = impl_->op_layernorm_backward(self, scale, bias, var, y, dscale, dbias, din, eps);

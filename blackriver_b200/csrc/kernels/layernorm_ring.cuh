@@ -412,12 +412,17 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
             for (int i = 0; i < NVT; i++)
 #pragma unroll
                 for (int e = 0; e < VN; e++) {
-                    // vy becomes xhat; a row past the end has dy = 0 and adds nothing
+                    // vy becomes xhat and vdy becomes dy * gamma; a row past the end has dy = 0 and adds nothing.  The
+                    // column sums do not depend on the row sums, so they are taken here, before the barrier.
                     const float xhat = fmaf(vy[r][i].v[e], ginv[i][e], cofs[i][e]);
+                    const float d = vdy[r][i].v[e];
+                    const float g = d * gam[i][e];
                     vy[r][i].v[e] = xhat;
-                    const float g = vdy[r][i].v[e] * gam[i][e];
+                    vdy[r][i].v[e] = g;
                     a += g;
                     b = fmaf(g, xhat, b);
+                    acc_g[i][e] = fmaf(xhat, d, acc_g[i][e]);
+                    acc_b[i][e] += d;
                 }
             sums[2 * r] = a;
             sums[2 * r + 1] = b;
@@ -433,21 +438,16 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
         for (int r = 0; r < R; r++) {
             const int64_t row = r0 + r;
             if (row >= rows) continue;
-            const float mg = sums[2 * r] * inv_h, mgx = sums[2 * r + 1] * inv_h;
+            // dx = (g - mean(g) - xhat * mean(g * xhat)) * rstd = g * rstd + (xhat * c2 + c1)
             const float rstd = rsqrtf(var0[r]);
+            const float c1 = -sums[2 * r] * inv_h * rstd, c2 = -sums[2 * r + 1] * inv_h * rstd;
 #pragma unroll
             for (int i = 0; i < NVT; i++) {
                 if (!own[i]) continue;
                 const int idx = i * nthreads + tid;
                 Vec<T> o;
 #pragma unroll
-                for (int e = 0; e < VN; e++) {
-                    const float d = vdy[r][i].v[e];
-                    const float xhat = vy[r][i].v[e];
-                    o.v[e] = (d * gam[i][e] - mg - xhat * mgx) * rstd;
-                    acc_g[i][e] = fmaf(xhat, d, acc_g[i][e]);
-                    acc_b[i][e] += d;
-                }
+                for (int e = 0; e < VN; e++) o.v[e] = fmaf(vdy[r][i].v[e], rstd, fmaf(vy[r][i].v[e], c2, c1));
                 o.store_stream(dx + row * hidden + idx * VN);
             }
         }

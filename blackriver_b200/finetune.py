@@ -73,6 +73,7 @@ class Trainer:
         self.p_bwd = [e.build(f"slot_{k if self.n_slots > 1 else 0} stage_backward") for k in range(self.n_slots)]
         self.p_begin = e.build("zero_grads 1 op.accumulate")
         self.p_sync = e.build("op.sync")
+        self.p_score = None          # built on first use
         self.step_no = 0
         self.losses = []
 
@@ -114,13 +115,30 @@ class Trainer:
         e.execute(f"0 op.accumulate {self.lr} {self.step_no} {gs} optimizer_step")
         return float(np.mean(self.losses)) if self.losses else None
 
+    def score(self, microbatches):
+        """Forward only (prefill scoring): runs every micro-batch through the stages and, on the rank that holds the
+        head, returns a list of (token_nll [batch, tokens] float32, mean NLL) per micro-batch -- token_nll[b, t] is the
+        NLL of ids[b, t+1] at position t, 0 where that pair is not counted.  Other ranks return an empty list."""
+        e = self.env
+        if self.p_score is None:
+            self.p_score = [e.build(f"slot_{k} stage_score") for k in range(self.n_slots)]
+        out = []
+        for k, mb in enumerate(microbatches):
+            self._feed(mb)
+            e.run(self.p_score[k % self.n_slots])
+            if self.last:
+                e.change(0)
+                nll = e.read("token_nll").copy()        # synchronises the compute stream
+                out.append((nll, host.last_loss()))
+        return out
+
     def sync(self):
         self.env.run(self.p_sync)
 
     def close(self):
         # the training switches live in the process-wide computing context: hand them back at their defaults
         self.env.execute("0 op.accumulate 1 op.loss_scale 1 op.verbose")
-        for p in self.p_fwd + self.p_bwd + [self.p_begin, self.p_sync]:
+        for p in self.p_fwd + self.p_bwd + [self.p_begin, self.p_sync] + (self.p_score or []):
             self.env.free_program(p)
         self.env.close()
 

@@ -246,6 +246,8 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
          build_model            allocates everything (call once)
          init_model             seeded random initialisation (weights N(0, init_std), biases 0, LN 1/0)
          model_forward / model_backward / zero_grads / ( lr step grad_scale -- ) optimizer_step
+         model_score            after model_forward, on the last stage: per-token next-token NLL into "token_nll" (fp32
+                                [batch, tokens], 0 where no target is counted), forward only; stage_score = stage_forward + it
        Inputs are written to "ids_", "mask_", "lens_" (host int tensors) in hash 0; on a stage that is
        not the first the incoming activations go to "stage_in" and the outgoing gradient is
        "stage_in_g"; on a stage that is not the last "stage_out" / "stage_out_g" play the same roles.
@@ -357,6 +359,7 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         for nm in slot_names("xf"):
             w(f'    {BTH} "cuda" "DTYPE" @ op.create "{nm}" !')
         w(f'    {logits_rows} "VOCAB_SIZE" @ 2 "cuda" "DTYPE" @ op.create "all_logits" !')
+        w(f'    {batch} {tokens} 2 "cuda" "float" op.create "token_nll" !')
     for name, shape in main_params:
         dims = " ".join(str(d) for d in shape)
         for suffix, dt in (("", '"DTYPE" @'), ("_g", '"DTYPE" @'), (".master", '"float"'), (".m", '"float"'), (".v", '"float"')):
@@ -434,6 +437,13 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         w(f'    {g("stage_out", "ln_mean", "ln_f_var", "ln_f.weight", "ln_f.bias", "xf", "LN_EPS")} op.layernorm')
     w("%end")
 
+    # forward-only scoring (prefill): per-token NLL of the next token into "token_nll", mean kept for op.last_loss
+    w("%def model_score")
+    w("    0 #")
+    if last_stage:
+        w(f'    {g("xf", "ids_", "mask_", "word_embeddings.weight", "all_logits", "token_nll")} op.token_nll')
+    w("%end")
+
     w("%def model_backward")
     w("    0 #")
     if last_stage:
@@ -465,6 +475,9 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w("    model_forward")
     if next_rank is not None:
         w(f'    0 # "stage_out" @ {next_rank} io.nccl.send')
+    w("%end")
+    w("%def stage_score")
+    w("    stage_forward model_score")
     w("%end")
     w("%def stage_backward")
     if next_rank is not None:

@@ -121,6 +121,49 @@ def test_small_model_step(host):
         env.close()
 
 
+def test_prefill_token_nll(host):
+    """Forward-only scoring (the long-context prefill configuration at test size): per-token next-token NLL from the
+    words path against the fp32 oracle; full-length and padded sequences; the logits band is smaller than the batch."""
+    from blackriver_b200 import finetune
+    H, heads, V, L, B, T = 128, 2, 512, 2, 2, 160
+    rng = np.random.default_rng(4)
+    mbs = []
+    for lens in ([160, 160], [160, 71]):
+        ids = rng.integers(0, V, (B, T)).astype(np.int32)
+        mask = (np.arange(T)[None, :] < np.array(lens)[:, None]).astype(np.int32)
+        ids[mask == 0] = 3
+        mbs.append((ids, mask, np.array(lens, np.int32)))
+    tr = finetune.Trainer(H, heads, V, L, B, T, n_micro=2, rank=0, world=1, seed=11, init_std=0.05, logits_rows=100)
+    try:
+        env = tr.env
+        env.change(0)
+        main_names = ("word_embeddings.weight", "word_embeddings_layernorm.weight", "word_embeddings_layernorm.bias", "ln_f.weight", "ln_f.bias")
+        p_main = {k: env.read(k).astype(np.float32) for k in main_names}
+        layers = []
+        for i in range(1, L + 1):
+            env.change(i)
+            layers.append({k: env.read(k).astype(np.float32) for k in orc.LAYER_PARAMS})
+        env.change(0)
+        got = tr.score(mbs)
+        assert len(got) == 2
+        for (ids, mask, lens), (nll, mean) in zip(mbs, got):
+            x = orc.embedding_gather(p_main["word_embeddings.weight"], ids)
+            h, _, _ = orc.layernorm(x, p_main["word_embeddings_layernorm.weight"], p_main["word_embeddings_layernorm.bias"], 1e-5)
+            al = orc.alibi(heads, T); xm = orc.build_xmask(mask)
+            for p in layers:
+                h, _ = orc.layer_forward(h, p, al, xm, heads, 1e-5)
+            xf, _, _ = orc.layernorm(h, p_main["ln_f.weight"], p_main["ln_f.bias"], 1e-5)
+            tg, items = orc.loss_targets(ids, mask)
+            logits = xf.reshape(B * T, H) @ p_main["word_embeddings.weight"].T
+            total, row_loss, _ = orc.logsoftmax_nll(logits, tg.reshape(-1))
+            assert nll.shape == (B, T) and nll.dtype == np.float32
+            assert np.array_equal(nll == 0, (tg < 0))                     # exactly the uncounted positions are zero
+            assert relerr(nll, row_loss.reshape(B, T)) <= 2e-2
+            assert abs(mean - total / items) <= 1e-3 * abs(total / items)
+    finally:
+        tr.close()
+
+
 def test_adam_kernel_matches_oracle():
     from blackriver_b200 import brk, ops
     rng = np.random.default_rng(1)
