@@ -304,48 +304,56 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
                    int64_t rows, int hidden, float eps) {
     constexpr int VN = Vec<T>::N;
     constexpr int R = LnrBwdRows<T, NVT>::R;
+    constexpr int RED = (2 * R + 1) * 32;      // per phase: 2R row sums x 32 warps, then rstd of the R rows
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int nvec = hidden / VN;
     const size_t row_bytes = (size_t)nvec * 16;
     const size_t stage_bytes = (size_t)R * 2 * row_bytes;      // [R][dy, y][nvec packets]
     unsigned char* ring = smem_raw;
-    float* red = reinterpret_cast<float*>(ring + (size_t)DEPTH * stage_bytes);      // [2][2R][32]
+    float* red = reinterpret_cast<float*>(ring + (size_t)DEPTH * stage_bytes);      // [2][RED]
     const int nthreads = (int)blockDim.x;      // a multiple of 32
     const int nwarp = nthreads >> 5;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-    // row groups of this CTA: group blockIdx.x + j * gridDim.x holds rows group*R .. group*R + R-1
-    const int64_t ngroups = (rows + R - 1) / R;
-    const int64_t nj = ngroups > (int64_t)blockIdx.x ? (ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // Row groups of this CTA: group blockIdx.x + j * gridDim.x holds rows group*R .. group*R + R-1.  Everything that
+    // walks over the groups (first row, byte offsets) is advanced by a constant per step instead of recomputed.
+    const int64_t stride_rows = (int64_t)gridDim.x * R;
+    const size_t stride_bytes = (size_t)stride_rows * row_bytes;
+    const int64_t first_row = (int64_t)blockIdx.x * R;
 
     bool own[NVT];
+    uint32_t off[NVT];      // byte offset of this thread's packets inside a row
 #pragma unroll
-    for (int i = 0; i < NVT; i++) own[i] = i * nthreads + tid < nvec;
+    for (int i = 0; i < NVT; i++) {
+        own[i] = i * nthreads + tid < nvec;
+        off[i] = (uint32_t)(i * nthreads + tid) * 16u;
+    }
 
-    auto prefetch = [&](int64_t j, int stage) {      // this thread's packets of group j; one commit group per call
-        if (j < nj) {
-            const int64_t r0 = ((int64_t)blockIdx.x + j * gridDim.x) * R;
-            uint4* dst = reinterpret_cast<uint4*>(ring + (size_t)stage * stage_bytes);
+    // prefetch cursor: first row / source addresses of the next group to copy
+    int64_t pf_row = first_row;
+    const unsigned char* pf_dy = reinterpret_cast<const unsigned char*>(dy) + (size_t)first_row * row_bytes;
+    const unsigned char* pf_y = reinterpret_cast<const unsigned char*>(y) + (size_t)first_row * row_bytes;
+    auto prefetch = [&](int stage) {      // this thread's packets of the next group; one commit group per call, empty past the end
+        unsigned char* dst = ring + (size_t)stage * stage_bytes;
 #pragma unroll
-            for (int r = 0; r < R; r++) {
-                if (r0 + r < rows) {
-                    const uint4* sdy = reinterpret_cast<const uint4*>(dy + (r0 + r) * hidden);
-                    const uint4* sy = reinterpret_cast<const uint4*>(y + (r0 + r) * hidden);
+        for (int r = 0; r < R; r++) {
+            if (pf_row + r < rows) {
 #pragma unroll
-                    for (int i = 0; i < NVT; i++) {
-                        const int idx = i * nthreads + tid;
-                        if (own[i]) {
-                            cp_async_16(dst + (size_t)(2 * r) * nvec + idx, sdy + idx);
-                            cp_async_16(dst + (size_t)(2 * r + 1) * nvec + idx, sy + idx);
-                        }
+                for (int i = 0; i < NVT; i++) {
+                    if (own[i]) {
+                        cp_async_16(dst + (size_t)(2 * r) * row_bytes + off[i], pf_dy + (size_t)r * row_bytes + off[i]);
+                        cp_async_16(dst + (size_t)(2 * r + 1) * row_bytes + off[i], pf_y + (size_t)r * row_bytes + off[i]);
                     }
                 }
             }
         }
         cp_async_commit();
+        pf_row += stride_rows;
+        pf_dy += stride_bytes;
+        pf_y += stride_bytes;
     };
 #pragma unroll
-    for (int d = 0; d < DEPTH; d++) prefetch(d, d);
+    for (int d = 0; d < DEPTH; d++) prefetch(d);
 
     const float inv_h = 1.0f / (float)hidden;
     float gam[NVT][VN], cofs[NVT][VN], ginv[NVT][VN], acc_g[NVT][VN], acc_b[NVT][VN];
@@ -367,34 +375,31 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
         }
     }
 
-    // var of the rows two stages ahead is fetched now: a global load issued where it is needed would put its
-    // whole latency on the critical path of every stage (all threads meet at a barrier per stage)
-    auto load_var = [&](int64_t jj, float (&out)[R]) {
-#pragma unroll
-        for (int r = 0; r < R; r++) {
-            const int64_t row = ((int64_t)blockIdx.x + jj * gridDim.x) * R + r;
-            out[r] = (jj < nj && row < rows) ? __ldg(var + row) : 1.0f;
-        }
+    // Threads 0 .. R-1 look after var: thread r fetches var of row r of the group two steps ahead (a load issued where
+    // the value is needed would put its whole latency on the critical path of every step, since all threads meet at a
+    // barrier per step) and hands rsqrt(var) to the block through shared memory together with the row sums.
+    const bool var_thread = tid < R;
+    const float* var_ptr = var + first_row + tid;      // row of this thread in the current group
+    auto load_var = [&](int ahead) {
+        return (var_thread && first_row + tid + (int64_t)ahead * stride_rows < rows) ? __ldg(var_ptr + (int64_t)ahead * stride_rows) : 1.0f;
     };
-    float var0[R], var1[R], var2[R];
-    load_var(0, var0);
-    load_var(1, var1);
+    float var0 = load_var(0), var1 = load_var(1);
+    int64_t rows_left = rows - first_row;      // rows from the current group's first row to the end
 
     int phase = 0, stage = 0;
-    for (int64_t j = 0; j < nj; j++, phase ^= 1) {
-        load_var(j + 2, var2);
-        cp_async_wait<DEPTH - 1>();      // group j has landed (this thread's own packets)
-        const int64_t r0 = ((int64_t)blockIdx.x + j * gridDim.x) * R;
-        const uint4* sp = reinterpret_cast<const uint4*>(ring + (size_t)stage * stage_bytes);
+    unsigned char* dx_row = reinterpret_cast<unsigned char*>(dx) + (size_t)first_row * row_bytes;
+    for (; rows_left > 0; rows_left -= stride_rows, dx_row += stride_bytes, var_ptr += stride_rows, phase ^= 1) {
+        const float var2 = (var_thread && rows_left - tid > 2 * stride_rows) ? __ldg(var_ptr + 2 * stride_rows) : 1.0f;
+        cp_async_wait<DEPTH - 1>();      // the current group has landed (this thread's own packets)
+        const unsigned char* sp = ring + (size_t)stage * stage_bytes;
         Vec<T> vdy[R][NVT], vy[R][NVT];
 #pragma unroll
         for (int r = 0; r < R; r++) {
 #pragma unroll
             for (int i = 0; i < NVT; i++) {
-                const int idx = i * nthreads + tid;
-                if (own[i] && r0 + r < rows) {
-                    vdy[r][i].unpack(sp[(size_t)(2 * r) * nvec + idx]);
-                    vy[r][i].unpack(sp[(size_t)(2 * r + 1) * nvec + idx]);
+                if (own[i] && r < rows_left) {
+                    vdy[r][i].unpack(*reinterpret_cast<const uint4*>(sp + (size_t)(2 * r) * row_bytes + off[i]));
+                    vy[r][i].unpack(*reinterpret_cast<const uint4*>(sp + (size_t)(2 * r + 1) * row_bytes + off[i]));
                 } else {
 #pragma unroll
                     for (int e = 0; e < VN; e++) {
@@ -404,6 +409,7 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
                 }
             }
         }
+
         float sums[2 * R];
 #pragma unroll
         for (int r = 0; r < R; r++) {
@@ -428,36 +434,34 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
             sums[2 * r + 1] = b;
         }
         // this thread's packets of the stage have been read and used by now: refill them with the group DEPTH ahead
-        prefetch(j + DEPTH, stage);
+        prefetch(stage);
         if (++stage == DEPTH) stage = 0;
-        float* rp = red + phase * (2 * R * 32);
+        float* rp = red + phase * RED;
         lnr_warp_reduce_store<2 * R>(sums, rp, lane, warp);
+        if (var_thread) rp[2 * R * 32 + tid] = rsqrtf(var0);
         __syncthreads();
         lnr_block_totals<2 * R>(sums, rp, lane, nwarp);
 #pragma unroll
         for (int r = 0; r < R; r++) {
-            const int64_t row = r0 + r;
-            if (row >= rows) continue;
+            if (r >= rows_left) continue;
             // dx = (g - mean(g) - xhat * mean(g * xhat)) * rstd = g * rstd + (xhat * c2 + c1)
-            const float rstd = rsqrtf(var0[r]);
+            const float rstd = rp[2 * R * 32 + r];
             const float c1 = -sums[2 * r] * inv_h * rstd, c2 = -sums[2 * r + 1] * inv_h * rstd;
 #pragma unroll
             for (int i = 0; i < NVT; i++) {
                 if (!own[i]) continue;
-                const int idx = i * nthreads + tid;
                 Vec<T> o;
 #pragma unroll
                 for (int e = 0; e < VN; e++) o.v[e] = fmaf(vdy[r][i].v[e], rstd, fmaf(vy[r][i].v[e], c2, c1));
-                o.store_stream(dx + row * hidden + idx * VN);
+                __stcs(reinterpret_cast<uint4*>(dx_row + (size_t)r * row_bytes + off[i]), o.pack());
             }
         }
-#pragma unroll
-        for (int r = 0; r < R; r++) {
-            var0[r] = var1[r];
-            var1[r] = var2[r];
-        }
+        var0 = var1;
+        var1 = var2;
     }
     cp_async_wait<0>();
+    // the kernel that adds up the partial rows may start its launch now; it waits for this grid to finish before it reads
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     float* pg = partial + (size_t)blockIdx.x * 2 * hidden;
     float* pb = pg + hidden;
@@ -500,7 +504,7 @@ static int launch_ln_bwd_ring_d(const T* dy, const T* gamma, const T* beta, cons
     const int nvec = hidden / VN;
     const size_t row_bytes = (size_t)hidden * sizeof(T);
     const int threads = ((nvec + NVT - 1) / NVT + 31) / 32 * 32;
-    const size_t smem = (size_t)DEPTH * R * 2 * row_bytes + 2 * 2 * R * 32 * sizeof(float);
+    const size_t smem = (size_t)DEPTH * R * 2 * row_bytes + 2 * (2 * R + 1) * 32 * sizeof(float);
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
