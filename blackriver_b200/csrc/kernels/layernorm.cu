@@ -309,7 +309,7 @@ ln_bwd_reduce_kernel(const float* partial, T* dgamma, T* dbeta, int nparts, int 
     const int j = blockIdx.x * 32 + tx;
     // when launched as a programmatic dependent of the kernel that writes the partials: wait for that grid to
     // finish (returns at once otherwise)
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    pdl_wait();
     float s = 0.0f;
     if (j < 2 * hidden)
         for (int p = ty; p < nparts; p += 8) s += partial[(size_t)p * 2 * hidden + j];
@@ -323,6 +323,7 @@ ln_bwd_reduce_kernel(const float* partial, T* dgamma, T* dbeta, int nparts, int 
         if (accumulate) t += to_f32(*out);
         *out = from_f32<T>(t);
     }
+    pdl_launch_dependents();
 }
 
 // Generic path: one CTA per row for dx; column sums by a thread-per-column kernel.
@@ -416,18 +417,8 @@ static int ln_bwd_dispatch(const void* dy_, const void* gamma_, const void* beta
                 rc = launch_ln_bwd_ring<T, (Vec<T>::N == 4 ? 4 : 2)>(dy, gamma, beta, var, y, dx, partial, rows, h, eps, &rgrid, st);
             if (rc) return rc;
             // programmatic dependent launch: the reduce kernel's launch overlaps the tail of the kernel above
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3((unsigned)((2 * h + 31) / 32));
-            cfg.blockDim = dim3(256);
-            cfg.dynamicSmemBytes = 0;
-            cfg.stream = st;
-            cudaLaunchAttribute attr[1];
-            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[0].val.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = attr;
-            cfg.numAttrs = 1;
             const float* cpartial = partial;
-            cudaError_t le = cudaLaunchKernelEx(&cfg, ln_bwd_reduce_kernel<T>, cpartial, dgamma, dbeta, rgrid, h, accumulate);
+            cudaError_t le = launch_pdl(ln_bwd_reduce_kernel<T>, (2 * h + 31) / 32, 256, 0, st, cpartial, dgamma, dbeta, rgrid, h, accumulate);
             if (le != cudaSuccess) {
                 set_cuda_error(le, "ln_bwd_reduce_kernel");
                 return BRK_CUDA_ERROR;

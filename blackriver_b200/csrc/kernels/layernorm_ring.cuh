@@ -30,6 +30,25 @@ __device__ __forceinline__ void cp_async_wait() {      // at most N of this thre
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// Launch as a programmatic dependent of the kernel before it in the stream: the launch itself overlaps that kernel's
+// tail.  Every kernel launched this way executes pdl_wait() before it touches global memory.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float ln_guard_gamma(float g, float eps) { return g >= 0.0f ? g + eps : g - eps; }
 
 // One 16-byte packet of y = xhat * gamma + beta with xhat = x * rstd + shift.  fp32 tensors: all in fp32.
@@ -99,6 +118,7 @@ ln_fwd_ring_kernel(const T* x, const T* gamma, const T* beta, T* y, float* mean,
     const size_t row_bytes = (size_t)nvec * 16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int team = warp / WPR, member = warp % WPR;
+    pdl_wait();
     uint4* s_gamma = reinterpret_cast<uint4*>(smem_raw);
     uint4* s_beta = s_gamma + nvec;
     unsigned char* my_ring = smem_raw + 2 * row_bytes + (size_t)team * DEPTH * row_bytes;      // this team's DEPTH row slots
@@ -183,6 +203,7 @@ ln_fwd_ring_kernel(const T* x, const T* gamma, const T* beta, T* y, float* mean,
         }
     }
     cp_async_wait<0>();
+    pdl_launch_dependents();
 }
 
 // Row slots per team that fit next to gamma and beta: 3, 2 or 0 (= rows too large or too small for this kernel).
@@ -211,7 +232,12 @@ static int launch_ln_fwd_ring_d(const T* x, const T* gamma, const T* beta, T* y,
     const int64_t want = (rows + LNR_FWD_TEAMS - 1) / LNR_FWD_TEAMS;
     const int64_t cap = sm_count();
     const int grid = (int)(want < cap ? want : cap);
-    ln_fwd_ring_kernel<T, NV, DEPTH, WPR><<<grid, LNR_FWD_TEAMS * WPR * 32, smem, st>>>(x, gamma, beta, y, mean, var, rows, hidden, eps);
+    cudaError_t le = launch_pdl(ln_fwd_ring_kernel<T, NV, DEPTH, WPR>, grid, LNR_FWD_TEAMS * WPR * 32, smem, st, x, gamma, beta, y, mean,
+                                var, rows, hidden, eps);
+    if (le != cudaSuccess) {
+        set_cuda_error(le, "ln_fwd_ring_kernel");
+        return BRK_CUDA_ERROR;
+    }
     return launch_status("ln_fwd_ring_kernel");
 }
 
@@ -314,6 +340,7 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
     const int nthreads = (int)blockDim.x;      // a multiple of 32
     const int nwarp = nthreads >> 5;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_wait();
 
     // Row groups of this CTA: group blockIdx.x + j * gridDim.x holds rows group*R .. group*R + R-1.  Everything that
     // walks over the groups (first row, byte offsets) is advanced by a constant per step instead of recomputed.
@@ -461,7 +488,7 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
     }
     cp_async_wait<0>();
     // the kernel that adds up the partial rows may start its launch now; it waits for this grid to finish before it reads
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    pdl_launch_dependents();
 
     float* pg = partial + (size_t)blockIdx.x * 2 * hidden;
     float* pb = pg + hidden;
@@ -514,7 +541,12 @@ static int launch_ln_bwd_ring_d(const T* dy, const T* gamma, const T* beta, cons
         set_cuda_error(attr_err, "ln_bwd_ring smem attribute");
         return BRK_CUDA_ERROR;
     }
-    ln_bwd_ring_kernel<T, NVT, DEPTH><<<grid, threads, smem, st>>>(dy, gamma, beta, var, y, dx, partial, rows, hidden, eps);
+    cudaError_t le = launch_pdl(ln_bwd_ring_kernel<T, NVT, DEPTH>, grid, threads, smem, st, dy, gamma, beta, var, y, dx, partial, rows,
+                                hidden, eps);
+    if (le != cudaSuccess) {
+        set_cuda_error(le, "ln_bwd_ring_kernel");
+        return BRK_CUDA_ERROR;
+    }
     return launch_status("ln_bwd_ring_kernel");
 }
 
