@@ -56,6 +56,7 @@ template <typename T, bool BWD>
 __global__ void __launch_bounds__(GELU_THREADS)
 gelu_vec_kernel(const T* dy, const T* x, T* out, int64_t nvec) {
     constexpr int VN = Vec<T>::N;
+    pdl_wait();
     const int64_t stride = (int64_t)gridDim.x * GELU_THREADS;
     for (int64_t base = (int64_t)blockIdx.x * GELU_THREADS + threadIdx.x; base < nvec; base += stride * GELU_UNROLL) {
         // the packets stay packed (4 registers each) until their turn: more loads in flight per register
@@ -82,6 +83,7 @@ gelu_vec_kernel(const T* dy, const T* x, T* out, int64_t nvec) {
             }
         }
     }
+    pdl_launch_dependents();
 }
 
 template <typename T, bool BWD>
@@ -105,7 +107,11 @@ static int gelu_dispatch(const void* dy_, const void* x_, void* out_, int64_t n,
         int64_t want = (nvec + (int64_t)GELU_THREADS * GELU_UNROLL - 1) / ((int64_t)GELU_THREADS * GELU_UNROLL);
         int64_t cap = (int64_t)sm_count() * 16;
         int grid = (int)(want < cap ? want : cap);
-        gelu_vec_kernel<T, BWD><<<grid, GELU_THREADS, 0, st>>>(dy, x, out, nvec);
+        cudaError_t le = launch_pdl(gelu_vec_kernel<T, BWD>, grid, GELU_THREADS, 0, st, dy, x, out, nvec);
+        if (le != cudaSuccess) {
+            set_cuda_error(le, "gelu_vec_kernel");
+            return BRK_CUDA_ERROR;
+        }
         int rc = launch_status("gelu_vec_kernel");
         if (rc) return rc;
     }

@@ -299,26 +299,38 @@ ln_bwd_kernel(const T* dy, const T* gamma, const T* beta,
     }
 }
 
-// out[j] = sum_p partial[p][j], j over 2*hidden (dgamma then dbeta).  32 columns x 8 partial lanes per
-// CTA; each lane adds every 8th partial, the lanes are combined in a fixed order (deterministic).
+// out[j] = sum_p partial[p][j], j over 2*hidden (dgamma then dbeta).  32 columns x 16 partial lanes per CTA; each
+// lane adds every 16th partial into four interleaved accumulators (independent loads in flight), and the lanes
+// are combined in a fixed order (deterministic).
+constexpr int LN_RED_LANES = 16;
+
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(32 * LN_RED_LANES)
 ln_bwd_reduce_kernel(const float* partial, T* dgamma, T* dbeta, int nparts, int hidden, int accumulate) {
-    __shared__ float red[8][33];
+    __shared__ float red[LN_RED_LANES][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int j = blockIdx.x * 32 + tx;
     // when launched as a programmatic dependent of the kernel that writes the partials: wait for that grid to
     // finish (returns at once otherwise)
     pdl_wait();
-    float s = 0.0f;
-    if (j < 2 * hidden)
-        for (int p = ty; p < nparts; p += 8) s += partial[(size_t)p * 2 * hidden + j];
-    red[ty][tx] = s;
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+    if (j < 2 * hidden) {
+        const size_t stride = (size_t)2 * hidden;
+        int p = ty;
+        for (; p + 3 * LN_RED_LANES < nparts; p += 4 * LN_RED_LANES) {
+            s0 += partial[(size_t)p * stride + j];
+            s1 += partial[(size_t)(p + LN_RED_LANES) * stride + j];
+            s2 += partial[(size_t)(p + 2 * LN_RED_LANES) * stride + j];
+            s3 += partial[(size_t)(p + 3 * LN_RED_LANES) * stride + j];
+        }
+        for (; p < nparts; p += LN_RED_LANES) s0 += partial[(size_t)p * stride + j];
+    }
+    red[ty][tx] = (s0 + s1) + (s2 + s3);
     __syncthreads();
     if (ty == 0 && j < 2 * hidden) {
         float t = 0.0f;
 #pragma unroll
-        for (int k = 0; k < 8; k++) t += red[k][tx];
+        for (int k = 0; k < LN_RED_LANES; k++) t += red[k][tx];
         T* out = j < hidden ? dgamma + j : dbeta + (j - hidden);
         if (accumulate) t += to_f32(*out);
         *out = from_f32<T>(t);
@@ -418,7 +430,7 @@ static int ln_bwd_dispatch(const void* dy_, const void* gamma_, const void* beta
             if (rc) return rc;
             // programmatic dependent launch: the reduce kernel's launch overlaps the tail of the kernel above
             const float* cpartial = partial;
-            cudaError_t le = launch_pdl(ln_bwd_reduce_kernel<T>, (2 * h + 31) / 32, 256, 0, st, cpartial, dgamma, dbeta, rgrid, h, accumulate);
+            cudaError_t le = launch_pdl(ln_bwd_reduce_kernel<T>, (2 * h + 31) / 32, 32 * LN_RED_LANES, 0, st, cpartial, dgamma, dbeta, rgrid, h, accumulate);
             if (le != cudaSuccess) {
                 set_cuda_error(le, "ln_bwd_reduce_kernel");
                 return BRK_CUDA_ERROR;
@@ -436,7 +448,7 @@ static int ln_bwd_dispatch(const void* dy_, const void* gamma_, const void* beta
             ln_bwd_kernel<T, 4><<<grid, threads, 0, st>>>(dy, gamma, beta, var, y, dx, partial, rows, h, eps);
         int rc = launch_status("ln_bwd_kernel");
         if (rc) return rc;
-        ln_bwd_reduce_kernel<T><<<(2 * h + 31) / 32, 256, 0, st>>>(partial, dgamma, dbeta, grid, h, accumulate);
+        ln_bwd_reduce_kernel<T><<<(2 * h + 31) / 32, 32 * LN_RED_LANES, 0, st>>>(partial, dgamma, dbeta, grid, h, accumulate);
         return launch_status("ln_bwd_reduce_kernel");
     }
     // column sums first: dx may alias dy or y

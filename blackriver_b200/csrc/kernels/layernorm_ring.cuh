@@ -30,25 +30,6 @@ __device__ __forceinline__ void cp_async_wait() {      // at most N of this thre
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// Launch as a programmatic dependent of the kernel before it in the stream: the launch itself overlaps that kernel's
-// tail.  Every kernel launched this way executes pdl_wait() before it touches global memory.
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3((unsigned)block);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 __device__ __forceinline__ float ln_guard_gamma(float g, float eps) { return g >= 0.0f ? g + eps : g - eps; }
 
 // One 16-byte packet of y = xhat * gamma + beta with xhat = x * rstd + shift.  fp32 tensors: all in fp32.
