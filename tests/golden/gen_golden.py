@@ -19,7 +19,7 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BLACKRIVER_REFERENCE", os.path.join(os.sep, "root", "reference"))
 sys.path.insert(0, os.path.join(REF, "bloomz-7b"))
 import model as refmodel  # noqa: E402
 

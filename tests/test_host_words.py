@@ -9,7 +9,7 @@ import pytest
 
 from blackriver_b200 import host, words
 
-REF = "/root/reference/bloomz-7b"
+REF = os.path.join(os.environ.get("BLACKRIVER_REFERENCE", os.path.join(os.sep, "root", "reference")), "bloomz-7b")
 
 
 @pytest.fixture()

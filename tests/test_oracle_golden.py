@@ -102,7 +102,7 @@ def test_targets_and_mask_small_exact():
 
 
 def test_builders_on_reference_inputs(golden_dir):
-    ref = "/root/reference/bloomz-7b"
+    ref = os.path.join(os.environ.get("BLACKRIVER_REFERENCE", os.path.join(os.sep, "root", "reference")), "bloomz-7b")
     if not os.path.exists(os.path.join(ref, "xinput.ids.bin")):
         pytest.skip("reference data files not present on this machine")
     d = load(golden_dir, "xinput_digest.npz")
