@@ -1,0 +1,150 @@
+"""Discrete-event model of the pipeline schedules, for reasoning about them without GPUs.
+
+A schedule is one ordered list of operations per rank -- what the rank's compute stream executes:
+    ("work", cost)                  compute
+    ("send", peer) / ("recv", peer) a stage hand-off; matched in order per (sender, receiver) pair
+Two link models:
+    rendezvous   a send completes only when the receiver has reached the matching recv (what
+                 ncclSend / ncclRecv of a 16.8 MB activation do), so sender and receiver leave together
+    buffered     a send never waits (one-sided write into a per-micro-batch receive window); the
+                 receiver waits for the data
+`simulate` reports whether every rank finishes (a False is a deadlock of the schedule under that link
+model) and the makespan.  Costs are in units of one decoder layer's forward; a layer's backward costs
+two, the head (final LayerNorm + LM head + loss) `head_cost` layers for forward + backward together.
+
+The model reproduces the measured scaling of the all-forward-then-all-backward schedule (0.84 on 4
+GPUs, 0.58-0.64 on 8) and is how candidate schedules are compared before they are built."""
+from . import finetune
+
+FWD, BWD = 1.0, 2.0      # cost of one layer, forward / backward
+
+
+def stage_costs(counts, head_cost):
+    """(forward, backward) cost per micro-batch of every stage; the head splits 1 : 2 like a layer."""
+    out = []
+    for r, c in enumerate(counts):
+        extra = head_cost if r == len(counts) - 1 else 0.0
+        out.append((c * FWD + extra * FWD, c * BWD + extra * BWD))
+    return out
+
+
+def gpipe_programs(counts, n_micro, head_cost=finetune.LM_HEAD_COST_IN_LAYERS):
+    """Every micro-batch forward through all stages, then every micro-batch backward (finetune.Trainer.step)."""
+    world = len(counts)
+    costs = stage_costs(counts, head_cost)
+    progs = []
+    for r in range(world):
+        ops = []
+        for _ in range(n_micro):
+            if r > 0:
+                ops.append(("recv", r - 1))
+            ops.append(("work", costs[r][0]))
+            if r < world - 1:
+                ops.append(("send", r + 1))
+        for _ in range(n_micro):
+            if r < world - 1:
+                ops.append(("recv", r + 1))
+            ops.append(("work", costs[r][1]))
+            if r > 0:
+                ops.append(("send", r - 1))
+        progs.append(ops)
+    return progs
+
+
+def one_f_one_b_programs(counts, n_micro, head_cost=finetune.LM_HEAD_COST_IN_LAYERS):
+    """Warm-up forwards, then alternating one forward / one backward, then the remaining backwards."""
+    world = len(counts)
+    costs = stage_costs(counts, head_cost)
+    progs = []
+    for r in range(world):
+        warm = min(world - 1 - r, n_micro)
+        ops = []
+
+        def fwd():
+            if r > 0:
+                ops.append(("recv", r - 1))
+            ops.append(("work", costs[r][0]))
+            if r < world - 1:
+                ops.append(("send", r + 1))
+
+        def bwd():
+            if r < world - 1:
+                ops.append(("recv", r + 1))
+            ops.append(("work", costs[r][1]))
+            if r > 0:
+                ops.append(("send", r - 1))
+
+        for _ in range(warm):
+            fwd()
+        for _ in range(n_micro - warm):
+            fwd()
+            bwd()
+        for _ in range(warm):
+            bwd()
+        progs.append(ops)
+    return progs
+
+
+def simulate(programs, link="rendezvous"):
+    """Runs the per-rank programs; returns (finished, makespan, per-rank busy time)."""
+    assert link in ("rendezvous", "buffered")
+    world = len(programs)
+    pc = [0] * world
+    clock = [0.0] * world
+    busy = [0.0] * world
+    mailbox = {}      # (src, dst) -> arrival times of sent, not yet received messages (buffered links)
+    progressed = True
+    while progressed:
+        progressed = False
+        for r in range(world):
+            while pc[r] < len(programs[r]):
+                op = programs[r][pc[r]]
+                if op[0] == "work":
+                    clock[r] += op[1]
+                    busy[r] += op[1]
+                elif op[0] == "send":
+                    dst = op[1]
+                    if link == "buffered":
+                        mailbox.setdefault((r, dst), []).append(clock[r])
+                    else:
+                        nxt = programs[dst][pc[dst]] if pc[dst] < len(programs[dst]) else None
+                        if nxt != ("recv", r):
+                            break      # the receiver is not there yet
+                        t = max(clock[r], clock[dst])
+                        clock[r] = clock[dst] = t
+                        pc[dst] += 1
+                elif op[0] == "recv":
+                    if link == "rendezvous":
+                        break          # completed by the sender's branch above
+                    box = mailbox.get((op[1], r))
+                    if not box:
+                        break
+                    clock[r] = max(clock[r], box.pop(0))
+                pc[r] += 1
+                progressed = True
+    finished = all(pc[r] == len(programs[r]) for r in range(world))
+    return finished, max(clock), busy
+
+
+def efficiency(counts, n_micro, programs, link="rendezvous", head_cost=finetune.LM_HEAD_COST_IN_LAYERS):
+    """Scaling efficiency the schedule would reach: one GPU's time for the same work / (ranks x makespan)."""
+    ok, span, _ = simulate(programs, link)
+    if not ok:
+        return None
+    single = n_micro * (sum(counts) + head_cost) * (FWD + BWD)
+    return single / (len(counts) * span)
+
+
+def report(n_layers=30, n_micro=16, head_cost=finetune.LM_HEAD_COST_IN_LAYERS):
+    rows = []
+    for world in (2, 4, 8):
+        counts = finetune.partition_layers(n_layers, world, head_cost)
+        for name, build in (("all-forward-all-backward", gpipe_programs), ("one-forward-one-backward", one_f_one_b_programs)):
+            for link in ("rendezvous", "buffered"):
+                rows.append((world, counts, name, link, efficiency(counts, n_micro, build(counts, n_micro, head_cost), link, head_cost)))
+    return rows
+
+
+if __name__ == "__main__":
+    for world, counts, name, link, eff in report():
+        print(f"{world} GPUs {counts}  {name:26s} {link:10s}  " + ("deadlock" if eff is None else f"{eff:.3f}"))
