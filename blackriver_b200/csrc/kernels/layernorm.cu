@@ -160,7 +160,8 @@ static int ln_fwd_dispatch(const void* x_, const void* gamma_, const void* beta_
             if (nv <= 4) return launch_ln_fwd_ring<T, 4>(x, gamma, beta, y, mean, var, rows, h, eps, st);
             if (nv <= 8) return launch_ln_fwd_ring<T, 8>(x, gamma, beta, y, mean, var, rows, h, eps, st);
             if (nv <= 16) return launch_ln_fwd_ring<T, 16>(x, gamma, beta, y, mean, var, rows, h, eps, st);
-            if (VN * 32 <= 128) return launch_ln_fwd_ring<T, (VN * 32 <= 128 ? 32 : 16)>(x, gamma, beta, y, mean, var, rows, h, eps, st);
+            // 17 .. 32 packets per lane fit the registers only for fp32 (nv * VN <= 128 above): fp16 never gets here
+            return launch_ln_fwd_ring<T, (VN == 4 ? 32 : 16)>(x, gamma, beta, y, mean, var, rows, h, eps, st);
         }
         if (nv <= 1) return launch_ln_fwd<T, 1>(x, gamma, beta, y, mean, var, rows, h, eps, st);
         if (nv <= 2) return launch_ln_fwd<T, 2>(x, gamma, beta, y, mean, var, rows, h, eps, st);
