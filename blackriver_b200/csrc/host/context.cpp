@@ -1,5 +1,9 @@
 #include "context.hpp"
 
+#include <sys/stat.h>
+#include <unistd.h>
+#include <ctime>
+
 #include <unistd.h>
 
 #include <chrono>
@@ -185,15 +189,23 @@ void CollectiveContext::boot_from_file(int rank, int world, const std::string& p
         }
         br_assert(::rename(tmp.c_str(), path.c_str()) == 0, "can't publish the NCCL id file");
     } else {
+        // a file left behind by an earlier job under the same name must not be taken for this job's id:
+        // only a file written since shortly before this rank started counts (the ranks of a job start together)
+        const time_t not_before = ::time(nullptr) - 30;
         bool got = false;
         for (int i = 0; i < timeout_s * 20 && !got; i++) {
-            std::ifstream in(path, std::ios::binary);
-            if (in && in.read(reinterpret_cast<char*>(&id), sizeof(id))) got = true;
-            else std::this_thread::sleep_for(std::chrono::milliseconds(50));
+            struct stat st;
+            if (::stat(path.c_str(), &st) == 0 && st.st_mtime >= not_before) {
+                std::ifstream in(path, std::ios::binary);
+                if (in && in.read(reinterpret_cast<char*>(&id), sizeof(id))) got = true;
+            }
+            if (!got) std::this_thread::sleep_for(std::chrono::milliseconds(50));
         }
         br_assert(got, "timed out waiting for the NCCL id file");
     }
     boot(rank, world, id);
+    // every rank has read the id once the communicator exists: the publisher takes the file away again
+    if (rank == 0) ::unlink(path.c_str());
 }
 
 void CollectiveContext::shutdown() {

@@ -23,6 +23,8 @@
 #include <string>
 #include <vector>
 
+#include <unistd.h>
+
 #include "common.hpp"
 #include "context.hpp"
 #include "dag.hpp"
@@ -32,7 +34,7 @@
 namespace {
 
 struct Options {
-    std::string script, data, id_file = "/tmp/train_bloom.ncclid";
+    std::string script, data, id_file;      // id_file default: a name shared by the processes of one launch (same parent)
     int layers = -1;          // decoder layers of THIS stage (hash tables = layers + 1)
     int steps = 3, micro = 1, batch = 2, tokens = 128, vocab = 250880, min_len = 1;
     uint64_t seed = 3;
@@ -48,6 +50,7 @@ void usage() {
                  "  STAGE.words   script of this rank's stage (python -m blackriver_b200.emit_stage prints the command)\n"
                  "  --data PREFIX raw int32 files PREFIX.ids.bin, PREFIX.mask.bin [micro, batch, tokens] and\n"
                  "                PREFIX.lens.bin [micro, batch]; without it seeded random ids with right padding\n"
+                 "  --id-file     where rank 0 publishes the NCCL id (default /tmp/train_bloom.<parent pid>.ncclid)\n"
                  "  environment   RANK, WORLD_SIZE, LOCAL_RANK (default 0, 1, 0)\n");
 }
 
@@ -161,6 +164,7 @@ int main(int argc, char** argv) {
         return 2;
     }
     const int rank = env_int("RANK", 0), world = env_int("WORLD_SIZE", 1), local = env_int("LOCAL_RANK", rank);
+    if (o.id_file.empty()) o.id_file = "/tmp/train_bloom." + std::to_string((long)getppid()) + ".ncclid";
     try {
         br::ComputingContext::boot(local);
         if (world > 1) br::CollectiveContext::boot_from_file(rank, world, o.id_file);
