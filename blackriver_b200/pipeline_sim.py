@@ -135,6 +135,62 @@ def efficiency(counts, n_micro, programs, link="rendezvous", head_cost=finetune.
     return single / (len(counts) * span)
 
 
+def greedy_estimate(layer_counts, n_micro, head_cost=finetune.LM_HEAD_COST_IN_LAYERS, tail_layers=0, tail_replicas=1,
+                    split_backward=False):
+    """Upper estimate for schedules that need buffered links: greedy list scheduling of the tasks F(stage, mb), B(stage, mb)
+    and, with split_backward, W(stage, mb) -- the weight gradients, which nothing downstream waits for and which therefore
+    fill idle time (priority: B, then F, then W).  The stages are the entries of layer_counts, one rank each, followed
+    by a tail stage of `tail_layers` layers + the head, replicated on `tail_replicas` ranks that take the micro-batches in
+    turn.  Costs: forward, input-gradient and weight-gradient pass of a layer one unit each (the backward of the other
+    schedules is the last two together).  Returns the scaling efficiency."""
+    stages = [float(c) for c in layer_counts] + [float(tail_layers) + head_cost]
+    n_stage = len(stages)
+    n_body = len(layer_counts)
+    world = n_body + tail_replicas
+    kinds = 3 if split_backward else 2
+
+    def rank_of(s, m):
+        return s if s < n_body else n_body + m % tail_replicas
+
+    def cost(s, kind):
+        return stages[s] if (split_backward or kind == 0) else 2.0 * stages[s]
+
+    ready = [[] for _ in range(world)]
+    clock = [0.0] * world
+    for m in range(n_micro):
+        ready[rank_of(0, m)].append(((1, m, 0), 0.0, 0, m, 0))
+    left = kinds * n_stage * n_micro
+    while left:
+        best = None
+        for r in range(world):
+            if not ready[r]:
+                continue
+            avail = [x for x in ready[r] if x[1] <= clock[r] + 1e-12]
+            cand, start = (min(avail), clock[r]) if avail else (min(ready[r], key=lambda x: (x[1], x[0])), None)
+            if start is None:
+                start = cand[1]
+            if best is None or start < best[0]:
+                best = (start, r, cand)
+        start, r, cand = best
+        ready[r].remove(cand)
+        _, _, s, m, kind = cand
+        end = start + cost(s, kind)
+        clock[r] = end
+        left -= 1
+        if kind == 0:
+            if s + 1 < n_stage:
+                ready[rank_of(s + 1, m)].append(((1, m, s + 1), end, s + 1, m, 0))
+            else:
+                ready[rank_of(s, m)].append(((0, m, s), end, s, m, 1))
+        elif kind == 1:
+            if split_backward:
+                ready[rank_of(s, m)].append(((2, m, s), end, s, m, 2))
+            if s > 0:
+                ready[rank_of(s - 1, m)].append(((0, m, s - 1), end, s - 1, m, 1))
+    single = n_micro * (sum(layer_counts) + tail_layers + head_cost) * 3.0
+    return single / (world * max(clock))
+
+
 def report(n_layers=30, n_micro=16, head_cost=finetune.LM_HEAD_COST_IN_LAYERS):
     rows = []
     for world in (2, 4, 8):
@@ -148,3 +204,10 @@ def report(n_layers=30, n_micro=16, head_cost=finetune.LM_HEAD_COST_IN_LAYERS):
 if __name__ == "__main__":
     for world, counts, name, link, eff in report():
         print(f"{world} GPUs {counts}  {name:26s} {link:10s}  " + ("deadlock" if eff is None else f"{eff:.3f}"))
+    print("greedy estimates, buffered links, 16 micro-batches:")
+    for label, kw in (("4 GPUs [9,9,9]+head", dict(layer_counts=[9, 9, 9], tail_layers=3)),
+                      ("8 GPUs [5,5,4,4,4,4,4]+head", dict(layer_counts=[5, 5, 4, 4, 4, 4, 4])),
+                      ("8 GPUs [5,5,5,4,4,4] + (3 layers + head) x 2 ranks", dict(layer_counts=[5, 5, 5, 4, 4, 4], tail_layers=3, tail_replicas=2))):
+        a = greedy_estimate(n_micro=16, **kw)
+        b = greedy_estimate(n_micro=16, split_backward=True, **kw)
+        print(f"  {label:52s} backward whole {a:.3f}   weight gradients deferred {b:.3f}")

@@ -28,3 +28,15 @@ def test_one_forward_one_backward_needs_buffered_links():
     progs = ps.one_f_one_b_programs(counts, 16)
     assert ps.simulate(progs, "rendezvous")[0] is False      # two neighbours each waiting to send to the other
     assert ps.simulate(progs, "buffered")[0] is True
+
+
+def test_greedy_estimates():
+    # without deferring anything the greedy order is no better than the Trainer's schedule ...
+    whole = ps.greedy_estimate([5, 5, 4, 4, 4, 4, 4], 16)
+    c8 = [5, 5, 4, 4, 4, 4, 4, 0]
+    assert abs(whole - ps.efficiency(c8, 16, ps.gpipe_programs(c8, 16))) < 0.02
+    # ... deferring the weight gradients into the idle time and sharing the head between two ranks is what closes the gap
+    split = ps.greedy_estimate([5, 5, 4, 4, 4, 4, 4], 16, split_backward=True)
+    shared = ps.greedy_estimate([5, 5, 5, 4, 4, 4], 16, tail_layers=3, tail_replicas=2, split_backward=True)
+    assert whole < split < shared and shared >= 0.85
+    assert ps.greedy_estimate([9, 9, 9], 16, tail_layers=3, split_backward=True) >= 0.93
