@@ -28,6 +28,17 @@ def test_library_exports_every_declared_symbol():
     assert set(names) == set(brk.SIGNATURES), "python binding table and header disagree"
 
 
+def test_host_library_exports_every_declared_symbol():
+    from blackriver_b200 import host
+    txt = open(os.path.join(ROOT, "include", "br_host.h")).read()
+    names = re.findall(r"^BRH_API[^;(]*?\b(brh_\w+)\s*\(", txt, flags=re.M)
+    assert len(names) >= 25
+    lib = host.lib()
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/br_host.h but not exported by libbr_host.so"
+    assert set(names) == set(host.SIGNATURES), "python binding table and header disagree"
+
+
 def test_every_declaration_cites_the_reference():
     txt = open(os.path.join(ROOT, "include", "brk.h")).read()
     assert txt.count("blackriver/") >= 10
