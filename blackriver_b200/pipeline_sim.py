@@ -136,13 +136,14 @@ def efficiency(counts, n_micro, programs, link="rendezvous", head_cost=finetune.
 
 
 def greedy_estimate(layer_counts, n_micro, head_cost=finetune.LM_HEAD_COST_IN_LAYERS, tail_layers=0, tail_replicas=1,
-                    split_backward=False):
+                    split_backward=False, return_order=False):
     """Upper estimate for schedules that need buffered links: greedy list scheduling of the tasks F(stage, mb), B(stage, mb)
     and, with split_backward, W(stage, mb) -- the weight gradients, which nothing downstream waits for and which therefore
     fill idle time (priority: B, then F, then W).  The stages are the entries of layer_counts, one rank each, followed
     by a tail stage of `tail_layers` layers + the head, replicated on `tail_replicas` ranks that take the micro-batches in
     turn.  Costs: forward, input-gradient and weight-gradient pass of a layer one unit each (the backward of the other
-    schedules is the last two together).  Returns the scaling efficiency."""
+    schedules is the last two together).  Returns the scaling efficiency, and with return_order also the order in which
+    every rank starts its tasks: a static schedule that `replay` can execute."""
     stages = [float(c) for c in layer_counts] + [float(tail_layers) + head_cost]
     n_stage = len(stages)
     n_body = len(layer_counts)
@@ -157,6 +158,7 @@ def greedy_estimate(layer_counts, n_micro, head_cost=finetune.LM_HEAD_COST_IN_LA
 
     ready = [[] for _ in range(world)]
     clock = [0.0] * world
+    order = [[] for _ in range(world)]      # (kind, stage, micro-batch) in the order each rank starts them
     for m in range(n_micro):
         ready[rank_of(0, m)].append(((1, m, 0), 0.0, 0, m, 0))
     left = kinds * n_stage * n_micro
@@ -176,6 +178,7 @@ def greedy_estimate(layer_counts, n_micro, head_cost=finetune.LM_HEAD_COST_IN_LA
         _, _, s, m, kind = cand
         end = start + cost(s, kind)
         clock[r] = end
+        order[r].append(("FBW"[kind], s, m))
         left -= 1
         if kind == 0:
             if s + 1 < n_stage:
@@ -188,7 +191,65 @@ def greedy_estimate(layer_counts, n_micro, head_cost=finetune.LM_HEAD_COST_IN_LA
             if s > 0:
                 ready[rank_of(s - 1, m)].append(((0, m, s - 1), end, s - 1, m, 1))
     single = n_micro * (sum(layer_counts) + tail_layers + head_cost) * 3.0
+    if return_order:
+        return single / (world * max(clock)), order
     return single / (world * max(clock))
+
+
+def replay(order, layer_counts, n_micro, head_cost=finetune.LM_HEAD_COST_IN_LAYERS, tail_layers=0, tail_replicas=1,
+           split_backward=False):
+    """Executes a static schedule -- per rank the list of ("F" | "B" | "W", stage, micro-batch) in issue order, as
+    greedy_estimate(..., return_order=True) produces it -- with buffered links: a task starts when the rank has finished
+    the task before it and its inputs have arrived.  Returns (finished, efficiency, what has to be kept): the largest
+    number of micro-batches whose activations a rank holds at once (forward done, backward not yet) and the largest
+    number of deferred weight-gradient passes (backward done, W not yet), per rank."""
+    stages = [float(c) for c in layer_counts] + [float(tail_layers) + head_cost]
+    n_stage, n_body = len(stages), len(layer_counts)
+    world = n_body + tail_replicas
+    done = {}
+    pc = [0] * world
+    clock = [0.0] * world
+    live_act = [0] * world
+    live_w = [0] * world
+    peak_act = [0] * world
+    peak_w = [0] * world
+
+    def needs(kind, s, m):
+        if kind == "F":
+            return [("F", s - 1, m)] if s > 0 else []
+        if kind == "B":
+            return [("F", s, m)] + ([("B", s + 1, m)] if s + 1 < n_stage else [])
+        return [("B", s, m)]
+
+    progressed = True
+    while progressed:
+        progressed = False
+        for r in range(world):
+            while pc[r] < len(order[r]):
+                kind, s, m = order[r][pc[r]]
+                deps = needs(kind, s, m)
+                if any(d not in done for d in deps):
+                    break
+                start = max([clock[r]] + [done[d] for d in deps])
+                c = stages[s] if (split_backward or kind == "F") else 2.0 * stages[s]
+                clock[r] = done[(kind, s, m)] = start + c
+                if kind == "F":
+                    live_act[r] += 1
+                elif kind == "B":
+                    if split_backward:
+                        live_w[r] += 1
+                    else:
+                        live_act[r] -= 1
+                else:
+                    live_w[r] -= 1
+                    live_act[r] -= 1      # the layer inputs are needed until the weight gradients have been taken
+                peak_act[r] = max(peak_act[r], live_act[r])
+                peak_w[r] = max(peak_w[r], live_w[r])
+                pc[r] += 1
+                progressed = True
+    finished = all(pc[r] == len(order[r]) for r in range(world))
+    single = n_micro * (sum(layer_counts) + tail_layers + head_cost) * 3.0
+    return finished, (single / (world * max(clock)) if finished else None), {"activations": peak_act, "deferred": peak_w}
 
 
 def report(n_layers=30, n_micro=16, head_cost=finetune.LM_HEAD_COST_IN_LAYERS):

@@ -40,3 +40,17 @@ def test_greedy_estimates():
     shared = ps.greedy_estimate([5, 5, 5, 4, 4, 4], 16, tail_layers=3, tail_replicas=2, split_backward=True)
     assert whole < split < shared and shared >= 0.85
     assert ps.greedy_estimate([9, 9, 9], 16, tail_layers=3, split_backward=True) >= 0.93
+
+
+def test_static_schedule_replays_to_the_same_makespan():
+    kw = dict(layer_counts=[5, 5, 5, 4, 4, 4], n_micro=16, tail_layers=3, tail_replicas=2, split_backward=True)
+    eff, order = ps.greedy_estimate(return_order=True, **kw)
+    assert sum(len(o) for o in order) == 3 * 7 * 16                      # every task of every stage and micro-batch, once
+    ok, eff2, keep = ps.replay(order, **kw)
+    assert ok and abs(eff - eff2) < 1e-9
+    assert max(keep["activations"]) <= 16 and max(keep["deferred"]) <= 16
+    # a schedule with a task before its producer does not finish
+    bad = [list(o) for o in order]
+    i = next(j for j, t in enumerate(bad[0]) if t[0] == "B")
+    bad[0][0], bad[0][i] = bad[0][i], bad[0][0]
+    assert ps.replay(bad, **kw)[0] is False
