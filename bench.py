@@ -621,6 +621,14 @@ def run_case(args):
         c = torch.empty(m, n, device=dev).half()
         for _ in range(reps * 2):
             ops.gemm_f16(a, b, c, m, n, k, 0, 1, k, k, n)
+    elif args.case == "gemm_dw":
+        # weight gradient of the h -> 4h projection for one micro-batch: W_g [16384, 4096] += dy^T [16384, 2048] x [2048, 4096]
+        m, n, k = 16384, 4096, 2048
+        a = torch.randn(k, m, generator=g, device=dev).half()
+        b = torch.randn(k, n, generator=g, device=dev).half()
+        c = torch.zeros(m, n, device=dev).half()
+        for _ in range(reps * 2):
+            ops.gemm_f16(a, b, c, m, n, k, 1, 0, m, n, n, accumulate=True)
     elif args.case == "attn":
         from blackriver_b200 import brk
         B, T, heads, d = 2, 1024, 32, 128
@@ -776,7 +784,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fine-tune workload with fewer layers (development aid)")
     ap.add_argument("--micro", type=int, default=0, help="fine-tune workload with fewer micro-batches (development aid)")
     ap.add_argument("--skip-ops", action="store_true", help="do not run the operator microbench before the fine-tune step")
-    ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "attn"],
+    ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "gemm_dw", "attn"],
                     help="profiling aid: run a few launches of one kernel family on a small case and exit")
     ap.add_argument("--rows", type=int, default=1024, help="rows of the --case run")
     args = ap.parse_args()

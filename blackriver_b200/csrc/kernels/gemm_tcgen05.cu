@@ -12,6 +12,7 @@
 // Operands may be K-major or MN-major in memory (all four transposition cases of the backward
 // pass); the shared-memory descriptors and the instruction descriptor carry the difference.
 // Tails in m, n, k are handled by TMA zero fill on loads and predication on stores.
+#include <cstring>
 #include <mutex>
 
 #include "brk_common.cuh"
@@ -87,7 +88,9 @@ __device__ __forceinline__ void tc_store_chunk(const TcParams& p, const uint32_t
             }
         }
     } else {
-        for (int e = 0; e < 32 && col0 + e < p.n; e++) {
+#pragma unroll
+        for (int e = 0; e < 32; e++) {       // fully unrolled so that v stays in registers
+            if (col0 + e >= p.n) break;
             float f = __uint_as_float(v[e]);
             if (p.bias) f += __half2float(p.bias[col0 + e]);
             if (rrow) f += __half2float(rrow[e]);
@@ -100,6 +103,7 @@ __device__ __forceinline__ void tc_store_chunk(const TcParams& p, const uint32_t
 
 __device__ __forceinline__ bool tc_vec_ok(const TcParams& p) {
     return (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) &&
+           (!p.bias || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
            (!p.residual || ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0))) &&
            (!p.gelu_out || ((p.ldg % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.gelu_out) & 15) == 0)));
 }
@@ -218,9 +222,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int quarter = warp & 3;  // TMEM lanes this warp may touch: 32*quarter .. +31
         uint32_t tcount = 0;
         bool ok = true;
-        const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) &&
-                            (!p.residual || ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0))) &&
-                            (!p.gelu_out || ((p.ldg % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.gelu_out) & 15) == 0)));
+        const bool vec_ok = tc_vec_ok(p);
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
             const int buf = tcount & 1;
@@ -262,10 +264,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // arrivals to both CTAs; both CTAs' epilogue warps release the accumulator on the leader's barrier.
 // ------------------------------------------------------------------------------------------
 constexpr int TC2_STAGES = 6;
+constexpr uint32_t TC2_OUT_BOX_BYTES = 32 * 64 * 2;      // one staged output box: 32 rows x 64 fp16 columns
+constexpr uint32_t TC2_OUT_BYTES = 4 * 2 * TC2_OUT_BOX_BYTES;   // two boxes for each of the four epilogue warps
 
-template <bool A_MN, bool B_MN>
+// Staged epilogue (STAGED = true; outputs without residual / GELU side output and a TMA-compatible C):
+// every epilogue warp converts 32 rows x 64 columns of its accumulator quarter to fp16 (+ bias), writes
+// them into a 128-byte-swizzled box of shared memory and hands the box to the TMA unit, as a tiled
+// store, or -- when the GEMM accumulates into C (weight gradients over micro-batches) -- as a tiled
+// reduction that adds the box to global memory at the memory side.  The SM therefore never reads C,
+// writes leave as full 128-byte rows, and tensor memory is released as soon as the accumulator has
+// been read, before the stores drain.
+template <bool A_MN, bool B_MN, bool STAGED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, TcParams p) {
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_c, TcParams p) {
     constexpr int BN = 256;                              // pair tile: 256 (M) x 256 (N)
     constexpr uint32_t A_BYTES = 128 * TC_BK * 2;        // this CTA's 128 rows of A
     constexpr uint32_t B_BYTES = 128 * TC_BK * 2;        // this CTA's 128 of the 256 B rows
@@ -275,7 +287,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + TC2_STAGES * STAGE_BYTES);
+    unsigned char* out_boxes = tiles + TC2_STAGES * STAGE_BYTES;     // 1024-byte aligned: the swizzle pattern follows the address
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(out_boxes + (STAGED ? TC2_OUT_BYTES : 0));
     uint64_t* empty_bar = full_bar + TC2_STAGES;
     uint64_t* tmem_full = empty_bar + TC2_STAGES;
     uint64_t* tmem_empty = tmem_full + 2;
@@ -299,6 +312,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         fence_barrier_init();
         prefetch_tensormap(&tmap_a);
         prefetch_tensormap(&tmap_b);
+        if (STAGED) prefetch_tensormap(&tmap_c);
     }
     if (warp == 1) {
         tmem_alloc_pair(tmem_base_smem, TMEM_COLS);
@@ -378,25 +392,92 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int quarter = warp & 3;
         uint32_t tcount = 0;
         bool ok = true;
-        const bool vec_ok = tc_vec_ok(p);
-        for (int tile = pair; tile < num_tiles && ok; tile += npairs, tcount++) {
-            const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            const int buf = tcount & 1;
-            ok = mbar_wait(&tmem_full[buf], (tcount >> 1) & 1);
-            if (!ok) break;
-            tcgen05_fence_after();
-            const int row = tm * 256 + (int)rank * 128 + quarter * 32 + lane;
-            const bool row_ok = row < p.m;
+        if constexpr (!STAGED) {
+            const bool vec_ok = tc_vec_ok(p);
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs, tcount++) {
+                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                const int buf = tcount & 1;
+                ok = mbar_wait(&tmem_full[buf], (tcount >> 1) & 1);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const int row = tm * 256 + (int)rank * 128 + quarter * 32 + lane;
+                const bool row_ok = row < p.m;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, v);
-                tmem_ld_wait();
-                tc_store_chunk(p, v, row, row_ok, tn * BN + c0, vec_ok);
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, v);
+                    tmem_ld_wait();
+                    tc_store_chunk(p, v, row, row_ok, tn * BN + c0, vec_ok);
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_leader(&tmem_empty[buf]);
             }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_leader(&tmem_empty[buf]);
+        } else {
+            unsigned char* my_boxes = out_boxes + quarter * (2 * TC2_OUT_BOX_BYTES);
+            const bool bias_vec = p.bias && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
+            uint32_t nbox = 0;                       // boxes handed to the TMA unit so far by this warp
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs, tcount++) {
+                const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                const int buf = tcount & 1;
+                ok = mbar_wait(&tmem_full[buf], (tcount >> 1) & 1);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const int row0 = tm * 256 + (int)rank * 128 + quarter * 32;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+                for (int g = 0; g < BN / 64; g++) {
+                    uint32_t v[64];
+                    tmem_ld_32x32b_x32(taddr + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+                    tmem_ld_32x32b_x32(taddr + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+                    tmem_ld_wait();
+                    if (g == BN / 64 - 1) {          // the accumulator is in registers: the issuer may refill it
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_leader(&tmem_empty[buf]);
+                    }
+                    const int col0 = tn * BN + g * 64;
+                    if (row0 >= p.m || col0 >= p.n) continue;          // box entirely outside C (uniform over the warp)
+                    unsigned char* box = my_boxes + (nbox & 1) * TC2_OUT_BOX_BYTES;
+                    if (nbox >= 2) {                 // the box used two stores ago must have been read out
+                        if (lane == 0) bulk_wait_read<1>();
+                        __syncwarp();
+                    }
+#pragma unroll
+                    for (int q = 0; q < 8; q++) {
+                        float f[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) f[e] = __uint_as_float(v[q * 8 + e]);
+                        if (p.bias) {
+                            const int c = col0 + q * 8;
+                            if (bias_vec && c + 8 <= p.n) {
+                                Vec<__half> b;
+                                b.load(p.bias + c);
+#pragma unroll
+                                for (int e = 0; e < 8; e++) f[e] += b.v[e];
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; e++)
+                                    if (c + e < p.n) f[e] += __half2float(p.bias[c + e]);
+                            }
+                        }
+                        Vec<__half> o;
+#pragma unroll
+                        for (int e = 0; e < 8; e++) o.v[e] = f[e];
+                        // 128-byte swizzle: 16-byte chunk q of row r lives at chunk q ^ (r & 7)
+                        *reinterpret_cast<uint4*>(box + lane * 128 + ((q ^ (lane & 7)) << 4)) = o.pack();
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (p.accumulate) tma_reduce_add_2d(&tmap_c, box, col0, row0);
+                        else tma_store_2d(&tmap_c, box, col0, row0);
+                        bulk_commit();
+                    }
+                    nbox++;
+                }
+            }
+            if (lane == 0) bulk_wait_all();
         }
         if (!ok && lane == 0) atomicExch(&g_tc_error, 6);
     }
@@ -464,13 +545,13 @@ static int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUt
     return launch_tc<BN, true, true>(ta, tb, p, st);
 }
 
-template <bool A_MN, bool B_MN>
-static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p, cudaStream_t st) {
-    constexpr size_t smem = 1024 + (size_t)TC2_STAGES * (2 * 128 * TC_BK * 2) + 256;
+template <bool A_MN, bool B_MN, bool STAGED>
+static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const TcParams& p, cudaStream_t st) {
+    constexpr size_t smem = 1024 + (size_t)TC2_STAGES * (2 * 128 * TC_BK * 2) + (STAGED ? TC2_OUT_BYTES : 0) + 256;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(gemm_tc_pair_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_err = cudaFuncSetAttribute(gemm_tc_pair_kernel<A_MN, B_MN, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     });
     if (attr_err != cudaSuccess) {
         set_cuda_error(attr_err, "gemm_tc_pair smem attribute");
@@ -491,7 +572,7 @@ static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const Tc
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<A_MN, B_MN>, ta, tb, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<A_MN, B_MN, STAGED>, ta, tb, tc, p);
     if (e != cudaSuccess) {
         set_cuda_error(e, "gemm_tc_pair_kernel launch");
         return BRK_CUDA_ERROR;
@@ -499,19 +580,24 @@ static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const Tc
     return launch_status("gemm_tc_pair_kernel");
 }
 
-static int dispatch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p, cudaStream_t st) {
-    if (!a_mn && !b_mn) return launch_tc_pair<false, false>(ta, tb, p, st);
-    if (!a_mn && b_mn) return launch_tc_pair<false, true>(ta, tb, p, st);
-    if (a_mn && !b_mn) return launch_tc_pair<true, false>(ta, tb, p, st);
-    return launch_tc_pair<true, true>(ta, tb, p, st);
+template <bool STAGED>
+static int dispatch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const TcParams& p,
+                         cudaStream_t st) {
+    if (!a_mn && !b_mn) return launch_tc_pair<false, false, STAGED>(ta, tb, tc, p, st);
+    if (!a_mn && b_mn) return launch_tc_pair<false, true, STAGED>(ta, tb, tc, p, st);
+    if (a_mn && !b_mn) return launch_tc_pair<true, false, STAGED>(ta, tb, tc, p, st);
+    return launch_tc_pair<true, true, STAGED>(ta, tb, tc, p, st);
 }
 
 // 0 = choose by shape, 1 = always the single-CTA kernel, 2 = the CTA-pair kernel whenever it applies
 static int g_tc_mode = 0;
+// 0 = staged (TMA store / reduce) epilogue where it applies, 1 = always the direct register epilogue
+static int g_tc_epilogue = 0;
 
 }  // namespace brk
 
 extern "C" void brk_gemm_f16_set_mode(int mode) { brk::g_tc_mode = mode; }
+extern "C" void brk_gemm_f16_set_epilogue(int mode) { brk::g_tc_epilogue = mode; }
 
 extern "C" int brk_gemm_f16_supported(int64_t m, int64_t n, int64_t k, int trans_a, int trans_b, int64_t lda, int64_t ldb,
                                       const void* a, const void* b) {
@@ -566,7 +652,14 @@ extern "C" int brk_gemm_f16(const void* a, const void* b, void* c, int64_t m, in
     cudaStream_t st = (cudaStream_t)stream;
     if (use_pair) {
         p.tiles_m = (int)((m + 255) / 256);
-        return dispatch_pair(a_mn, b_mn, ta, tb, p, st);
+        // outputs that are plain, biased or accumulated leave through shared memory and the TMA unit when C's
+        // layout allows a tensor map; residual / GELU epilogues keep the direct register path
+        CUtensorMap tc;
+        const bool staged = g_tc_epilogue != 1 && !residual && !gelu_out &&
+                            make_tmap_2d_f16(&tc, c, (uint64_t)m, (uint64_t)n, (uint64_t)ldc, 64, 32);
+        if (staged) return dispatch_pair<true>(a_mn, b_mn, ta, tb, tc, p, st);
+        std::memset(&tc, 0, sizeof(tc));
+        return dispatch_pair<false>(a_mn, b_mn, ta, tb, tc, p, st);
     }
     if (bn == 256) return dispatch_major<256>(a_mn, b_mn, ta, tb, p, st);
     return dispatch_major<128>(a_mn, b_mn, ta, tb, p, st);

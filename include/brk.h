@@ -180,7 +180,9 @@ BRK_API int brk_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n
  * follows it (cudnnAddTensor, blackriver/cuda_tensor.cpp:180-188), with the epilogue
  *     out = acc (+ bias[n]) (+ residual[m,n]) (+ C[m,n] when accumulate != 0);  C = fp16(out);
  *     gelu_out = fp16(bloom_gelu(out)) when gelu_out != NULL.
- * Requirements: lda, ldb multiples of 8 elements and a, b 16-byte aligned (TMA); any m, n, k.
+ * Requirements: lda, ldb multiples of 8 elements and a, b 16-byte aligned (TMA); any m, n, k.  bias,
+ * residual, gelu_out and c may have any alignment (16-byte aligned pointers with row strides that are
+ * multiples of 8 take the 128-bit paths, anything else a scalar epilogue).
  * brk_gemm_f16_supported() answers whether a problem meets them (callers fall back to brk_gemm).
  * The kernels bound every internal wait; brk_gemm_f16_status() (synchronous) returns non-zero if
  * one of them gave up since the last query. */
@@ -193,6 +195,11 @@ BRK_API int brk_gemm_f16_status(void);
 /* Kernel selection for measurements: 0 = by shape (default), 1 = single-CTA tiles only, 2 = CTA-pair
  * (cta_group::2, 256 x 256 tiles) whenever m, n > 128. */
 BRK_API void brk_gemm_f16_set_mode(int mode);
+/* Epilogue selection of the CTA-pair kernel, for measurements: 0 (default) = outputs without residual or
+ * GELU side output whose C is 16-byte aligned with ldc a multiple of 8 leave through shared memory as TMA
+ * tiled stores (TMA tiled reductions when accumulate != 0, so C is never read by the SMs: the sum
+ * C + fp16(acc) is then rounded to fp16 at the memory side); 1 = always the register epilogue. */
+BRK_API void brk_gemm_f16_set_epilogue(int mode);
 
 /* ---- fused attention (fp16, tcgen05) ------------------------------------------------------------
  * Replaces the op_qk -> op_add(alibi) -> op_add(xmask) -> op_softmax -> op_attn chain of layer_forward

@@ -35,9 +35,10 @@ def gelu_ref(x):
     return x * 0.5 * (1 + np.tanh(0.79788456 * x * (1 + 0.044715 * x * x)))
 
 
-def run(ops, m, n, k, ta, tb, seed, bias=False, res=False, acc=False, gelu=False, mode=0):
+def run(ops, m, n, k, ta, tb, seed, bias=False, res=False, acc=False, gelu=False, mode=0, epi=0, bias_offset=0):
     from blackriver_b200 import brk
     brk.lib().brk_gemm_f16_set_mode(mode)      # 1 = single-CTA tiles, 2 = CTA-pair (cta_group::2) tiles
+    brk.lib().brk_gemm_f16_set_epilogue(epi)   # 0 = TMA store / reduce epilogue where it applies, 1 = register epilogue
     rng = np.random.default_rng(seed)
     A = h16(rng.standard_normal((k, m) if ta else (m, k)))
     B = h16(rng.standard_normal((n, k) if tb else (k, n)))
@@ -46,10 +47,17 @@ def run(ops, m, n, k, ta, tb, seed, bias=False, res=False, acc=False, gelu=False
     R = h16(rng.standard_normal((m, n))) if res else None
     dev = lambda x: None if x is None else torch.from_numpy(x).cuda()
     C = dev(C0); G = torch.empty_like(C) if gelu else None
-    ops.gemm_f16(dev(A), dev(B), C, m, n, k, ta, tb, A.shape[1], B.shape[1], n, bias=dev(bs), residual=dev(R), ldr=n,
+    dbias = dev(bs)
+    if bias and bias_offset:        # a bias that starts at an element offset inside a larger buffer: not 16-byte aligned
+        pad = torch.zeros(n + bias_offset, dtype=torch.float16, device="cuda")
+        pad[bias_offset:] = dbias
+        dbias = pad[bias_offset:]
+        assert dbias.data_ptr() % 16 != 0
+    ops.gemm_f16(dev(A), dev(B), C, m, n, k, ta, tb, A.shape[1], B.shape[1], n, bias=dbias, residual=dev(R), ldr=n,
                  gelu_out=G, ldg=n, accumulate=acc)
     torch.cuda.synchronize()
     brk.lib().brk_gemm_f16_set_mode(0)
+    brk.lib().brk_gemm_f16_set_epilogue(0)
     assert brk.lib().brk_gemm_f16_status() == 0
     a = (A.T if ta else A).astype(np.float64); b = (B.T if tb else B).astype(np.float64)
     ref = a @ b
@@ -61,14 +69,14 @@ def run(ops, m, n, k, ta, tb, seed, bias=False, res=False, acc=False, gelu=False
         assert relerr(G.float().cpu().numpy(), gelu_ref(ref)) <= TOL16
 
 
-@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("mode,epi", [(1, 0), (2, 0), (2, 1)])
 @pytest.mark.parametrize("ta,tb", [(0, 1), (0, 0), (1, 1), (1, 0)])
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 512, 128), (200, 328, 136), (130, 72, 40), (1, 8, 8), (384, 1000, 264),
                                    (520, 264, 72)])
-def test_all_layouts_and_tails(ops, m, n, k, ta, tb, mode):
+def test_all_layouts_and_tails(ops, m, n, k, ta, tb, mode, epi):
     if (ta and m % 8) or (not tb and n % 8):
         pytest.skip("this storage order needs a leading dimension that is a multiple of 8")
-    run(ops, m, n, k, ta, tb, seed=m + n + k, mode=mode)
+    run(ops, m, n, k, ta, tb, seed=m + n + k, mode=mode, epi=epi)
 
 
 def test_epilogues(ops):
@@ -77,6 +85,40 @@ def test_epilogues(ops):
     run(ops, 256, 512, 128, 1, 0, 3, acc=True)
     run(ops, 200, 328, 136, 0, 1, 4, bias=True, res=True, acc=True, gelu=True)
     run(ops, 200, 328, 136, 0, 1, 4, bias=True, res=True, acc=True, gelu=True, mode=1)
+    # the staged epilogue with tails in both directions: plain, bias, accumulate (TMA reduction), both; and its register twin
+    for epi in (0, 1):
+        run(ops, 520, 328, 136, 1, 0, 5, acc=True, epi=epi)
+        run(ops, 520, 328, 136, 0, 1, 6, bias=True, epi=epi)
+        run(ops, 520, 1000, 72, 0, 0, 7, bias=True, acc=True, epi=epi)
+        run(ops, 304, 264, 72, 1, 1, 8, epi=epi)
+
+
+def test_bias_at_an_odd_element_offset(ops):
+    """A bias vector that is a view at an element offset of a larger buffer (possible through op.view) is not
+    16-byte aligned: every epilogue has to read it with scalar loads."""
+    for mode, epi in ((1, 0), (2, 0), (2, 1)):
+        run(ops, 256, 512, 128, 0, 1, 21, bias=True, mode=mode, epi=epi, bias_offset=1)
+        run(ops, 200, 328, 136, 0, 1, 22, bias=True, res=True, gelu=True, mode=mode, epi=epi, bias_offset=3)
+
+
+def test_sixteen_accumulations_stay_within_tolerance(ops):
+    """Weight gradients are summed over the micro-batches of a step by the GEMM itself (accumulate): 16 different
+    products added into one fp16 C must stay within the fp16 tolerance of the float64 sum, in both epilogues."""
+    from blackriver_b200 import brk
+    m, n, k = 512, 384, 256
+    rng = np.random.default_rng(31)
+    for epi in (0, 1):
+        brk.lib().brk_gemm_f16_set_epilogue(epi)
+        C = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+        ref = np.zeros((m, n), np.float64)
+        for i in range(16):
+            A = h16(rng.standard_normal((k, m))); B = h16(rng.standard_normal((k, n)))
+            ops.gemm_f16(torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), C, m, n, k, 1, 0, m, n, n, accumulate=True)
+            ref += A.T.astype(np.float64) @ B.astype(np.float64)
+        torch.cuda.synchronize()
+        brk.lib().brk_gemm_f16_set_epilogue(0)
+        assert brk.lib().brk_gemm_f16_status() == 0
+        assert relerr(C.float().cpu().numpy(), ref) <= TOL16
 
 
 def test_matches_oracle_linear_and_backward(ops):
