@@ -420,7 +420,8 @@ def run_finetune(args):
         host.collective_boot_local(0, 1)
 
     tr = finetune.Trainer(cfg["hidden"], cfg["heads"], cfg["vocab"], cfg["n_layers"], cfg["batch"], cfg["tokens"], cfg["n_micro"],
-                          rank=rank, world=world, seed=cfg["seed"], logits_rows=cfg["batch"] * cfg["tokens"])
+                          rank=rank, world=world, seed=cfg["seed"], logits_rows=cfg["batch"] * cfg["tokens"],
+                          overlap=not args.no_overlap)
     mbs = finetune.make_microbatches(cfg["n_micro"], cfg["batch"], cfg["tokens"], cfg["vocab"], cfg["min_len"], cfg["seed"])
     tokens_per_step = cfg["n_micro"] * cfg["batch"] * cfg["tokens"]
     valid_per_step = int(sum(int(m[2].sum()) for m in mbs))
@@ -480,13 +481,21 @@ def run_finetune(args):
         dist.broadcast_object_list(box, src=world - 1)
         loss = box[0]
 
+    if world == 1:
+        schedule_name = "forward + backward per micro-batch"
+    elif tr.overlap:
+        schedule_name = ("static forward / input-gradient / weight-gradient task lists per rank (greedy, simulated efficiency %.2f), "
+                         "one-sided hand-offs on transfer streams" % tr.simulated_efficiency)
+    else:
+        schedule_name = "all forwards then all backwards, NCCL send / receive on the compute stream"
     if rank == 0:
         ms_per_step = ms_total / args.steps
         value = tokens_per_step / (ms_per_step * 1e-3)
         e2e_value = tokens_per_step / (ms_e2e / e2e_steps * 1e-3)
-        feeds = 1 if world == 1 else 2
-        h2d = feeds * sum(m[0].nbytes + m[1].nbytes + m[2].nbytes for m in mbs)
-        d2h = cfg["n_micro"] * 8
+        # every forward and input-gradient task copies its micro-batch's ids / mask / lengths host -> device; before the
+        # optimizer the losses and the two kernel status words are read back
+        h2d = sum(finetune.pack_inputs(mbs[k]).nbytes for _, k in tr.tasks if k is not None)
+        d2h = cfg["n_micro"] * 4 + 8
         peak_tf, peak_src = load_tensor_peak()
         my_layers = tr.counts[0]
         flops = cfg["n_micro"] * finetune.gemm_flops_per_microbatch(cfg["hidden"], cfg["vocab"], my_layers, cfg["batch"] * cfg["tokens"],
@@ -502,7 +511,7 @@ def run_finetune(args):
             "data": "synthetic",
             "config": {"workload": FT_WORKLOAD, "layers": cfg["n_layers"], "micro_batches": cfg["n_micro"],
                        "tokens_per_step": tokens_per_step, "valid_tokens_per_step": valid_per_step,
-                       "parallelism": "pp%d" % world, "stage_layers": tr.counts, "schedule": "all-forward-all-backward over micro-batch slots",
+                       "parallelism": "pp%d" % world, "stage_layers": tr.counts, "schedule": schedule_name, "slots": tr.n_slots,
                        "l2": "inputs larger than L2: per step every kernel streams >= 14 GB of weights and activations between re-uses"},
             "clocks": clocks, "gpu_launches": launches * args.steps,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -783,6 +792,8 @@ def main():
     ap.add_argument("--workload", default="finetune", choices=["finetune", "ops"])
     ap.add_argument("--layers", type=int, default=0, help="fine-tune workload with fewer layers (development aid)")
     ap.add_argument("--micro", type=int, default=0, help="fine-tune workload with fewer micro-batches (development aid)")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="multi-GPU: the plain schedule (all forwards, all backwards, NCCL hand-offs) instead of the overlapped one")
     ap.add_argument("--skip-ops", action="store_true", help="do not run the operator microbench before the fine-tune step")
     ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "gemm_dw", "attn"],
                     help="profiling aid: run a few launches of one kernel family on a small case and exit")

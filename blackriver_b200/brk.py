@@ -39,7 +39,10 @@ SIGNATURES = {
     "brk_gelu_bwd": (i32, [p, p, p, i64, i32, p]),
     "brk_logsoftmax_nll_fwd": (i32, [p, p, p, p, i64, i64, i32, p]),
     "brk_logsoftmax_nll_fwd_bwd": (i32, [p, p, p, p, i64, i64, f32, i32, p]),
+    "brk_logsoftmax_nll_fwd_bwd_counted": (i32, [p, p, p, p, i64, i64, f32, p, i32, p]),
     "brk_sum_f32": (i32, [p, p, i64, p]),
+    "brk_sum_div_f32": (i32, [p, p, p, i64, p]),
+    "brk_signal_u32": (i32, [p, C.c_uint32, p]),
     "brk_loss_targets": (i32, [p, p, p, p, i32, i32, p]),
     "brk_add_bcast": (i32, [p, p, p, C.POINTER(i64), C.POINTER(i64), i32, p]),
     "brk_fill": (i32, [p, f32, i64, i32, p]),

@@ -135,6 +135,51 @@ int brh_env_tensor_read(void* env, const char* name, void* host, size_t bytes) {
     });
 }
 
+// Asynchronous host -> device write: the bytes are copied out of `host` into a pinned ring before the call returns and
+// travel on the compute stream from there.  The ring is cut into quarters; entering a quarter waits (on the host) for
+// the copies queued from it one lap earlier.
+namespace {
+constexpr size_t STAGE_BYTES = (size_t)16 << 20;
+constexpr size_t STAGE_QUARTER = STAGE_BYTES / 4;
+unsigned char* g_stage = nullptr;
+size_t g_stage_head = 0;
+cudaEvent_t g_stage_done[4] = {nullptr, nullptr, nullptr, nullptr};
+bool g_stage_used[4] = {false, false, false, false};
+
+unsigned char* stage_take(size_t bytes) {
+    br_assert(bytes <= STAGE_QUARTER, "asynchronous tensor writes are limited to 4 MiB each");
+    if (!g_stage) {
+        BR_CUDA_CHECK(cudaMallocHost(&g_stage, STAGE_BYTES));
+        for (auto& e : g_stage_done) BR_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    size_t q = g_stage_head / STAGE_QUARTER;
+    if (g_stage_head + bytes > (q + 1) * STAGE_QUARTER) {      // does not fit the rest of this quarter: move on
+        BR_CUDA_CHECK(cudaEventRecord(g_stage_done[q], ComputingContext::cuda_stream));
+        g_stage_used[q] = true;
+        q = (q + 1) % 4;
+        g_stage_head = q * STAGE_QUARTER;
+        if (g_stage_used[q]) BR_CUDA_CHECK(cudaEventSynchronize(g_stage_done[q]));
+    }
+    unsigned char* p = g_stage + g_stage_head;
+    g_stage_head += (bytes + 63) / 64 * 64;
+    return p;
+}
+}  // namespace
+
+int brh_env_tensor_write_async(void* env, const char* name, const void* host, size_t bytes) {
+    return guarded([&] {
+        tensor_t t = ENV->hash().find_tensor(name);
+        br_assert(bytes == t->bytes(), "byte count does not match the tensor");
+        if (t->is_cuda()) {
+            unsigned char* staged = stage_take(bytes);
+            std::memcpy(staged, host, bytes);
+            BR_CUDA_CHECK(cudaMemcpyAsync(t->data(), staged, bytes, cudaMemcpyHostToDevice, ComputingContext::cuda_stream));
+        } else {
+            std::memcpy(t->data(), host, bytes);
+        }
+    });
+}
+
 int brh_profile_start(void) { return guarded([] { Profiler::start(); }); }
 int brh_profile_stop(char* out, size_t cap) {
     return guarded([&] {

@@ -22,7 +22,8 @@ namespace br {
 struct ComputingContext {
     static int cuda_device;
     static cudaStream_t cuda_stream;   // compute
-    static cudaStream_t comm_stream;   // NCCL send/recv and staged host transfers
+    static cudaStream_t comm_stream;   // staged host transfers
+    static cudaStream_t link_stream[2];   // stage hand-offs of PipeLinks: [0] towards the previous rank, [1] towards the next
     static cudaEvent_t compute_done;   // recorded on cuda_stream before a send reads a tensor
     static cudaEvent_t comm_done;      // recorded on comm_stream after a recv wrote a tensor
 
@@ -72,6 +73,41 @@ struct CollectiveContext {
     static ncclUniqueId make_unique_id();
     static void shutdown();
     static int now();  // whole seconds since boot, as the reference's echo prints
+};
+
+// One-sided stage hand-offs between neighbouring pipeline ranks of one node, replacing ncclSend / ncclRecv on the
+// compute stream (blackriver/cuda_tensor.cpp:75-96) where transfers have to overlap compute.
+//
+// Every rank owns one device block, exported to its two neighbours through CUDA IPC:
+//   * windows [2 sides][slots][slot_bytes]: side 0 is written by the previous rank (activations going forward),
+//     side 1 by the next rank (gradients going backward); a slot is one micro-batch in flight;
+//   * arrive[side][slot]: how many times that window has been filled (written by the sender after its copy);
+//   * ack[dir][slot]: how many of this rank's sends in direction dir (1 = to the next rank, 0 = to the previous one)
+//     the receiver has finished reading (written by the receiver).
+// A send is a device-to-device copy into the neighbour's window on a transfer stream of its own (the copy engines
+// move it; no SM runs a communication kernel) followed by a one-thread kernel that raises arrive; the consumer's
+// compute stream waits for the counter with a stream memory operation (cuStreamWaitValue32), so no kernel spins
+// either.  A sender never waits for its receiver except when it is about to overwrite a window the receiver has
+// not released yet.  With one rank the block is its own neighbour in both directions (loop-back).
+struct PipeLinks {
+    static constexpr int MAX_SLOTS = 64;
+    static bool is_open;
+    static int slots;
+    static size_t slot_bytes;
+
+    // Collective over all ranks of the communicator.  Throws if CUDA IPC or stream memory operations are unavailable.
+    static void open(size_t slot_bytes, int slots);
+    // A single-rank process may play `ranks` pipeline ranks itself (tests on one GPU): called before open, it makes
+    // open create one block per played rank, chained like real neighbours; select says whose turn it is.
+    static void emulate(int ranks);
+    static void select(int rank);
+    static void close();
+    static void* window(int side, int slot);                 // this rank's own window
+    // queue: [after everything on the compute stream so far] copy `bytes` from src into the neighbour's window, raise arrive
+    static void send(int dir, int slot, const void* src, size_t bytes);
+    static void fence(int dir);                              // compute stream waits for the last copy queued in direction dir
+    static void wait(int side, int slot);                    // compute stream waits for the next filling of window (side, slot)
+    static void release(int side, int slot);                 // after the compute stream's work so far: the sender may overwrite it
 };
 
 struct MemoryContext {

@@ -63,6 +63,14 @@ struct Scratch {
     }
 };
 
+// int32 tensor -> device pointer; host tensors are staged through `scratch`
+inline const int32_t* int_on_device(const tensor_t& t, Scratch& sc) {
+    if (t->is_cuda()) return (const int32_t*)t->data();
+    int32_t* d = (int32_t*)sc.take(t->bytes());
+    BR_CUDA_CHECK(cudaMemcpyAsync(d, t->data(), t->bytes(), cudaMemcpyHostToDevice, stream()));
+    return d;
+}
+
 // One GEMM, routed to the tensor-core kernel when the element type is fp16 and the layout meets
 // TMA's rules (single problem, alpha 1, beta 0 or 1), otherwise to the general SIMT kernel.
 template <DataType DT>
@@ -139,7 +147,8 @@ ComputingReturn CUDATensor<DT>::io_save(tensor_t self, const char* fileName) {
 }
 
 // Stage hand-off on the compute stream, in program order with the kernels around it
-// (blackriver/cuda_tensor.cpp:75-96); the pipelined driver uses the asynchronous words instead.
+// (blackriver/cuda_tensor.cpp:75-96).  The overlapped pipeline does not use these: it moves activations and
+// gradients with the one-sided io.link.* words (PipeLinks), which never occupy the compute stream.
 template <DataType DT>
 ComputingReturn CUDATensor<DT>::io_nccl_send(tensor_t self, int dst) {
     if (!CollectiveContext::has_comm) return OP_ATTR_ERROR;
@@ -390,6 +399,64 @@ LossReturn CUDATensor<DT>::op_loss_backward(tensor_t self, tensor_t ids_, tensor
     return loss;
 }
 
+// op_loss_backward queued without a host round trip (the reference synchronises twice per group of rows,
+// blackriver/cuda_tensor.cpp:569-577 and 686-691): the number of counted positions stays on the device, the gradient
+// factor loss_scale / items is formed inside the log-softmax kernel and the mean loss is left in loss_out[0].
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_loss_backward_async(tensor_t self, tensor_t ids_, tensor_t mask_, tensor_t lm_head, tensor_t all_logits,
+                                                       tensor_t x_g, tensor_t lm_head_g, tensor_t loss_out, int defer_weight) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (self->shape().dim() != 3 || !dev_ok<DT>({lm_head, all_logits})) return OP_INPUT_ERROR;
+    if (!ids_ || !mask_ || ids_->dtype() != DataType::Int || mask_->dtype() != DataType::Int) return OP_INPUT_ERROR;
+    if (!dev_ok<DT>({x_g, lm_head_g}) || x_g->items() != self->items() || lm_head_g->items() != lm_head->items()) return OP_OUTPUT_ERROR;
+    if (!dev_ok<DataType::Float>({loss_out}) || loss_out->items() < 1) return OP_OUTPUT_ERROR;
+    const int batch = (int)self->shape()[0], tokens = (int)self->shape()[1];
+    const int64_t hidden = self->shape()[2], vocab = lm_head->shape()[0];
+    const int64_t n = (int64_t)batch * tokens;
+    if ((int64_t)ids_->items() < n || (int64_t)mask_->items() < n) return OP_INPUT_ERROR;
+    const int64_t band = std::min<int64_t>((int64_t)all_logits->items() / vocab, n);
+    if (band < 1 || (defer_weight && band < n)) return OP_ATTR_ERROR;
+    constexpr int dt = brk_dtype<DT>();
+    const size_t es = DataType_size(DT);
+
+    Scratch sc;
+    const int32_t* d_ids = int_on_device(ids_, sc);
+    const int32_t* d_mask = int_on_device(mask_, sc);
+    int32_t* d_target = (int32_t*)sc.take(n * 4);
+    int32_t* d_count = (int32_t*)sc.take(4);
+    float* d_rowloss = (float*)sc.take(n * 4);
+    int st = brk_loss_targets(d_ids, d_mask, d_target, d_count, batch, tokens, sptr());
+    void* logits = all_logits->data();
+    for (int64_t r0 = 0; r0 < n && st == BRK_OK; r0 += band) {
+        const int64_t rows = std::min(band, n - r0);
+        const unsigned char* x = (const unsigned char*)mem_ + r0 * hidden * es;
+        unsigned char* dx = (unsigned char*)x_g->data() + r0 * hidden * es;
+        st = gemm_any<DT>(x, lm_head->data(), logits, rows, vocab, hidden, 0, 1, hidden, hidden, vocab, 0.0f, nullptr);
+        if (st == BRK_OK) {
+            ProfScope prof("nll_fwd_bwd");
+            st = brk_logsoftmax_nll_fwd_bwd_counted(logits, d_target + r0, d_rowloss + r0, logits, rows, vocab, ComputingContext::loss_scale,
+                                                    d_count, dt, sptr());
+        }
+        if (st == BRK_OK) st = gemm_any<DT>(logits, lm_head->data(), dx, rows, hidden, vocab, 0, 0, vocab, hidden, hidden, 0.0f, nullptr);
+        if (st == BRK_OK && !defer_weight)
+            st = gemm_any<DT>(logits, x, lm_head_g->data(), vocab, hidden, rows, 1, 0, vocab, hidden, hidden, 1.0f, nullptr);
+    }
+    if (st == BRK_OK) st = brk_sum_div_f32(d_rowloss, d_count, (float*)loss_out->data(), n, sptr());
+    return ret(st);
+}
+
+// lm_head_g += dlogits^T x, the weight-gradient GEMM that op_loss_backward_async left out
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_loss_backward_w(tensor_t self, tensor_t x, tensor_t lm_head_g) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (!dev_ok<DT>({x}) || x->shape().dim() != 3) return OP_INPUT_ERROR;
+    if (!dev_ok<DT>({lm_head_g}) || lm_head_g->shape().dim() != 2) return OP_OUTPUT_ERROR;
+    const int64_t n = (int64_t)(x->shape()[0] * x->shape()[1]), hidden = x->shape()[2];
+    const int64_t vocab = lm_head_g->shape()[0];
+    if ((int64_t)lm_head_g->shape()[1] != hidden || (int64_t)self->items() < n * vocab) return OP_INPUT_ERROR;
+    return ret(gemm_any<DT>(mem_, x->data(), lm_head_g->data(), vocab, hidden, n, 1, 0, vocab, hidden, hidden, 1.0f, nullptr));
+}
+
 // Forward-only scoring over the LM head (no counterpart in the reference, whose only inference hook is op_last_logits):
 // the same banded logits GEMM and target rule as op_loss_backward, row losses only.
 template <DataType DT>
@@ -470,6 +537,36 @@ ComputingReturn CUDATensor<DT>::op_linear_backward(tensor_t self, tensor_t x, te
     { ProfScope prof("colsum"); st = brk_colsum_ws(mem_, bias_g->data(), n, out, acc, dt, ComputingContext::cuda_workspace, ComputingContext::workspace_size, sptr()); }
     if (st == BRK_OK) st = gemm_any<DT>(mem_, x->data(), weight_g->data(), out, in, n, 1, 0, out, in, in, acc ? 1.0f : 0.0f, nullptr);
     if (st == BRK_OK) st = gemm_any<DT>(mem_, weight->data(), x_g->data(), n, in, out, 0, 0, out, in, in, 0.0f, nullptr);
+    return ret(st);
+}
+
+// x_g = dy W alone: the part of op_linear_backward that the previous pipeline stage waits for
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_linear_backward_x(tensor_t self, tensor_t weight, tensor_t x_g) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (!dev_ok<DT>({weight}) || weight->shape().dim() != 2) return OP_INPUT_ERROR;
+    int64_t out = (int64_t)weight->shape()[0], in = (int64_t)weight->shape()[1];
+    if (self->items() % out != 0) return OP_INPUT_ERROR;
+    int64_t n = (int64_t)self->items() / out;
+    if (!dev_ok<DT>({x_g}) || (int64_t)x_g->items() != n * in) return OP_OUTPUT_ERROR;
+    return ret(gemm_any<DT>(mem_, weight->data(), x_g->data(), n, in, out, 0, 0, out, in, in, 0.0f, nullptr));
+}
+
+// b_g = sum_n dy ; W_g = dy^T x: the part nothing downstream waits for (it can run any time before the optimizer)
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_linear_backward_w(tensor_t self, tensor_t x, tensor_t weight_g, tensor_t bias_g) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (!dev_ok<DT>({x})) return OP_INPUT_ERROR;
+    if (!dev_ok<DT>({weight_g, bias_g}) || weight_g->shape().dim() != 2) return OP_OUTPUT_ERROR;
+    int64_t out = (int64_t)weight_g->shape()[0], in = (int64_t)weight_g->shape()[1];
+    if (self->items() % out != 0 || (int64_t)bias_g->items() != out) return OP_INPUT_ERROR;
+    int64_t n = (int64_t)self->items() / out;
+    if ((int64_t)x->items() != n * in) return OP_INPUT_ERROR;
+    constexpr int dt = brk_dtype<DT>();
+    const int acc = ComputingContext::grad_accumulate;
+    int st;
+    { ProfScope prof("colsum"); st = brk_colsum_ws(mem_, bias_g->data(), n, out, acc, dt, ComputingContext::cuda_workspace, ComputingContext::workspace_size, sptr()); }
+    if (st == BRK_OK) st = gemm_any<DT>(mem_, x->data(), weight_g->data(), out, in, n, 1, 0, out, in, in, acc ? 1.0f : 0.0f, nullptr);
     return ret(st);
 }
 
@@ -567,14 +664,6 @@ const float* device_slopes(int heads) {
     BR_CUDA_CHECK(cudaMemcpyAsync(d, sf.data(), heads * sizeof(float), cudaMemcpyHostToDevice, stream()));
     BR_CUDA_CHECK(cudaStreamSynchronize(stream()));
     cache.emplace_back(heads, d);
-    return d;
-}
-
-// int32 tensor -> device pointer; host tensors are staged through `scratch`
-const int32_t* int_on_device(const tensor_t& t, Scratch& sc) {
-    if (t->is_cuda()) return (const int32_t*)t->data();
-    int32_t* d = (int32_t*)sc.take(t->bytes());
-    BR_CUDA_CHECK(cudaMemcpyAsync(d, t->data(), t->bytes(), cudaMemcpyHostToDevice, stream()));
     return d;
 }
 

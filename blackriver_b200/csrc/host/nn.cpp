@@ -2,7 +2,9 @@
 
 #include <array>
 
+#include "brk.h"
 #include "context.hpp"
+#include "cuda_tensor.hpp"
 #include "tensortype.hpp"
 
 namespace br {
@@ -34,6 +36,7 @@ BR_WORD(Sync, {
     if (ComputingContext::booted) {
         BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::cuda_stream));
         BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::comm_stream));
+        for (int d = 0; d < 2; d++) BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::link_stream[d]));
     }
 })
 
@@ -261,6 +264,87 @@ BR_WORD(Verbose, { ComputingContext::verbose = stack.pop_number() != 0.0 ? 1 : 0
 // ( -- loss )  value of the most recent op.loss_backward
 BR_WORD(LastLoss, { stack.push_number((double)g_last_loss); })
 
+// ( dy w x_g -- )  first half of op.linear_backward
+BR_WORD(LinearBackwardX, {
+    auto t = pop_tensors<3>(stack);
+    t[0]->op_linear_backward_x(t[0], t[1], t[2]);
+})
+// ( dy x w_g b_g -- )  second half of op.linear_backward
+BR_WORD(LinearBackwardW, {
+    auto t = pop_tensors<4>(stack);
+    t[0]->op_linear_backward_w(t[0], t[1], t[2], t[3]);
+})
+// ( x ids mask lm_head workspace x_g lm_head_g loss_out defer -- )  op.loss_backward without a host round trip
+BR_WORD(LossBackwardAsync, {
+    int defer = (int)stack.pop_number();
+    auto t = pop_tensors<8>(stack);
+    t[0]->op_loss_backward_async(t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7], defer);
+})
+// ( workspace x lm_head_g -- )  the LM-head weight gradient a deferring op.loss_backward_async left out
+BR_WORD(LossBackwardW, {
+    auto t = pop_tensors<3>(stack);
+    t[0]->op_loss_backward_w(t[0], t[1], t[2]);
+})
+// ( -- code )  waits for the device; 0 when no tensor-core kernel gave up a bounded wait since the last query,
+// else 16 * (GEMM status) + (attention status)
+BR_WORD(KernelStatus, {
+    int code = 0;
+    if (ComputingContext::booted) {
+        BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::cuda_stream));
+        code = 16 * brk_gemm_f16_status() + brk_flash_attn_status();
+    }
+    stack.push_number((double)code);
+})
+
+// ---- one-sided stage hand-offs (PipeLinks) ----
+// ( bytes_per_slot slots -- )  collective over all ranks
+BR_WORD(LinkOpen, {
+    int slots = (int)stack.pop_number();
+    size_t bytes = (size_t)stack.pop_number();
+    PipeLinks::open(bytes, slots);
+})
+BR_WORD(LinkClose, { (void)stack; PipeLinks::close(); })
+// ( ranks -- )  before io.link.open, single-rank process only: play that many pipeline ranks in this process
+BR_WORD(LinkEmulate, { PipeLinks::emulate((int)stack.pop_number()); })
+// ( rank -- )  the played rank the following io.link words act for
+BR_WORD(LinkRank, { PipeLinks::select((int)stack.pop_number()); })
+// ( side slot d1 .. dn n dtype -- t )  this rank's window as a tensor; side 0 = from the previous rank, 1 = from the next
+BR_WORD(LinkWindow, {
+    std::string dtype = stack.pop_string();
+    auto shape = pop_shape(stack);
+    int slot = (int)stack.pop_number();
+    int side = (int)stack.pop_number();
+    ShapeType s(shape);
+    void* mem = PipeLinks::window(side, slot);
+    tensor_t t;
+    if (dtype == "half") t = std::make_shared<TensorType>(new CUDATensor<DataType::F16>(mem), s);
+    else if (dtype == "float") t = std::make_shared<TensorType>(new CUDATensor<DataType::Float>(mem), s);
+    else br_panic("io.link.window: dtype must be half or float");
+    br_assert(t->bytes() <= PipeLinks::slot_bytes, "io.link.window: the shape does not fit a window");
+    stack.push_tensor(t);
+})
+// ( t dir slot -- )  dir 1 = to the next rank, 0 = to the previous rank
+BR_WORD(LinkSend, {
+    int slot = (int)stack.pop_number();
+    int dir = (int)stack.pop_number();
+    tensor_t t = stack.pop_tensor();
+    br_assert(t->is_cuda(), "io.link.send moves device tensors");
+    PipeLinks::send(dir, slot, t->data(), t->bytes());
+})
+// ( dir -- )  the compute stream waits until the last tensor sent in that direction has left its buffer
+BR_WORD(LinkFence, { PipeLinks::fence((int)stack.pop_number()); })
+// ( side slot -- )
+BR_WORD(LinkWait, {
+    int slot = (int)stack.pop_number();
+    int side = (int)stack.pop_number();
+    PipeLinks::wait(side, slot);
+})
+BR_WORD(LinkRelease, {
+    int slot = (int)stack.pop_number();
+    int side = (int)stack.pop_number();
+    PipeLinks::release(side, slot);
+})
+
 BR_WORD(IoDump, {
     tensor_t t = stack.pop_tensor();
     t->io_dump(t);
@@ -334,6 +418,21 @@ void load_nn_words(Enviroment& env) {
     env.insert_native_word("op.loss_scale", LossScale::creator);
     env.insert_native_word("op.last_loss", LastLoss::creator);
     env.insert_native_word("op.verbose", Verbose::creator);
+
+    env.insert_native_word("op.linear_backward_x", LinearBackwardX::creator);
+    env.insert_native_word("op.linear_backward_w", LinearBackwardW::creator);
+    env.insert_native_word("op.loss_backward_async", LossBackwardAsync::creator);
+    env.insert_native_word("op.loss_backward_w", LossBackwardW::creator);
+    env.insert_native_word("op.kernel_status", KernelStatus::creator);
+    env.insert_native_word("io.link.open", LinkOpen::creator);
+    env.insert_native_word("io.link.close", LinkClose::creator);
+    env.insert_native_word("io.link.emulate", LinkEmulate::creator);
+    env.insert_native_word("io.link.rank", LinkRank::creator);
+    env.insert_native_word("io.link.window", LinkWindow::creator);
+    env.insert_native_word("io.link.send", LinkSend::creator);
+    env.insert_native_word("io.link.fence", LinkFence::creator);
+    env.insert_native_word("io.link.wait", LinkWait::creator);
+    env.insert_native_word("io.link.release", LinkRelease::creator);
 
     env.insert_native_word("op.sync", Sync::creator);
     env.insert_native_word("op.create", Create::creator);

@@ -107,6 +107,19 @@ struct TransformerComputing {
     virtual LossReturn op_token_nll(tensor_t self, tensor_t ids, tensor_t mask, tensor_t lm_head, tensor_t all_logits, tensor_t out) {
         return OP_TODO_ERROR;
     }
+    // The two halves of op_linear_backward, so that a pipeline stage can hand x_g to its predecessor before it spends
+    // time on its own weight gradients: self = dy ; x_g = dy W (overwritten)
+    virtual ComputingReturn op_linear_backward_x(tensor_t self, tensor_t weight, tensor_t x_g) { return OP_TODO_ERROR; }
+    // self = dy ; b_g = sum_n dy ; W_g = dy^T x (overwritten, or added to under op.accumulate)
+    virtual ComputingReturn op_linear_backward_w(tensor_t self, tensor_t x, tensor_t weight_g, tensor_t bias_g) { return OP_TODO_ERROR; }
+    // op_loss_backward without a host round trip: the 1/items factor is formed on the device and the mean loss goes to
+    // loss_out[0] (device fp32) instead of being returned.  With defer_weight != 0 (needs a logits band covering every
+    // row) the LM-head weight gradient is left out; op_loss_backward_w adds it later from the band, which then still
+    // holds the logits' gradient.
+    virtual ComputingReturn op_loss_backward_async(tensor_t self, tensor_t ids, tensor_t mask, tensor_t lm_head, tensor_t all_logits,
+                                                   tensor_t x_g, tensor_t lm_head_g, tensor_t loss_out, int defer_weight) { return OP_TODO_ERROR; }
+    // self = the band holding dlogits [rows, vocab] ; lm_head_g += dlogits^T x
+    virtual ComputingReturn op_loss_backward_w(tensor_t self, tensor_t x, tensor_t lm_head_g) { return OP_TODO_ERROR; }
 };
 
 }  // namespace br

@@ -236,6 +236,27 @@ ComputingReturn TensorType::io_nccl_sendrecv(tensor_t self, tensor_t recv, int p
     op_check(r, "nccl_sendrecv");
 }
 
+ComputingReturn TensorType::op_linear_backward_x(tensor_t self, tensor_t weight, tensor_t x_g) {
+    SELF_CHECK();
+    auto r = impl_->op_linear_backward_x(self, weight, x_g);
+    op_check(r, "linear_backward_x");
+}
+ComputingReturn TensorType::op_linear_backward_w(tensor_t self, tensor_t x, tensor_t weight_g, tensor_t bias_g) {
+    SELF_CHECK();
+    auto r = impl_->op_linear_backward_w(self, x, weight_g, bias_g);
+    op_check(r, "linear_backward_w");
+}
+ComputingReturn TensorType::op_loss_backward_async(tensor_t self, tensor_t ids, tensor_t mask, tensor_t lm_head, tensor_t all_logits, tensor_t x_g, tensor_t lm_head_g, tensor_t loss_out, int defer_weight) {
+    SELF_CHECK();
+    auto r = impl_->op_loss_backward_async(self, ids, mask, lm_head, all_logits, x_g, lm_head_g, loss_out, defer_weight);
+    op_check(r, "loss_backward_async");
+}
+ComputingReturn TensorType::op_loss_backward_w(tensor_t self, tensor_t x, tensor_t lm_head_g) {
+    SELF_CHECK();
+    auto r = impl_->op_loss_backward_w(self, x, lm_head_g);
+    op_check(r, "loss_backward_w");
+}
+
 ComputingReturn TensorType::io_load(tensor_t self, const char* fileName) {
     SELF_CHECK();
     auto r = impl_->io_load(self, fileName);

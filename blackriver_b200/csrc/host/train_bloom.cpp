@@ -149,10 +149,16 @@ MicroBatches make_data(const Options& o) {
     return d;
 }
 
-void write_host_ints(br::Enviroment& env, const char* name, const int* src, size_t count) {
-    br::tensor_t t = env.hash().find_tensor(name);
-    br_assert(!t->is_cuda() && t->bytes() == count * sizeof(int), (std::string("unexpected tensor ") + name).c_str());
-    std::memcpy(t->data(), src, count * sizeof(int));
+// ids [batch, tokens], mask [batch, tokens] and lens [batch] of micro-batch m, packed in the order of the stage
+// script's device tensor "inp"
+std::vector<int> packed_inputs(const Options& o, const MicroBatches& d, int m) {
+    const size_t bt = (size_t)o.batch * o.tokens;
+    std::vector<int> p;
+    p.reserve(2 * bt + o.batch);
+    p.insert(p.end(), d.ids.begin() + (size_t)m * bt, d.ids.begin() + (size_t)(m + 1) * bt);
+    p.insert(p.end(), d.mask.begin() + (size_t)m * bt, d.mask.begin() + (size_t)(m + 1) * bt);
+    p.insert(p.end(), d.lens.begin() + (size_t)m * o.batch, d.lens.begin() + (size_t)(m + 1) * o.batch);
+    return p;
 }
 
 }  // namespace
@@ -180,39 +186,40 @@ int main(int argc, char** argv) {
             ss << o.loss_scale << " op.loss_scale " << o.verbose << " op.verbose";
             env.execute(ss.str());
         }
-        std::vector<br::DaG*> fwd, bwd;
-        for (int k = 0; k < n_slots; k++) {
+        std::vector<br::DaG*> fwd, bwd;          // one program per micro-batch: its slot, and the cell of "loss_all" it fills
+        for (int m = 0; m < o.micro; m++) {
             std::stringstream f, b;
-            f << "slot_" << k << " stage_forward";
-            b << "slot_" << k << " stage_backward";
+            f << "slot_" << (m % n_slots) << " stage_forward";
+            b << "slot_" << (m % n_slots) << " \"loss@" << m << "\" stage_backward_async";
             fwd.push_back(env.build(f.str()));
             bwd.push_back(env.build(b.str()));
         }
         br::DaG* begin = env.build("zero_grads 1 op.accumulate");
         br::DaG* sync = env.build("op.sync");
+        br::DaG* status = env.build("op.kernel_status");
 
         const MicroBatches data = make_data(o);
         const size_t bt = (size_t)o.batch * o.tokens;
+        // the packed inputs live (unchanged) for the whole run, so the queued copies may read them at any later time
+        std::vector<std::vector<int>> packed;
+        for (int m = 0; m < o.micro; m++) packed.push_back(packed_inputs(o, data, m));
         auto feed = [&](int m) {
             env.change(0);
-            write_host_ints(env, "ids_", data.ids.data() + (size_t)m * bt, bt);
-            write_host_ints(env, "mask_", data.mask.data() + (size_t)m * bt, bt);
-            write_host_ints(env, "lens_", data.lens.data() + (size_t)m * o.batch, (size_t)o.batch);
+            br::tensor_t t = env.hash().find_tensor("inp");
+            br_assert(t->is_cuda() && t->bytes() == packed[m].size() * sizeof(int), "unexpected input tensor \"inp\"");
+            BR_CUDA_CHECK(cudaMemcpyAsync(t->data(), packed[m].data(), t->bytes(), cudaMemcpyHostToDevice, br::ComputingContext::cuda_stream));
         };
+        std::vector<float> losses((size_t)o.micro);
 
         for (int step = 1; step <= o.steps; step++) {
             env.run(sync);
             const auto t0 = std::chrono::steady_clock::now();
             env.run(begin);
-            double loss_sum = 0.0;
-            int loss_n = 0;
             if (world == 1) {
                 for (int m = 0; m < o.micro; m++) {
                     feed(m);
-                    env.run(fwd[0]);
-                    env.run(bwd[0]);
-                    loss_sum += br::last_loss();
-                    loss_n++;
+                    env.run(fwd[m]);
+                    env.run(bwd[m]);
                 }
             } else {
                 for (int m = 0; m < o.micro; m++) {
@@ -222,16 +229,25 @@ int main(int argc, char** argv) {
                 for (int m = 0; m < o.micro; m++) {
                     feed(m);
                     env.run(bwd[m]);
-                    if (last) {
-                        loss_sum += br::last_loss();
-                        loss_n++;
-                    }
                 }
-                if (first || last) {      // the two holders of the tied table sum their gradients
-                    std::stringstream ss;
-                    ss << (first ? world - 1 : 0) << " sync_tied_grads";
-                    env.execute(ss.str());
-                }
+            }
+            // the one wait of the step: no update is applied on top of a tensor-core kernel that gave up a wait
+            env.run(status);
+            const int code = (int)env.stack().pop_number();
+            br_assert(code == 0, "a tensor-core kernel gave up a bounded wait; the optimizer step was not applied");
+            double loss_sum = 0.0;
+            int loss_n = 0;
+            if (last) {
+                env.change(0);
+                br::tensor_t t = env.hash().find_tensor("loss_all");
+                BR_CUDA_CHECK(cudaMemcpy(losses.data(), t->data(), losses.size() * sizeof(float), cudaMemcpyDeviceToHost));
+                for (float v : losses) loss_sum += v;
+                loss_n = o.micro;
+            }
+            if (world > 1 && (first || last)) {      // the two holders of the tied table sum their gradients
+                std::stringstream ss;
+                ss << (first ? world - 1 : 0) << " sync_tied_grads";
+                env.execute(ss.str());
             }
             {
                 // gradients were summed over the micro-batches and carry the loss scale: Adam divides both out
@@ -254,6 +270,7 @@ int main(int argc, char** argv) {
         for (auto* p : bwd) delete p;
         delete begin;
         delete sync;
+        delete status;
     } catch (const std::exception& e) {
         std::fprintf(stderr, "train_bloom rank %d: %s\n", rank, e.what());
         return 1;

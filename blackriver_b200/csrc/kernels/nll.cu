@@ -101,7 +101,12 @@ __device__ __forceinline__ void row_max_sum(const T* z, int64_t vocab, float& m_
 template <typename T, bool VEC, bool BWD>
 __global__ void __launch_bounds__(NLL_THREADS, 1)
 nll_kernel(const T* logits, const int32_t* __restrict__ target, float* __restrict__ row_loss,
-           float* __restrict__ row_lse, T* dlogits, int64_t rows, int64_t vocab, float grad_scale) {
+           float* __restrict__ row_lse, T* dlogits, int64_t rows, int64_t vocab, float grad_scale, const int32_t* __restrict__ count) {
+    // with a device-side count of contributing rows the factor becomes grad_scale / count (mean over counted rows)
+    if (count != nullptr) {
+        const int32_t c = *count;
+        grad_scale = grad_scale / (float)(c > 0 ? c : 1);
+    }
     constexpr int VN = Vec<T>::N;
     __shared__ float red[64];
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -179,7 +184,7 @@ nll_kernel(const T* logits, const int32_t* __restrict__ target, float* __restric
 
 template <typename T, bool BWD>
 static int nll_dispatch(const void* logits_, const int32_t* target, float* row_loss, float* row_lse, void* dlogits_,
-                        int64_t rows, int64_t vocab, float grad_scale, cudaStream_t st) {
+                        int64_t rows, int64_t vocab, float grad_scale, const int32_t* count, cudaStream_t st) {
     const T* logits = (const T*)logits_;
     T* dlogits = (T*)dlogits_;
     constexpr int VN = Vec<T>::N;
@@ -187,9 +192,9 @@ static int nll_dispatch(const void* logits_, const int32_t* target, float* row_l
     int64_t cap = (int64_t)sm_count();
     int grid = (int)(rows < cap ? rows : cap);
     if (vec)
-        nll_kernel<T, true, BWD><<<grid, NLL_THREADS, 0, st>>>(logits, target, row_loss, row_lse, dlogits, rows, vocab, grad_scale);
+        nll_kernel<T, true, BWD><<<grid, NLL_THREADS, 0, st>>>(logits, target, row_loss, row_lse, dlogits, rows, vocab, grad_scale, count);
     else
-        nll_kernel<T, false, BWD><<<grid, NLL_THREADS, 0, st>>>(logits, target, row_loss, row_lse, dlogits, rows, vocab, grad_scale);
+        nll_kernel<T, false, BWD><<<grid, NLL_THREADS, 0, st>>>(logits, target, row_loss, row_lse, dlogits, rows, vocab, grad_scale, count);
     return launch_status("nll_kernel");
 }
 
@@ -200,6 +205,23 @@ __global__ void __launch_bounds__(1024) sum_f32_kernel(const float* x, float* ou
     for (int64_t i = threadIdx.x; i < n; i += blockDim.x) a += x[i];
     block_sum2(a, b, red);
     if (threadIdx.x == 0) out[0] = a;
+}
+
+// out[0] = (sum of x) / max(count, 1), single CTA, fixed order: the mean loss without a host round trip
+__global__ void __launch_bounds__(1024) sum_div_f32_kernel(const float* x, const int32_t* count, float* out, int64_t n) {
+    __shared__ float red[64];
+    float a = 0.0f, b = 0.0f;
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) a += x[i];
+    block_sum2(a, b, red);
+    if (threadIdx.x == 0) {
+        const int32_t c = *count;
+        out[0] = a / (float)(c > 0 ? c : 1);
+    }
+}
+
+__global__ void signal_u32_kernel(volatile uint32_t* flag, uint32_t value) {
+    __threadfence_system();
+    *flag = value;
 }
 
 __global__ void loss_targets_kernel(const int32_t* ids, const int32_t* mask, int32_t* target, int32_t* count, int batch,
@@ -238,8 +260,8 @@ extern "C" int brk_logsoftmax_nll_fwd(const void* logits, const int32_t* target,
     if (rows < 0 || vocab <= 0 || vocab > 0x7fffffffLL) return BRK_ATTR_ERROR;
     if (rows == 0) return BRK_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == BRK_F32) return brk::nll_dispatch<float, false>(logits, target, row_loss, row_lse, nullptr, rows, vocab, 0.0f, st);
-    if (dtype == BRK_F16) return brk::nll_dispatch<__half, false>(logits, target, row_loss, row_lse, nullptr, rows, vocab, 0.0f, st);
+    if (dtype == BRK_F32) return brk::nll_dispatch<float, false>(logits, target, row_loss, row_lse, nullptr, rows, vocab, 0.0f, nullptr, st);
+    if (dtype == BRK_F16) return brk::nll_dispatch<__half, false>(logits, target, row_loss, row_lse, nullptr, rows, vocab, 0.0f, nullptr, st);
     return BRK_ATTR_ERROR;
 }
 
@@ -250,9 +272,36 @@ extern "C" int brk_logsoftmax_nll_fwd_bwd(const void* logits, const int32_t* tar
     if (rows < 0 || vocab <= 0 || vocab > 0x7fffffffLL) return BRK_ATTR_ERROR;
     if (rows == 0) return BRK_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == BRK_F32) return brk::nll_dispatch<float, true>(logits, target, row_loss, nullptr, dlogits, rows, vocab, grad_scale, st);
-    if (dtype == BRK_F16) return brk::nll_dispatch<__half, true>(logits, target, row_loss, nullptr, dlogits, rows, vocab, grad_scale, st);
+    if (dtype == BRK_F32) return brk::nll_dispatch<float, true>(logits, target, row_loss, nullptr, dlogits, rows, vocab, grad_scale, nullptr, st);
+    if (dtype == BRK_F16) return brk::nll_dispatch<__half, true>(logits, target, row_loss, nullptr, dlogits, rows, vocab, grad_scale, nullptr, st);
     return BRK_ATTR_ERROR;
+}
+
+extern "C" int brk_logsoftmax_nll_fwd_bwd_counted(const void* logits, const int32_t* target, float* row_loss, void* dlogits,
+                                                  int64_t rows, int64_t vocab, float scale_numerator, const int32_t* count,
+                                                  int dtype, void* stream) {
+    if (!logits || !target || !count) return BRK_INPUT_ERROR;
+    if (!row_loss || !dlogits) return BRK_OUTPUT_ERROR;
+    if (rows < 0 || vocab <= 0 || vocab > 0x7fffffffLL) return BRK_ATTR_ERROR;
+    if (rows == 0) return BRK_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == BRK_F32) return brk::nll_dispatch<float, true>(logits, target, row_loss, nullptr, dlogits, rows, vocab, scale_numerator, count, st);
+    if (dtype == BRK_F16) return brk::nll_dispatch<__half, true>(logits, target, row_loss, nullptr, dlogits, rows, vocab, scale_numerator, count, st);
+    return BRK_ATTR_ERROR;
+}
+
+extern "C" int brk_sum_div_f32(const float* x, const int32_t* count, float* out, int64_t n, void* stream) {
+    if (!x || !count) return BRK_INPUT_ERROR;
+    if (!out) return BRK_OUTPUT_ERROR;
+    if (n < 0) return BRK_ATTR_ERROR;
+    brk::sum_div_f32_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(x, count, out, n);
+    return brk::launch_status("sum_div_f32_kernel");
+}
+
+extern "C" int brk_signal_u32(uint32_t* flag, uint32_t value, void* stream) {
+    if (!flag) return BRK_OUTPUT_ERROR;
+    brk::signal_u32_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(flag, value);
+    return brk::launch_status("signal_u32_kernel");
 }
 
 extern "C" int brk_sum_f32(const float* x, float* out, int64_t n, void* stream) {

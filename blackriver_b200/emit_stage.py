@@ -20,7 +20,7 @@ def stage_script(hidden, heads, vocab, n_layers, batch, tokens, n_micro, rank, w
     text = words.fused_words(
         hidden=hidden, heads=heads, vocab=vocab, n_layers=counts[rank], batch=batch, tokens=tokens, dtype=dtype,
         first_stage=first, last_stage=last, logits_rows=logits_rows, init_std=init_std, seed=seed,
-        layer_offset=sum(counts[:rank]), n_slots=n_micro if world > 1 else 1,
+        layer_offset=sum(counts[:rank]), n_slots=n_micro if world > 1 else 1, n_micro=n_micro,
         prev_rank=None if first else rank - 1, next_rank=None if last else rank + 1)
     return text, counts[rank]
 

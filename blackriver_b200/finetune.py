@@ -4,14 +4,14 @@ it) with the generated words scripts and runs training steps made of micro-batch
 It plays the role of the reference's driver (blackriver/train_bloom.cpp: BloomInput feeding ids
 and masks, BloomAttentions running the words) with one rank per GPU: rank r owns a contiguous
 block of layers, the first rank also the embedding, the last rank the final LayerNorm, the tied
-LM head and the loss.  Each step runs every micro-batch forward through the pipeline, then every
-micro-batch backward (activations of all micro-batches in flight are kept in per-micro-batch
-slots), sums the two copies of the tied-table gradient, and applies Adam.
+LM head and the loss.  Each step runs every micro-batch forward and backward through the pipeline
+(activations of the micro-batches in flight are kept in slots; schedule.py fixes the order of the
+tasks on every rank), sums the two copies of the tied-table gradient, and applies Adam.
 Everything that computes is a word executed by the words machine on device tensors.
 """
 import numpy as np
 
-from . import host, words
+from . import host, schedule, words
 
 LM_HEAD_COST_IN_LAYERS = 5.9      # measured step time of final LayerNorm + 250880-way head + loss, in 7b1 decoder layers (5.1 by FLOPs)
 
@@ -48,72 +48,148 @@ def make_microbatches(n_micro, batch, tokens, vocab, min_len, seed, pad_id=3):
     return out
 
 
+def pack_inputs(mb):
+    """ids [B,T], mask [B,T], lens [B] of one micro-batch as the int32 buffer the stage scripts call "inp"."""
+    ids, mask, lens = mb
+    return np.concatenate([np.asarray(ids, np.int32).ravel(), np.asarray(mask, np.int32).ravel(), np.asarray(lens, np.int32).ravel()])
+
+
 class Trainer:
+    """One pipeline stage (or the whole model) driven through the words machine.
+
+    world == 1: every micro-batch forward then backward.  world > 1 with overlap (the default): the stage's work is cut
+    into forward / input-gradient / weight-gradient tasks per micro-batch, executed in the static order that
+    schedule.build lays out for this rank, with one-sided hand-offs between neighbours (io.link.*); with overlap=False
+    the plain order (all forwards, then all backwards) over NCCL send / receive on the compute stream.
+    Nothing in a step waits for the device except one check before the optimizer: the status words of the tensor-core
+    kernels are read (an update computed from a kernel that gave up a wait is refused) together with the losses."""
+
     def __init__(self, hidden, heads, vocab, n_layers, batch, tokens, n_micro, rank=0, world=1, dtype="half", seed=0,
-                 loss_scale=1024.0, lr=1e-4, logits_rows=None, init_std=0.02, verbose=False, head_cost=LM_HEAD_COST_IN_LAYERS):
+                 loss_scale=1024.0, lr=1e-4, logits_rows=None, init_std=0.02, verbose=False, head_cost=LM_HEAD_COST_IN_LAYERS,
+                 overlap=None, n_slots=None, activation_budget=56 << 30, play_all_ranks=False):
         self.rank, self.world, self.n_micro = rank, world, n_micro
         self.batch, self.tokens = batch, tokens
         self.loss_scale, self.lr = float(loss_scale), float(lr)
         self.counts = partition_layers(n_layers, world, head_cost)
         self.first, self.last = rank == 0, rank == world - 1
+        self.overlap = (world > 1) if overlap is None else (bool(overlap) and world > 1)
         my_layers = self.counts[rank]
-        self.n_slots = n_micro if world > 1 else 1
+        if world == 1:
+            self.n_slots = 1
+        elif n_slots is not None:
+            self.n_slots = max(2, min(int(n_slots), n_micro)) if n_micro > 1 else 1
+        else:
+            act = batch * tokens * hidden * (2 if dtype == "half" else 4)
+            per_layer = (23 if self.overlap else 14) * act
+            self.n_slots = schedule.n_slots_for(world, n_micro, self.counts, per_layer, activation_budget) if n_micro > 1 else 1
+        if self.n_slots < 2:
+            self.overlap = False
+        if world > 1 and not self.overlap:
+            self.n_slots = n_micro        # all forwards run before the first backward: every micro-batch stays alive
         self.env = host.Env(my_layers + 1)
-        text = words.fused_words(
-            hidden=hidden, heads=heads, vocab=vocab, n_layers=my_layers, batch=batch, tokens=tokens, dtype=dtype,
-            first_stage=self.first, last_stage=self.last, logits_rows=logits_rows, init_std=init_std, seed=seed,
-            layer_offset=sum(self.counts[:rank]), n_slots=self.n_slots,
-            prev_rank=None if self.first else rank - 1, next_rank=None if self.last else rank + 1)
-        self.env.execute(text)
+        kw = dict(hidden=hidden, heads=heads, vocab=vocab, n_layers=my_layers, batch=batch, tokens=tokens, dtype=dtype,
+                  first_stage=self.first, last_stage=self.last, logits_rows=logits_rows, init_std=init_std, seed=seed,
+                  layer_offset=sum(self.counts[:rank]), n_slots=self.n_slots, n_micro=n_micro,
+                  prev_rank=None if self.first else rank - 1, next_rank=None if self.last else rank + 1)
+        # play_all_ranks: this single-rank process holds the Trainers of every rank of the pipeline (a test on one GPU
+        # that interleaves their task lists itself); the links then keep one block per played rank
+        self.played = bool(play_all_ranks) and self.overlap
+        self.env.execute(words.fused_words(overlap=self.overlap, **kw))
+        if self.played:
+            self.env.execute(f"{world} io.link.emulate {rank} io.link.rank")
         self.env.execute("build_model init_model zero_grads")
         self.env.execute(f"{self.loss_scale} op.loss_scale {1 if verbose else 0} op.verbose")
         e = self.env
-        # compiled once, run many times
-        self.p_fwd = [e.build(f"slot_{k if self.n_slots > 1 else 0} stage_forward") for k in range(self.n_slots)]
-        self.p_bwd = [e.build(f"slot_{k if self.n_slots > 1 else 0} stage_backward") for k in range(self.n_slots)]
-        self.p_begin = e.build("zero_grads 1 op.accumulate")
-        self.p_sync = e.build("op.sync")
+        S = self.n_slots
+        self.tasks = []          # (program, micro-batch to feed or None) in execution order
+        self._programs = []
+
+        def prog(text):
+            h = e.build(text)
+            self._programs.append(h)
+            return h
+
+        if world == 1:
+            self.order = None
+            for k in range(n_micro):
+                self.tasks.append((prog("slot_0 stage_forward"), k))
+                self.tasks.append((prog(f'slot_0 "loss@{k}" stage_backward_async'), k))
+        elif not self.overlap:
+            self.order = None
+            for k in range(n_micro):
+                self.tasks.append((prog(f"slot_{k % S} stage_forward"), k))
+            for k in range(n_micro):
+                self.tasks.append((prog(f'slot_{k % S} "loss@{k}" stage_backward_async'), k))
+        else:
+            costs = schedule.stage_costs(self.counts)
+            orders, self.simulated_step = schedule.build(world, n_micro, costs, S)
+            schedule.check(orders, n_micro, S)          # raises on a dependency or slot conflict before anything is queued
+            self.order = orders[rank]
+            self.simulated_efficiency = schedule.efficiency(self.simulated_step, costs, n_micro)
+            for t in self.order:
+                slot = t.k % S
+                if t.kind == "F":
+                    self.tasks.append((prog(f"slot_{slot} stage_f"), t.k))
+                elif t.kind == "B":
+                    self.tasks.append((prog(f'slot_{slot} "loss@{t.k}" stage_b'), t.k))
+                else:
+                    self.tasks.append((prog(f"slot_{slot} stage_w"), None))
+        self.p_begin = prog("zero_grads 1 op.accumulate")
+        self.p_sync = prog("op.sync")
+        self.p_status = prog("op.kernel_status")
         self.p_score = None          # built on first use
         self.step_no = 0
         self.losses = []
 
-    def _feed(self, mb):
-        ids, mask, lens = mb
+    def _feed(self, packed):
         e = self.env
         e.change(0)
-        e.write("ids_", ids)
-        e.write("mask_", mask)
-        e.write("lens_", lens)
+        e.write_async("inp", packed)
 
-    def step(self, microbatches):
-        """One optimizer step over the micro-batches; returns the mean loss (last stage) or None."""
-        e = self.env
+    def begin_step(self, microbatches):
         assert len(microbatches) == self.n_micro
-        e.run(self.p_begin)
+        self._packed = [pack_inputs(mb) for mb in microbatches]
+        self.env.run(self.p_begin)
+
+    def run_task(self, i):
+        """Queues task i of this rank's list (step() runs them all in order; a test that emulates several ranks in one
+        process interleaves the lists of its Trainers itself)."""
+        program, k = self.tasks[i]
+        if self.played:
+            self.env.execute(f"{self.rank} io.link.rank")
+        if k is not None:
+            self._feed(self._packed[k])
+        self.env.run(program)
+
+    def check_and_read_losses(self):
+        """The one wait of the step: kernel status and losses, before anything is applied to the weights."""
+        e = self.env
+        e.run(self.p_status)
+        code = int(e.pop_number())
+        if code != 0:
+            raise RuntimeError(f"a tensor-core kernel gave up a bounded wait (status {code}); the optimizer step was not applied")
         self.losses = []
-        if self.world == 1:
-            for mb in microbatches:
-                self._feed(mb)
-                e.run(self.p_fwd[0])
-                e.run(self.p_bwd[0])
-                self.losses.append(host.last_loss())
-        else:
-            for k, mb in enumerate(microbatches):
-                self._feed(mb)
-                e.run(self.p_fwd[k])
-            for k, mb in enumerate(microbatches):
-                self._feed(mb)
-                e.run(self.p_bwd[k])
-                if self.last:
-                    self.losses.append(host.last_loss())
-            if self.first or self.last:
-                peer = self.world - 1 if self.first else 0
-                e.execute(f"{peer} sync_tied_grads")
+        if self.last:
+            e.change(0)
+            self.losses = [float(v) for v in e.read("loss_all")]
+
+    def apply_optimizer(self):
         self.step_no += 1
         # gradients were summed over micro-batches and carry the loss scale: Adam divides both out
         gs = 1.0 / (self.loss_scale * self.n_micro)
-        e.execute(f"0 op.accumulate {self.lr} {self.step_no} {gs} optimizer_step")
+        self.env.execute(f"0 op.accumulate {self.lr} {self.step_no} {gs} optimizer_step")
         return float(np.mean(self.losses)) if self.losses else None
+
+    def step(self, microbatches):
+        """One optimizer step over the micro-batches; returns the mean loss (last stage) or None."""
+        self.begin_step(microbatches)
+        for i in range(len(self.tasks)):
+            self.run_task(i)
+        self.check_and_read_losses()
+        if self.world > 1 and (self.first or self.last):
+            peer = self.world - 1 if self.first else 0
+            self.env.execute(f"{peer} sync_tied_grads")
+        return self.apply_optimizer()
 
     def score(self, microbatches):
         """Forward only (prefill scoring): runs every micro-batch through the stages and, on the rank that holds the
@@ -124,7 +200,7 @@ class Trainer:
             self.p_score = [e.build(f"slot_{k} stage_score") for k in range(self.n_slots)]
         out = []
         for k, mb in enumerate(microbatches):
-            self._feed(mb)
+            self._feed(pack_inputs(mb))
             e.run(self.p_score[k % self.n_slots])
             if self.last:
                 e.change(0)
@@ -137,8 +213,10 @@ class Trainer:
 
     def close(self):
         # the training switches live in the process-wide computing context: hand them back at their defaults
-        self.env.execute("0 op.accumulate 1 op.loss_scale 1 op.verbose")
-        for p in self.p_fwd + self.p_bwd + [self.p_begin, self.p_sync] + (self.p_score or []):
+        self.env.execute("op.sync 0 op.accumulate 1 op.loss_scale 1 op.verbose")
+        if self.overlap:
+            self.env.execute("io.link.close")
+        for p in self._programs + (self.p_score or []):
             self.env.free_program(p)
         self.env.close()
 

@@ -39,6 +39,7 @@ SIGNATURES = {
     "brh_env_tensor_info": (i32, [p, cstr, C.POINTER(p), C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(i64)]),
     "brh_env_tensor_write": (i32, [p, cstr, p, sz]),
     "brh_env_tensor_read": (i32, [p, cstr, p, sz]),
+    "brh_env_tensor_write_async": (i32, [p, cstr, p, sz]),
     "brh_last_loss": (f32, []),
     "brh_profile_start": (i32, []),
     "brh_profile_stop": (i32, [C.c_char_p, sz]),
@@ -198,6 +199,13 @@ class Env:
         a = np.ascontiguousarray(array, dtype=_NP[info["dtype"]])
         assert a.size == int(np.prod(info["shape"])), (name, a.shape, info["shape"])
         _check(lib().brh_env_tensor_write(self._h, name.encode(), a.ctypes.data_as(p), a.nbytes))
+
+    def write_async(self, name, array):
+        """Queues the write on the compute stream (the data is copied out of `array` before this returns)."""
+        info = self.tensor_info(name)
+        a = np.ascontiguousarray(array, dtype=_NP[info["dtype"]])
+        assert a.size == int(np.prod(info["shape"])), (name, a.shape, info["shape"])
+        _check(lib().brh_env_tensor_write_async(self._h, name.encode(), a.ctypes.data_as(p), a.nbytes))
 
     def read(self, name):
         info = self.tensor_info(name)

@@ -1,0 +1,187 @@
+"""Static task order of the overlapped pipeline.
+
+The reference runs its stages strictly one after the other: every layer's forward, then the loss and one backward
+(blackriver/train_bloom.cpp:211-241), with blocking hand-offs (bloomz-7b/train.words:250-258).  Here a training step is
+cut, per rank and micro-batch k, into three tasks
+
+    F(k)  forward of the stage                      needs F(k) of the previous rank
+    B(k)  input gradients of the stage               needs F(k) here and B(k) of the next rank
+    W(k)  weight gradients (column sums + dy^T x)    needs B(k) here; nothing waits for it but the optimizer
+
+and every rank executes a fixed list of them.  Hand-offs are one-sided and buffered (PipeLinks), so any list that
+respects the data dependencies is safe; the list decides how much of the fill and drain of the pipeline is spent idle.
+`build` produces the lists with a greedy event simulation (a rank that becomes free takes, in this order of
+preference, a ready B, a ready F, a pending W); `check` replays lists against the dependencies and reports a deadlock
+or a memory-slot conflict before anything is queued on a GPU.
+
+Slots: a rank keeps the saved activations of at most `n_slots` micro-batches, micro-batch k using slot k % n_slots, so
+F(k) may only start once W(k - n_slots) has finished on that rank.
+"""
+from dataclasses import dataclass
+
+# Relative costs of one decoder layer's three tasks and of the LM head + loss (same unit), from the measured
+# per-family device times of the 7b1-shaped step: forward GEMMs + attention forward; input-gradient GEMMs +
+# attention backward + LayerNorm / GELU backward; weight-gradient GEMMs + column sums.  The head's forward part
+# (logits GEMM + log-softmax) is counted with its B task because it runs there.
+LAYER_COST = (0.90, 1.05, 0.80)
+HEAD_COST = (0.1, 8.6, 4.5)
+
+
+@dataclass(frozen=True)
+class Task:
+    kind: str      # "F", "B" or "W"
+    k: int         # micro-batch
+
+
+def stage_costs(counts, layer_cost=LAYER_COST, head_cost=HEAD_COST):
+    """(F, B, W) cost of one micro-batch on every rank; the last rank carries the head."""
+    out = []
+    for r, n in enumerate(counts):
+        f, b, w = (n * c for c in layer_cost)
+        if r == len(counts) - 1:
+            f, b, w = f + head_cost[0], b + head_cost[1], w + head_cost[2]
+        out.append((max(f, 1e-3), max(b, 1e-3), max(w, 1e-3)))
+    return out
+
+
+def _deps(world, n_slots, r, t):
+    """Tasks (rank, Task) that must have finished before task t may start on rank r."""
+    d = []
+    if t.kind == "F":
+        if r > 0:
+            d.append((r - 1, Task("F", t.k)))
+        if t.k >= n_slots:
+            d.append((r, Task("W", t.k - n_slots)))
+    elif t.kind == "B":
+        d.append((r, Task("F", t.k)))
+        if r < world - 1:
+            d.append((r + 1, Task("B", t.k)))
+    else:
+        d.append((r, Task("B", t.k)))
+    return d
+
+
+def build(world, n_micro, costs, n_slots=None, link_latency=0.02, patience=0.25):
+    """Greedy list schedule.  costs[r] = (F, B, W) durations of one micro-batch on rank r.
+    `patience`: a rank about to start a W although a B or F becomes ready within patience x (cost of W) waits for that
+    task instead.  Returns (orders, makespan): orders[r] is rank r's task list, makespan the simulated step time."""
+    n_slots = n_micro if n_slots is None else max(1, min(n_slots, n_micro))
+    done = {}                                   # (rank, Task) -> finish time
+    orders = [[] for _ in range(world)]
+    free_at = [0.0] * world
+    nxt = [{"F": 0, "B": 0, "W": 0} for _ in range(world)]
+    total = 3 * n_micro
+    dur = {"F": 0, "B": 1, "W": 2}
+
+    def ready_time(r, t):
+        """Time at which every dependency has finished (None while one of them is not scheduled yet)."""
+        when = 0.0
+        for (dr, dt) in _deps(world, n_slots, r, t):
+            f = done.get((dr, dt))
+            if f is None:
+                return None
+            when = max(when, f + (link_latency if dr != r else 0.0))
+        return when
+
+    while any(len(o) < total for o in orders):
+        # Decisions are taken in the order of simulated time: the rank whose next start comes first decides next, so
+        # everything that finishes before that moment is already known.
+        best = None
+        for r in range(world):
+            if len(orders[r]) == total:
+                continue
+            cands = []
+            for pref, kind in enumerate(("B", "F", "W")):
+                k = nxt[r][kind]
+                if k >= n_micro:
+                    continue
+                when = ready_time(r, Task(kind, k))
+                if when is not None:
+                    cands.append((when, pref, kind, k))
+            if not cands:
+                continue
+            now = free_at[r]
+            startable = [c for c in cands if c[0] <= now + 1e-12]
+            if startable:
+                _, pref, kind, k = min(startable, key=lambda c: c[1])
+                start = now
+                if kind == "W":
+                    # a weight-gradient pass cannot be interrupted: leave a gap rather than make a task that feeds
+                    # another rank wait for most of it
+                    soon = [c for c in cands if c[1] < 2 and c[0] < now + patience * costs[r][2]]
+                    if soon:
+                        start, pref, kind, k = min(soon, key=lambda c: (c[0], c[1]))
+            else:
+                start, pref, kind, k = min(cands, key=lambda c: (c[0], c[1]))
+            if best is None or (start, r) < best[:2]:
+                best = (start, r, kind, k)
+        if best is None:
+            raise RuntimeError("schedule.build: no task can start (dependency cycle)")
+        start, r, kind, k = best
+        t = Task(kind, k)
+        done[(r, t)] = start + costs[r][dur[kind]]
+        free_at[r] = done[(r, t)]
+        orders[r].append(t)
+        nxt[r][kind] += 1
+    return orders, max(free_at)
+
+
+def gpipe(world, n_micro):
+    """All forwards, then backward and weight gradients micro-batch by micro-batch: the plain schedule."""
+    one = [Task("F", k) for k in range(n_micro)]
+    for k in range(n_micro):
+        one += [Task("B", k), Task("W", k)]
+    return [list(one) for _ in range(world)]
+
+
+def check(orders, n_micro, n_slots, costs=None, link_latency=0.02):
+    """Replays the per-rank lists against the dependencies.  Raises ValueError on an incomplete list, a task before its
+    dependency on the same rank, or a deadlock across ranks.  Returns the simulated step time when costs are given
+    (every rank executes its list in order, starting each task as soon as its dependencies have finished), else None."""
+    world = len(orders)
+    n_slots = max(1, min(n_slots, n_micro))
+    want = {Task(kind, k) for kind in "FBW" for k in range(n_micro)}
+    for r, o in enumerate(orders):
+        if len(o) != len(want) or set(o) != want:
+            raise ValueError(f"rank {r}: the list is not a permutation of F, B, W over {n_micro} micro-batches")
+    pos = [0] * world
+    done = {}
+    free_at = [0.0] * world
+    dur = {"F": 0, "B": 1, "W": 2}
+    while any(pos[r] < len(orders[r]) for r in range(world)):
+        moved = False
+        for r in range(world):
+            while pos[r] < len(orders[r]):
+                t = orders[r][pos[r]]
+                when = 0.0
+                ok = True
+                for (dr, dt) in _deps(world, n_slots, r, t):
+                    f = done.get((dr, dt))
+                    if f is None:
+                        ok = False
+                        break
+                    when = max(when, f + (link_latency if dr != r else 0.0))
+                if not ok:
+                    break
+                start = max(when, free_at[r])
+                free_at[r] = start + (costs[r][dur[t.kind]] if costs else 1.0)
+                done[(r, t)] = free_at[r]
+                pos[r] += 1
+                moved = True
+        if not moved:
+            stuck = {r: orders[r][pos[r]] for r in range(world) if pos[r] < len(orders[r])}
+            raise ValueError(f"deadlock: every rank waits for a task that never runs: {stuck}")
+    return max(free_at) if costs else None
+
+
+def efficiency(makespan, costs, n_micro):
+    """Simulated step time of one rank doing all the work, divided by (ranks x the pipeline's step time)."""
+    return n_micro * sum(sum(c) for c in costs) / (len(costs) * makespan)
+
+
+def n_slots_for(world, n_micro, layers_per_rank, bytes_per_layer_slot, budget_bytes=56 << 30):
+    """Micro-batches whose saved activations (and kept gradients) fit the activation budget of the fullest rank."""
+    if world == 1:
+        return 1
+    per_slot = max(1, max(layers_per_rank)) * bytes_per_layer_slot
+    return int(max(2, min(n_micro, budget_bytes // max(per_slot, 1))))

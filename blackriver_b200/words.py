@@ -241,22 +241,35 @@ def layer_param_elements(hidden):
 
 
 def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps=1e-5, first_stage=True, last_stage=True,
-                logits_rows=None, init_std=0.02, seed=0, layer_offset=0, n_slots=1, prev_rank=None, next_rank=None):
+                logits_rows=None, init_std=0.02, seed=0, layer_offset=0, n_slots=1, prev_rank=None, next_rank=None,
+                overlap=False, n_micro=1):
     """Script text defining the whole stage.  After executing it:
          build_model            allocates everything (call once)
          init_model             seeded random initialisation (weights N(0, init_std), biases 0, LN 1/0)
          model_forward / model_backward / zero_grads / ( lr step grad_scale -- ) optimizer_step
          model_score            after model_forward, on the last stage: per-token next-token NLL into "token_nll" (fp32
                                 [batch, tokens], 0 where no target is counted), forward only; stage_score = stage_forward + it
-       Inputs are written to "ids_", "mask_", "lens_" (host int tensors) in hash 0; on a stage that is
-       not the first the incoming activations go to "stage_in" and the outgoing gradient is
-       "stage_in_g"; on a stage that is not the last "stage_out" / "stage_out_g" play the same roles.
-       Pipeline use: n_slots > 1 keeps that many micro-batches' saved activations at once; `slot_k`
-       selects the set the next forward / backward works on, and stage_forward / stage_backward add the
-       NCCL receive from / send to prev_rank and next_rank around model_forward / model_backward.
-       A last stage that is not also the first may have n_layers == 0 (final LayerNorm + LM head only)."""
+       Inputs: one device int tensor "inp" in hash 0 holding ids [batch, tokens], mask [batch, tokens] and lens [batch]
+       back to back (the views "ids_", "mask_", "lens_" are what the operators read).  On a stage that is not the first
+       the incoming activations are "stage_in" and the outgoing gradient is "stage_in_g"; on a stage that is not the
+       last "stage_out" / "stage_out_g" play the same roles.
+       Pipeline use: n_slots > 1 keeps that many micro-batches' saved activations at once; `slot_k` selects the set the
+       next forward / backward works on, and stage_forward / stage_backward add the NCCL receive from / send to
+       prev_rank and next_rank around model_forward / model_backward.
+       A last stage that is not also the first may have n_layers == 0 (final LayerNorm + LM head only).
+
+       overlap=True (needs n_slots > 1 and the one-sided links, `io.link.open` being part of build_model) defines the
+       three tasks of the overlapped schedule instead, each preceded by `slot_k` (k = micro-batch % n_slots):
+         stage_f      wait for the activations in this slot's window, forward, send on, release the window
+         ( name -- ) stage_b   input gradients only (the micro-batch's mean loss goes to the view of "loss_all" called
+                      name, "loss@j"); send to the previous rank
+         stage_w      weight gradients of the slot's micro-batch from the kept dy tensors; releases the gradient window
+       The stage's incoming tensors are then the link windows themselves (no copy on arrival)."""
     assert n_layers >= 1 or (last_stage and not first_stage)
+    assert not overlap or (n_slots > 1 and not (first_stage and last_stage))
     SLOTTED = ("xattn_in", "qkv", "attn_out", "xb", "x4a", "x4b", "lse", "input_ln_var", "post_ln_var")
+    # gradients a deferred weight-gradient pass reads: kept per slot instead of living in shared scratch
+    KEPT_DY = ("d4", "dqkv", "dh2") if overlap else ()
 
     def slot_names(name):
         return [name] if n_slots == 1 else [f"{name}@{k}" for k in range(n_slots)]
@@ -285,6 +298,10 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     for name, cols in (("xattn_in", 1), ("qkv", 3), ("attn_out", 1), ("xa", 1), ("xb", 1), ("x4a", 4), ("x4b", 4), ("xout", 1)):
         for nm in (slot_names(name) if name in SLOTTED else [name]):
             w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "{dtype}" op.create "{nm}" !')
+    for name, cols in (("d4", 4), ("dqkv", 3), ("dh2", 1), ("yout_g", 1)):
+        if overlap:
+            for nm in slot_names(name):
+                w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "{dtype}" op.create "{nm}" !')
     for nm in slot_names("lse"):
         w(f'    {batch} {heads} {tokens} 3 "cuda" "float" op.create "{nm}" !')
     w(f'    {n} 1 "cuda" "float" op.create "ln_mean" !')
@@ -320,6 +337,26 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w(f'    {g("dh3", "dh2", "xin_g")} op.add')
     w("%end")
 
+    # the same backward in two passes: input gradients (what the previous stage waits for), then weight gradients
+    w("%def layer_backward_x")
+    w(f'    {g("yout_g", "dense_4h_to_h.weight", "d4")} op.linear_backward_x')
+    w(f'    {g("d4", "x4a", "d4")} op.gelu_backward')
+    w(f'    {g("d4", "dense_h_to_4h.weight", "dh1")} op.linear_backward_x')
+    w(f'    {g("dh1", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "post_ln_var", "xb", "post_attention_layernorm.weight_g", "post_attention_layernorm.bias_g", "dh2", "LN_EPS")} op.layernorm_backward')
+    w(f'    {g("yout_g", "dh2", "dh2")} op.add')
+    w(f'    {g("dh2", "dense.weight", "dh1")} op.linear_backward_x')
+    w(f'    {g("dh1", "qkv", "attn_out", "lse", "lens_", "dqkv", "HEADS_NUM")} op.flash_attn_backward')
+    w(f'    {g("dqkv", "query_key_value.weight", "dh1")} op.linear_backward_x')
+    w(f'    {g("dh1", "input_layernorm.weight", "input_layernorm.bias", "input_ln_var", "xattn_in", "input_layernorm.weight_g", "input_layernorm.bias_g", "dh3", "LN_EPS")} op.layernorm_backward')
+    w(f'    {g("dh3", "dh2", "xin_g")} op.add')
+    w("%end")
+    w("%def layer_backward_w")
+    w(f'    {g("yout_g", "x4b", "dense_4h_to_h.weight_g", "dense_4h_to_h.bias_g")} op.linear_backward_w')
+    w(f'    {g("d4", "xb", "dense_h_to_4h.weight_g", "dense_h_to_4h.bias_g")} op.linear_backward_w')
+    w(f'    {g("dh2", "attn_out", "dense.weight_g", "dense.bias_g")} op.linear_backward_w')
+    w(f'    {g("dqkv", "xattn_in", "query_key_value.weight_g", "query_key_value.bias_g")} op.linear_backward_w')
+    w("%end")
+
     # ---- ( seed -- ) seeded initialisation of one layer ----
     w("%def init_layer_fused")
     w('    "seed_" !')
@@ -334,14 +371,24 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w("%end")
 
     # ---- whole stage ----
+    act_bytes = batch * tokens * hidden * (2 if dtype == "half" else 4)
+    n_logit_bufs = n_slots if (overlap and last_stage) else 1      # a deferred LM-head weight gradient keeps its dlogits
     w("%def build_model")
     w("    0 #")
-    w(f'    {batch} {tokens} 2 "cpu" "int" op.create "ids_" !  {batch} {tokens} 2 "cpu" "int" op.create "mask_" !  {batch} 1 "cpu" "int" op.create "lens_" !')
-    for name, cols in (("d4", 4), ("dqkv", 3), ("dh1", 1), ("dh2", 1), ("dh3", 1), ("gA", 1), ("gB", 1)):
+    # token ids, mask and lengths of the micro-batch being worked on, on the device (one buffer, three views)
+    w(f'    {2 * n + batch} 1 "cuda" "int" op.create "inp" !')
+    w(f'    "inp" @ 0 {batch} {tokens} 2 op.view "ids_" !  "inp" @ {n} {batch} {tokens} 2 op.view "mask_" !  "inp" @ {2 * n} {batch} 1 op.view "lens_" !')
+    w(f'    {max(n_micro, 1)} 1 "cuda" "float" op.create "loss_all" !')
+    for j in range(max(n_micro, 1)):
+        w(f'    "loss_all" @ {j} 1 1 op.view "loss@{j}" !')
+    shared_scratch = [("dh1", 1), ("dh3", 1), ("gA", 1), ("gB", 1)] + ([] if overlap else [("d4", 4), ("dqkv", 3), ("dh2", 1)])
+    for name, cols in shared_scratch:
         w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "DTYPE" @ op.create "{name}" !')
     w(f'    {n} 1 "cuda" "float" op.create "ln_mean" !')
     for nm in slot_names("emb_ln_var") + slot_names("ln_f_var"):
         w(f'    {n} 1 "cuda" "float" op.create "{nm}" !')
+    if overlap:
+        w(f"    {act_bytes} {n_slots} io.link.open")
     main_params = []
     if first_stage:
         main_params += [("word_embeddings.weight", (vocab, hidden)), ("word_embeddings_layernorm.weight", (hidden,)),
@@ -349,6 +396,9 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         w(f'    {BTH} "cuda" "DTYPE" @ op.create "emb_raw" !')
         for nm in slot_names("emb_out"):
             w(f'    {BTH} "cuda" "DTYPE" @ op.create "{nm}" !')
+    elif overlap:
+        for k in range(n_slots):          # the activations arrive in this rank's own windows
+            w(f'    0 {k} {BTH} "DTYPE" @ io.link.window "stage_in@{k}" !')
     else:
         w(f'    {BTH} "cuda" "DTYPE" @ op.create "stage_in" !')
     if last_stage:
@@ -358,8 +408,19 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         w(f'    {BTH} "cuda" "DTYPE" @ op.create "xf_g" !')
         for nm in slot_names("xf"):
             w(f'    {BTH} "cuda" "DTYPE" @ op.create "{nm}" !')
-        w(f'    {logits_rows} "VOCAB_SIZE" @ 2 "cuda" "DTYPE" @ op.create "all_logits" !')
+        if n_logit_bufs == 1:
+            w(f'    {logits_rows} "VOCAB_SIZE" @ 2 "cuda" "DTYPE" @ op.create "all_logits" !')
+        else:
+            assert logits_rows >= n, "deferring the LM-head weight gradient needs a logits band that covers the micro-batch"
+            for k in range(n_logit_bufs):
+                w(f'    {logits_rows} "VOCAB_SIZE" @ 2 "cuda" "DTYPE" @ op.create "all_logits@{k}" !')
         w(f'    {batch} {tokens} 2 "cuda" "float" op.create "token_nll" !')
+        if overlap and n_layers >= 1:
+            for k in range(n_slots):      # what the final LayerNorm's backward hands to the last layer, kept for its W pass
+                w(f'    {BTH} "cuda" "DTYPE" @ op.create "stage_out_g@{k}" !')
+    elif overlap:
+        for k in range(n_slots):          # the gradients arrive in this rank's own windows
+            w(f'    1 {k} {BTH} "DTYPE" @ io.link.window "stage_out_g@{k}" !')
     for name, shape in main_params:
         dims = " ".join(str(d) for d in shape)
         for suffix, dt in (("", '"DTYPE" @'), ("_g", '"DTYPE" @'), (".master", '"float"'), (".m", '"float"'), (".v", '"float"')):
@@ -369,18 +430,26 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     for i in range(1, n_layers + 1):
         w(f"    {i} # create_layer_fused")
     # bindings: scratch and inputs into every layer hash; activations chained layer to layer
-    shared = ("d4", "dqkv", "dh1", "dh2", "dh3", "lens_", "LN_EPS", "HEADS_NUM")
+    shared = ("dh1", "dh3", "lens_", "LN_EPS", "HEADS_NUM") + (() if overlap else ("d4", "dqkv", "dh2"))
     for i in range(1, n_layers + 1):
         for name in shared:
             w(f'    0 # "{name}" @ {i} # "{name}" !')
         src = (f'{i - 1} # "xout" @' if i > 1 else ('0 # "emb_out" @' if first_stage else '0 # "stage_in" @'))
-        if not (i == 1 and first_stage and n_slots > 1):      # with slots the embedding output is bound by slot_k
+        if not (i == 1 and n_slots > 1 and (first_stage or overlap)):      # with slots the stage input is bound by slot_k
             w(f'    {src} {i} # "xinput" !')
-        # gradient buffers alternate so a layer never reads and writes the same one
-        gin, gout = ("gA", "gB") if (n_layers - i) % 2 == 0 else ("gB", "gA")
-        w(f'    0 # "{gin}" @ {i} # "yout_g" !  0 # "{gout}" @ {i} # "xin_g" !')
+        if not overlap:
+            # gradient buffers alternate so a layer never reads and writes the same one
+            gin, gout = ("gA", "gB") if (n_layers - i) % 2 == 0 else ("gB", "gA")
+            w(f'    0 # "{gin}" @ {i} # "yout_g" !  0 # "{gout}" @ {i} # "xin_g" !')
     w("    0 #")
-    if n_layers >= 1:
+    if overlap:
+        # every layer keeps its incoming gradient per slot (bound by slot_k); the first layer's outgoing gradient
+        # is a shared buffer, consumed at once (embedding backward) or copied out by the link before it is reused
+        if n_layers >= 1:
+            w(f'    "gA" @ 1 # "xin_g" !  0 #  "gA" @ "stage_in_g" !  {n_layers} # "xout" @ 0 # "stage_out" !')
+        else:
+            w('    "gA" @ "stage_in_g" !')
+    elif n_layers >= 1:
         w(f'    {n_layers} # "xout" @ 0 # "stage_out" !  {n_layers} # "yout_g" @ 0 # "stage_out_g" !  1 # "xin_g" @ 0 # "stage_in_g" !  0 #')
     else:             # head-only stage: what arrives is what the final LayerNorm reads
         w('    "stage_in" @ "stage_out" !  "gA" @ "stage_out_g" !  "gA" @ "stage_in_g" !')
@@ -391,12 +460,29 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         w(f"%def slot_{k}")
         if n_slots > 1:
             w("    0 #")
+            w(f'    {k} "slot_" !')
             for name in (["emb_out", "emb_ln_var"] if first_stage else []) + (["xf", "ln_f_var"] if last_stage else []):
                 w(f'    "{name}@{k}" @ "{name}" !')
+            if overlap:
+                if not first_stage:
+                    w(f'    "stage_in@{k}" @ "stage_in" !')
+                if not (last_stage and n_layers == 0):
+                    w(f'    "stage_out_g@{k}" @ "stage_out_g" !')
+                if last_stage and n_logit_bufs > 1:
+                    w(f'    "all_logits@{k}" @ "all_logits" !')
+                if n_layers == 0:
+                    w('    "stage_in" @ "stage_out" !')
             if first_stage:
                 w(f'    "emb_out" @ 1 # "xinput" ! 0 #')
+            elif overlap and n_layers >= 1:
+                w(f'    "stage_in" @ 1 # "xinput" ! 0 #')
             for i in range(1, n_layers + 1):
-                w(f"    {i} #  " + "  ".join(f'"{name}@{k}" @ "{name}" !' for name in SLOTTED))
+                w(f"    {i} #  " + "  ".join(f'"{name}@{k}" @ "{name}" !' for name in SLOTTED + KEPT_DY))
+                if overlap:
+                    # layer i reads the gradient the layer after it (or the stage's successor) produced for this slot
+                    w(f'    "yout_g@{k}" @ "yout_g" !' if i < n_layers else f'    0 # "stage_out_g" @ {i} # "yout_g" !')
+                    if i > 1:
+                        w(f'    {i - 1} # "yout_g@{k}" @ {i} # "xin_g" !')
         w("    0 #")
         w("%end")
 
@@ -457,6 +543,23 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         w(f'    {g("emb_raw", "ids_", "word_embeddings.weight_g")} op.embed_backward')
     w("%end")
 
+    # ( name -- ) the same backward queued without any host round trip; name = the one-element view of "loss_all"
+    # that receives this micro-batch's mean loss ("loss@j")
+    w("%def model_backward_async")
+    w('    0 # @ "loss_" !')
+    if last_stage:
+        w(f'    {g("xf", "ids_", "mask_", "word_embeddings.weight", "all_logits", "xf_g", "word_embeddings.weight_g", "loss_")} 0 op.loss_backward_async')
+        w(f'    {g("xf_g", "ln_f.weight", "ln_f.bias", "ln_f_var", "xf", "ln_f.weight_g", "ln_f.bias_g", "stage_out_g", "LN_EPS")} op.layernorm_backward')
+    if not overlap:
+        for i in range(n_layers, 0, -1):
+            w(f"    {i} # layer_backward_fused")
+        w("    0 #")
+        if first_stage:
+            w(f'    {g("stage_in_g", "word_embeddings_layernorm.weight", "word_embeddings_layernorm.bias", "emb_ln_var", "emb_out", "word_embeddings_layernorm.weight_g", "word_embeddings_layernorm.bias_g", "emb_raw", "LN_EPS")} op.layernorm_backward')
+            w(f'    {g("emb_raw", "ids_", "word_embeddings.weight_g")} op.embed_backward')
+    w('    0 # "loss_" !!')
+    w("%end")
+
     # ( lr step grad_scale -- )
     w("%def optimizer_step")
     w('    0 #  "gs_" ! "step_" ! "lr_" !')
@@ -468,24 +571,81 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w('    0 #  "gs_" !! "step_" !! "lr_" !!')
     w("%end")
 
-    # ---- pipeline hand-offs around the stage's forward / backward ----
-    w("%def stage_forward")
-    if prev_rank is not None:
-        w(f'    0 # "stage_in" @ {prev_rank} io.nccl.recv')
-    w("    model_forward")
-    if next_rank is not None:
-        w(f'    0 # "stage_out" @ {next_rank} io.nccl.send')
-    w("%end")
-    w("%def stage_score")
-    w("    stage_forward model_score")
-    w("%end")
-    w("%def stage_backward")
-    if next_rank is not None:
-        w(f'    0 # "stage_out_g" @ {next_rank} io.nccl.recv')
-    w("    model_backward")
-    if prev_rank is not None:
-        w(f'    0 # "stage_in_g" @ {prev_rank} io.nccl.send')
-    w("%end")
+    if overlap:
+        # ---- the three tasks of the overlapped schedule (each runs after slot_k) ----
+        w("%def stage_f")
+        w("    0 #")
+        if prev_rank is not None:
+            w('    0 "slot_" @ io.link.wait')
+        if next_rank is not None:
+            w("    1 io.link.fence")                 # the previous micro-batch's output has left "stage_out"
+        w("    model_forward")
+        if next_rank is not None:
+            w('    0 # "stage_out" @ 1 "slot_" @ io.link.send')
+        if prev_rank is not None:
+            w('    0 # 0 "slot_" @ io.link.release')
+        w("%end")
+        w("%def stage_score")
+        w("    stage_f model_score")
+        w("%end")
+        w("%def stage_b")                            # ( name -- )  name as for model_backward_async
+        w('    0 # @ "loss_" !')
+        if next_rank is not None:
+            w('    1 "slot_" @ io.link.wait')
+        if prev_rank is not None:
+            w("    0 io.link.fence")                 # the previous micro-batch's gradient has left "stage_in_g"
+        if last_stage:
+            # the LM-head weight gradient waits for stage_w; with no layers on this stage the final LayerNorm writes
+            # straight into the buffer that is sent back
+            w(f'    {g("xf", "ids_", "mask_", "word_embeddings.weight", "all_logits", "xf_g", "word_embeddings.weight_g", "loss_")} 1 op.loss_backward_async')
+            dst = "stage_out_g" if n_layers >= 1 else "stage_in_g"
+            w(f'    {g("xf_g", "ln_f.weight", "ln_f.bias", "ln_f_var", "xf", "ln_f.weight_g", "ln_f.bias_g", dst, "LN_EPS")} op.layernorm_backward')
+        for i in range(n_layers, 0, -1):
+            w(f"    {i} # layer_backward_x")
+        w("    0 #")
+        if first_stage:
+            w(f'    {g("stage_in_g", "word_embeddings_layernorm.weight", "word_embeddings_layernorm.bias", "emb_ln_var", "emb_out", "word_embeddings_layernorm.weight_g", "word_embeddings_layernorm.bias_g", "emb_raw", "LN_EPS")} op.layernorm_backward')
+            w(f'    {g("emb_raw", "ids_", "word_embeddings.weight_g")} op.embed_backward')
+        if prev_rank is not None:
+            w('    "stage_in_g" @ 0 "slot_" @ io.link.send')
+        w('    "loss_" !!')
+        w("%end")
+        w("%def stage_w")
+        w("    0 #")
+        if last_stage:
+            w(f'    {g("all_logits", "xf", "word_embeddings.weight_g")} op.loss_backward_w')
+        for i in range(n_layers, 0, -1):
+            w(f"    {i} # layer_backward_w")
+        w("    0 #")
+        if next_rank is not None:
+            w('    1 "slot_" @ io.link.release')
+        w("%end")
+    else:
+        # ---- pipeline hand-offs around the stage's forward / backward (NCCL, in stream order) ----
+        w("%def stage_forward")
+        if prev_rank is not None:
+            w(f'    0 # "stage_in" @ {prev_rank} io.nccl.recv')
+        w("    model_forward")
+        if next_rank is not None:
+            w(f'    0 # "stage_out" @ {next_rank} io.nccl.send')
+        w("%end")
+        w("%def stage_score")
+        w("    stage_forward model_score")
+        w("%end")
+        w("%def stage_backward")
+        if next_rank is not None:
+            w(f'    0 # "stage_out_g" @ {next_rank} io.nccl.recv')
+        w("    model_backward")
+        if prev_rank is not None:
+            w(f'    0 # "stage_in_g" @ {prev_rank} io.nccl.send')
+        w("%end")
+        w("%def stage_backward_async")               # ( name -- )
+        if next_rank is not None:
+            w(f'    0 # "stage_out_g" @ {next_rank} io.nccl.recv')
+        w("    model_backward_async")
+        if prev_rank is not None:
+            w(f'    0 # "stage_in_g" @ {prev_rank} io.nccl.send')
+        w("%end")
     # ( peer -- )  both holders of the tied embedding / LM-head table sum their gradients
     w("%def sync_tied_grads")
     w('    0 # "peer_" !')

@@ -65,6 +65,10 @@ BRH_API int brh_env_tensor_info(void* env, const char* name, void** data, int* i
 BRH_API int brh_env_tensor_write(void* env, const char* name, const void* host, size_t bytes);
 BRH_API int brh_env_tensor_read(void* env, const char* name, void* host, size_t bytes);
 
+/* Same write without waiting for the device: the bytes are copied out of `host` (into page-locked staging memory owned
+ * by the library) before the call returns and reach the tensor in compute-stream order.  At most 4 MiB per call. */
+BRH_API int brh_env_tensor_write_async(void* env, const char* name, const void* host, size_t bytes);
+
 /* Per-kernel-family device timing of the backend (CUDA events around every kernel-library call).
  * brh_profile_stop waits for the stream, writes a JSON object {"family": {"ms":..,"calls":..}} into
  * `out` and switches profiling off. */

@@ -105,8 +105,24 @@ BRK_API int brk_logsoftmax_nll_fwd(const void* logits, const int32_t* target, fl
 BRK_API int brk_logsoftmax_nll_fwd_bwd(const void* logits, const int32_t* target, float* row_loss, void* dlogits,
                                int64_t rows, int64_t vocab, float grad_scale, int dtype, void* stream);
 
+/* Same kernel with the gradient factor formed on the device: grad_scale = scale_numerator / max(count[0], 1),
+ * count = the number of counted positions written by brk_loss_targets.  Replaces the stream synchronisation
+ * with which the reference fetches that count before scaling (blackriver/cuda_tensor.cpp:569-577), so the
+ * loss step can be queued without a host round trip. */
+BRK_API int brk_logsoftmax_nll_fwd_bwd_counted(const void* logits, const int32_t* target, float* row_loss, void* dlogits,
+                                       int64_t rows, int64_t vocab, float scale_numerator, const int32_t* count,
+                                       int dtype, void* stream);
+
 /* Deterministic sum of n fp32 values into out[0] (single CTA, fixed order); the loss total. */
 BRK_API int brk_sum_f32(const float* x, float* out, int64_t n, void* stream);
+/* out[0] = sum(x[0..n)) / max(count[0], 1): the mean loss over counted positions (the division the reference
+ * does on the host, blackriver/cuda_tensor.cpp:691), kept on the device. */
+BRK_API int brk_sum_div_f32(const float* x, const int32_t* count, float* out, int64_t n, void* stream);
+/* flag[0] = value, written by the device in stream order after everything queued before it, with a system-wide
+ * fence first; `flag` may live in a peer GPU's memory.  It has no counterpart in the reference: it is the
+ * arrival / release signal of the one-sided stage hand-offs that replace io_nccl_send / io_nccl_recv
+ * (blackriver/cuda_tensor.cpp:75-96) in the overlapped pipeline. */
+BRK_API int brk_signal_u32(uint32_t* flag, uint32_t value, void* stream);
 
 /* Loss targets on the device, bit-exact restatement of the host loops at
  * blackriver/cuda_tensor.cpp:555-568 and 597-625: target[b,t] = ids[b,t+1] when t < T-1 and

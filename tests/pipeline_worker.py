@@ -1,9 +1,10 @@
 """Worker for the pipeline tests: run under torchrun with WORLD_SIZE ranks.
 
-backend nccl (GPU): trains a small model for two steps as a WORLD_SIZE-stage pipeline, then rank 0
-trains the same model on one GPU and compares losses and updated weights.
-backend gloo (CPU): checks the host-side logic only -- stage partition, identical micro-batches on
-every rank, stage scripts compile in the words machine."""
+backend nccl (GPU): trains a small model for two steps as a WORLD_SIZE-stage pipeline (overlapped schedule with
+one-sided hand-offs, or -- BR_TEST_OVERLAP=0 -- the plain order over NCCL send / receive), then rank 0 trains the same
+model on one GPU and compares losses and updated weights.
+backend gloo (CPU): checks the host-side logic only -- stage partition, identical micro-batches and identical task
+lists on every rank, stage scripts of both kinds compile in the words machine."""
 import json
 import os
 import sys
@@ -34,14 +35,24 @@ def main():
         assert all(g == gathered[0] for g in gathered), "ranks disagree on inputs or partition"
         assert sum(counts) == CFG["n_layers"] and all(c >= 1 for c in counts[:-1]) and counts[-1] >= 0
         first, last = rank == 0, rank == world - 1
-        env = host.Env(counts[rank] + 1)
-        env.execute(words.fused_words(hidden=CFG["hidden"], heads=CFG["heads"], vocab=CFG["vocab"], n_layers=counts[rank],
-                                      batch=CFG["batch"], tokens=CFG["tokens"], first_stage=first, last_stage=last,
-                                      n_slots=CFG["n_micro"], prev_rank=None if first else rank - 1,
-                                      next_rank=None if last else rank + 1, layer_offset=sum(counts[:rank])))
-        prog = env.build("slot_1 stage_forward slot_1 stage_backward")     # links every word of the stage
-        env.free_program(prog)
-        env.close()
+        from blackriver_b200 import schedule
+        costs = schedule.stage_costs(counts)
+        orders, _ = schedule.build(world, CFG["n_micro"], costs, CFG["n_micro"])
+        schedule.check(orders, CFG["n_micro"], CFG["n_micro"])
+        lists = [None] * world
+        dist.all_gather_object(lists, [[(t.kind, t.k) for t in o] for o in orders])
+        assert all(x == lists[0] for x in lists), "ranks disagree on the task lists"
+        for overlap in (False, True):
+            env = host.Env(counts[rank] + 1)
+            env.execute(words.fused_words(hidden=CFG["hidden"], heads=CFG["heads"], vocab=CFG["vocab"], n_layers=counts[rank],
+                                          batch=CFG["batch"], tokens=CFG["tokens"], first_stage=first, last_stage=last,
+                                          n_slots=CFG["n_micro"], n_micro=CFG["n_micro"], prev_rank=None if first else rank - 1,
+                                          next_rank=None if last else rank + 1, layer_offset=sum(counts[:rank]), overlap=overlap))
+            text = ('slot_1 stage_f slot_1 "loss@1" stage_b slot_1 stage_w' if overlap else
+                    'slot_1 stage_forward slot_1 stage_backward slot_1 "loss@1" stage_backward_async')
+            prog = env.build(text)     # links every word of the stage
+            env.free_program(prog)
+            env.close()
         dist.barrier()
         if rank == 0:
             json.dump({"ok": True, "counts": counts}, open(out_path, "w"))
@@ -56,7 +67,8 @@ def main():
     dist.broadcast_object_list(box, src=0)
     host.collective_boot(rank, world, box[0])
     tr = finetune.Trainer(CFG["hidden"], CFG["heads"], CFG["vocab"], CFG["n_layers"], CFG["batch"], CFG["tokens"], CFG["n_micro"],
-                          rank=rank, world=world, seed=9, lr=1e-3, init_std=0.05, head_cost=head_cost)
+                          rank=rank, world=world, seed=9, lr=1e-3, init_std=0.05, head_cost=head_cost,
+                          overlap=os.environ.get("BR_TEST_OVERLAP", "1") != "0")
     losses = [tr.step(mbs) for _ in range(2)]
     tr.sync()
     w_first = None
@@ -86,7 +98,7 @@ def main():
             "w_err": float(np.abs(w_first - ref_w).max() / np.abs(ref_w).max()),
             "table_err": float(np.abs(table - ref_table).max() / np.abs(ref_table).max()),
             "tables_agree": abs(tables[0] - tables[-1]) <= 1e-6 * abs(tables[0]),
-            "counts": tr.counts,
+            "counts": tr.counts, "overlap": tr.overlap, "n_slots": tr.n_slots,
         }
         json.dump(res, open(out_path, "w"))
     dist.barrier()

@@ -42,6 +42,7 @@ def slopes_f32(heads):
     (2, 300, 2, 128, (300, 131)),
     (1, 512, 2, 128, (512,)),
     (3, 200, 2, 64, (1, 200, 129)),
+    (1, 2048, 2, 128, (2048,)),          # the long-context prefill shape: 2048 positions, head dimension 128, no padding
 ])
 def test_flash_attention_forward(B, T, heads, d, lens):
     if not torch.cuda.is_available():
@@ -95,6 +96,7 @@ def test_flash_attention_empty_sequence_and_no_alibi():
     (2, 300, 2, 128, (300, 131)),
     (1, 512, 2, 128, (512,)),
     (3, 200, 2, 64, (1, 200, 0)),
+    (1, 2048, 2, 128, (2048,)),
 ])
 def test_flash_attention_backward(B, T, heads, d, lens):
     from blackriver_b200 import brk, ops

@@ -121,6 +121,91 @@ def test_small_model_step(host):
         env.close()
 
 
+def read_params(env, L):
+    main_names = ("word_embeddings.weight", "word_embeddings_layernorm.weight", "word_embeddings_layernorm.bias", "ln_f.weight", "ln_f.bias")
+    env.change(0)
+    p_main = {k: env.read(k).astype(np.float32) for k in main_names}
+    layers = []
+    for i in range(1, L + 1):
+        env.change(i)
+        layers.append({k: env.read(k).astype(np.float32) for k in orc.LAYER_PARAMS})
+    env.change(0)
+    return main_names, p_main, layers
+
+
+def test_sixteen_microbatches_accumulate_like_the_oracle(host):
+    """The benchmark's step sums the gradients of 16 different micro-batches in fp16 tensors at loss scale 1024 (the
+    weight-gradient GEMM adds into them, LayerNorm and embedding gradients likewise).  Every accumulated gradient must
+    stay within the fp16 bound of the fp32 oracle's sum, every per-micro-batch loss within 1e-3, and nothing may
+    overflow."""
+    from blackriver_b200 import finetune
+    H, heads, V, L, B, T, M = 128, 2, 512, 2, 2, 96, 16
+    scale = 1024.0
+    mbs = finetune.make_microbatches(M, B, T, V, 30, seed=21)
+    tr = finetune.Trainer(H, heads, V, L, B, T, n_micro=M, rank=0, world=1, seed=13, init_std=0.05, loss_scale=scale, logits_rows=80)
+    try:
+        env = tr.env
+        main_names, p_main, layers = read_params(env, L)
+        tr.begin_step(mbs)
+        for i in range(len(tr.tasks)):
+            tr.run_task(i)
+        tr.check_and_read_losses()               # synchronises; the optimizer is NOT applied, the gradients stay
+        sum_main = {k: 0.0 for k in main_names}
+        sum_layers = [{k + "_g": 0.0 for k in orc.LAYER_PARAMS} for _ in range(L)]
+        for j, (ids, mask, lens) in enumerate(mbs):
+            loss_ref, gmain, glayers = oracle_model(p_main, layers, ids, mask, heads)
+            assert abs(tr.losses[j] - loss_ref) <= 1e-3 * abs(loss_ref), j
+            for k in main_names:
+                sum_main[k] = sum_main[k] + gmain[k]
+            for i in range(L):
+                for k in sum_layers[i]:
+                    sum_layers[i][k] = sum_layers[i][k] + glayers[i][k]
+        env.change(0)
+        for k in main_names:
+            got = env.read(k + "_g").astype(np.float32)
+            assert np.isfinite(got).all(), k
+            assert relerr(got / scale, sum_main[k]) <= 2e-2, k
+        for i in range(1, L + 1):
+            env.change(i)
+            for k in orc.LAYER_PARAMS:
+                got = env.read(k + "_g").astype(np.float32)
+                assert np.isfinite(got).all(), (i, k)
+                assert relerr(got / scale, sum_layers[i - 1][k + "_g"]) <= 2e-2, (i, k)
+        env.change(0)
+    finally:
+        tr.close()
+
+
+def test_prefill_at_2048_tokens(host):
+    """The long-context prefill shape: 2048 positions, head dimension 128, no padding, per-token NLL against the oracle."""
+    from blackriver_b200 import finetune
+    H, heads, V, L, B, T = 128, 1, 512, 1, 1, 2048
+    rng = np.random.default_rng(6)
+    ids = rng.integers(0, V, (B, T)).astype(np.int32)
+    mask = np.ones((B, T), np.int32)
+    mbs = [(ids, mask, np.array([T], np.int32))]
+    tr = finetune.Trainer(H, heads, V, L, B, T, n_micro=1, rank=0, world=1, seed=17, init_std=0.05, logits_rows=512)
+    try:
+        env = tr.env
+        main_names, p_main, layers = read_params(env, L)
+        (nll, mean), = tr.score(mbs)
+        x = orc.embedding_gather(p_main["word_embeddings.weight"], ids)
+        h, _, _ = orc.layernorm(x, p_main["word_embeddings_layernorm.weight"], p_main["word_embeddings_layernorm.bias"], 1e-5)
+        al = orc.alibi(heads, T); xm = orc.build_xmask(mask)
+        for p in layers:
+            h, _ = orc.layer_forward(h, p, al, xm, heads, 1e-5)
+        xf, _, _ = orc.layernorm(h, p_main["ln_f.weight"], p_main["ln_f.bias"], 1e-5)
+        tg, items = orc.loss_targets(ids, mask)
+        assert items == T - 1
+        logits = xf.reshape(B * T, H) @ p_main["word_embeddings.weight"].T
+        total, row_loss, _ = orc.logsoftmax_nll(logits, tg.reshape(-1))
+        assert nll.shape == (B, T) and nll[0, T - 1] == 0          # the last position has no target
+        assert relerr(nll, row_loss.reshape(B, T)) <= 2e-2
+        assert abs(mean - total / items) <= 1e-3 * abs(total / items)
+    finally:
+        tr.close()
+
+
 def test_prefill_token_nll(host):
     """Forward-only scoring (the long-context prefill configuration at test size): per-token next-token NLL from the
     words path against the fp32 oracle; full-length and padded sequences; the logits band is smaller than the batch."""

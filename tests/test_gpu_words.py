@@ -199,3 +199,105 @@ def test_loss_backward_word(host):
         assert relerr(env.read("ln_f.weight_g"), dg_ref) <= TOL32 and relerr(env.read("ln_f.bias_g"), db_ref) <= TOL32
     finally:
         env.close()
+
+
+def test_async_loss_word_matches_the_blocking_one(host):
+    """op.loss_backward_async (no host round trip: the count of targets, the gradient factor and the mean loss stay on
+    the device) against the oracle, with the weight gradient taken at once and deferred to op.loss_backward_w."""
+    rng = np.random.default_rng(8)
+    B, T, H, V = 2, 24, 64, 520
+    x = (0.5 * rng.standard_normal((B, T, H))).astype(np.float32)
+    w = (0.3 * rng.standard_normal((V, H))).astype(np.float32)
+    ids = rng.integers(0, V, (B, T)).astype(np.int32)
+    mask = np.zeros((B, T), np.int32); mask[0, :24] = 1; mask[1, :9] = 1
+    wg0 = rng.standard_normal((V, H)).astype(np.float32)
+    loss_ref, xg_ref, wg_ref = orc.loss_backward(x, ids, mask, w, w_g=wg0.copy())
+    env = host.Env(1)
+    try:
+        env.execute(f'{B} {T} {H} 3 "cuda" "float" op.create "x" !  {B} {T} {H} 3 "cuda" "float" op.create "x_g" !')
+        env.execute(f'{V} {H} 2 "cuda" "float" op.create "w" !  {V} {H} 2 "cuda" "float" op.create "w_g" !')
+        env.execute(f'{B} {T} 2 "cuda" "int" op.create "ids" !  {B} {T} 2 "cuda" "int" op.create "mask" !  1 1 "cuda" "float" op.create "loss" !')
+        env.execute(f'{B * T} {V} 2 "cuda" "float" op.create "band_all" !  7 {V} 2 "cuda" "float" op.create "band_7" !')
+        env.write("x", x); env.write("w", w); env.write("ids", ids); env.write("mask", mask)
+        for band, defer in (("band_7", 0), ("band_all", 0), ("band_all", 1)):
+            env.write("w_g", wg0); env.write("loss", np.zeros(1, np.float32))
+            env.execute(f'"x" @ "ids" @ "mask" @ "w" @ "{band}" @ "x_g" @ "w_g" @ "loss" @ {defer} op.loss_backward_async op.sync')
+            assert abs(float(env.read("loss")[0]) - loss_ref) <= TOL32 * abs(loss_ref)
+            assert relerr(env.read("x_g"), xg_ref) <= TOL32
+            if defer:
+                assert np.array_equal(env.read("w_g"), wg0)                    # untouched until the deferred pass
+                env.execute(f'"{band}" @ "x" @ "w_g" @ op.loss_backward_w op.sync')
+            assert relerr(env.read("w_g"), wg_ref) <= TOL32
+        # all positions masked out: zero loss, zero gradients, nothing divided by zero
+        env.write("mask", np.zeros((B, T), np.int32)); env.write("w_g", wg0)
+        env.execute('"x" @ "ids" @ "mask" @ "w" @ "band_all" @ "x_g" @ "w_g" @ "loss" @ 0 op.loss_backward_async op.sync')
+        assert float(env.read("loss")[0]) == 0.0 and not env.read("x_g").any() and np.array_equal(env.read("w_g"), wg0)
+    finally:
+        env.close()
+
+
+def test_split_linear_backward_equals_the_whole(host):
+    rng = np.random.default_rng(9)
+    n, i, o = 48, 64, 96
+    env = host.Env(1)
+    try:
+        for name, shape in (("dy", (n, o)), ("x", (n, i)), ("w", (o, i)), ("b", (o,)), ("xg1", (n, i)), ("xg2", (n, i)), ("wg1", (o, i)),
+                            ("wg2", (o, i)), ("bg1", (o,)), ("bg2", (o,))):
+            env.execute(" ".join(str(d) for d in shape) + f' {len(shape)} "cuda" "float" op.create "{name}" !')
+        for name in ("dy", "x", "w", "b"):
+            env.write(name, rng.standard_normal(env.tensor_info(name)["shape"]).astype(np.float32))
+        env.execute('"dy" @ "x" @ "w" @ "b" @ "xg1" @ "wg1" @ "bg1" @ op.linear_backward')
+        env.execute('"dy" @ "w" @ "xg2" @ op.linear_backward_x  "dy" @ "x" @ "wg2" @ "bg2" @ op.linear_backward_w  op.sync')
+        for a, b in (("xg1", "xg2"), ("wg1", "wg2"), ("bg1", "bg2")):
+            assert np.array_equal(env.read(a), env.read(b))
+        xg_ref, wg_ref, bg_ref = orc.linear_backward(env.read("dy"), env.read("x"), env.read("w"))
+        assert relerr(env.read("xg2"), xg_ref) <= TOL32 and relerr(env.read("wg2"), wg_ref) <= TOL32 and relerr(env.read("bg2"), bg_ref) <= TOL32
+    finally:
+        env.close()
+
+
+def test_last_logits_on_the_device(host):
+    """op.last_logits (blackriver/cuda_tensor.cpp:415-462): the row before the first padded position, and -- the
+    reference's rule for a row without padding -- token 0; fp32 and fp16 tensors against the oracle."""
+    rng = np.random.default_rng(10)
+    B, T, H, V = 3, 16, 64, 200
+    x = rng.standard_normal((B, T, H)).astype(np.float32)
+    w = (0.2 * rng.standard_normal((V, H))).astype(np.float32)
+    mask = np.zeros((B, T), np.int32); mask[0, :5] = 1; mask[1, :] = 1; mask[2, :1] = 1
+    ref = orc.last_logits(x, mask, w)
+    assert np.allclose(ref[1], x[1, 0] @ w.T, atol=1e-4)                     # a full row reads token 0, as the reference does
+    assert np.allclose(ref[0], x[0, 4] @ w.T, atol=1e-4)
+    env = host.Env(1)
+    try:
+        env.execute(f'{B} {T} 2 "cpu" "int" op.create "mask" !')
+        env.write("mask", mask)
+        for dt, tol in (("float", TOL32), ("half", 2e-2)):
+            env.execute(f'{B} {T} {H} 3 "cuda" "{dt}" op.create "x" !  {V} {H} 2 "cuda" "{dt}" op.create "w" !  {B} {V} 2 "cuda" "{dt}" op.create "out" !')
+            env.write("x", x); env.write("w", w)
+            env.execute('"x" @ "mask" @ "w" @ "out" @ op.last_logits op.sync')
+            xr, wr = env.read("x").astype(np.float32), env.read("w").astype(np.float32)
+            assert relerr(env.read("out"), orc.last_logits(xr, mask, wr)) <= tol, dt
+    finally:
+        env.close()
+
+
+def test_device_save_and_load_round_trip(host, tmp_path):
+    """io.save / io.load of device tensors (blackriver/cuda_tensor.cpp:57-72): raw little-endian files; an fp16 tensor
+    also accepts an fp32 file of the same element count, as the weight dumps are fp32."""
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((6, 40)).astype(np.float32)
+    env = host.Env(1)
+    try:
+        env.execute('6 40 2 "cuda" "float" op.create "f" !  6 40 2 "cuda" "float" op.create "f2" !')
+        env.execute('6 40 2 "cuda" "half" op.create "h" !  6 40 2 "cuda" "half" op.create "h2" !')
+        env.write("f", a); env.write("h", a)
+        pf, ph = str(tmp_path / "f.bin"), str(tmp_path / "h.bin")
+        env.execute(f'"f" @ "{pf}" io.save  "h" @ "{ph}" io.save')
+        assert np.array_equal(np.fromfile(pf, np.float32).reshape(6, 40), a)
+        assert np.array_equal(np.fromfile(ph, np.float16).reshape(6, 40), a.astype(np.float16))
+        env.execute(f'"f2" @ "{pf}" io.load  "h2" @ "{ph}" io.load op.sync')
+        assert np.array_equal(env.read("f2"), a) and np.array_equal(env.read("h2"), a.astype(np.float16))
+        env.execute(f'"h2" @ op.zero  "h2" @ "{pf}" io.load op.sync')              # fp32 file into an fp16 tensor
+        assert np.array_equal(env.read("h2"), a.astype(np.float16))
+    finally:
+        env.close()

@@ -11,10 +11,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "pipeline_worker.py")
 
 
-def launch(world, backend, out_path, port, head_cost=0.5):
+def launch(world, backend, out_path, port, head_cost=0.5, overlap=True):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), WORKER, backend, out_path]
-    env = dict(os.environ, OMP_NUM_THREADS="2", BR_TEST_HEAD_COST=str(head_cost))
+    env = dict(os.environ, OMP_NUM_THREADS="2", BR_TEST_HEAD_COST=str(head_cost), BR_TEST_OVERLAP="1" if overlap else "0")
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return json.load(open(out_path))
@@ -52,18 +52,22 @@ def check_against_single(res):
 
 
 @pytest.mark.gpu
-def test_two_stage_pipeline_matches_single_gpu(tmp_path):
+@pytest.mark.parametrize("overlap", [True, False])
+def test_two_stage_pipeline_matches_single_gpu(tmp_path, overlap):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    check_against_single(launch(2, "nccl", str(tmp_path / "out.json"), 29531))
+    res = launch(2, "nccl", str(tmp_path / "out.json"), 29531 + int(overlap), overlap=overlap)
+    assert res["overlap"] == overlap
+    check_against_single(res)
 
 
 @pytest.mark.gpu
-def test_pipeline_with_head_only_last_stage(tmp_path):
+@pytest.mark.parametrize("overlap", [True, False])
+def test_pipeline_with_head_only_last_stage(tmp_path, overlap):
     import torch
     if torch.cuda.device_count() < 3:
         pytest.skip("needs three GPUs")
-    res = launch(3, "nccl", str(tmp_path / "out.json"), 29533, head_cost=2.5)
-    assert res["counts"] == [2, 2, 0]
+    res = launch(3, "nccl", str(tmp_path / "out.json"), 29535 + int(overlap), head_cost=2.5, overlap=overlap)
+    assert res["counts"] == [2, 2, 0] and res["overlap"] == overlap
     check_against_single(res)
