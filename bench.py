@@ -17,7 +17,7 @@ step, the tcgen05 GEMM: FLOPs of all GEMM launches of one step / their summed CU
 measured bf16 tensor peak.  `kernels` adds the HBM-bound operator microbench (`--workload ops`:
 fp16, 8192 tokens, LayerNorm / GELU / log-softmax+NLL) in GB/s against the measured HBM peak.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload finetune|ops]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload finetune|ops|c3|prefill]
 """
 import argparse
 import json
@@ -374,6 +374,17 @@ FT_WORKLOAD = ("BLOOM-7b1-architecture fine-tune step, random init: 30 layers, h
                "stages over the GPUs")
 
 
+# The other single-step configurations of the same model: one micro-batch of batch 4 x seq 512 on one GPU, and the
+# forward-only long-context prefill (8 sequences of 2048 tokens, no padding, per-token NLL), one sequence per micro-batch.
+C3 = dict(hidden=4096, heads=32, vocab=VOCAB, n_layers=30, batch=4, tokens=512, n_micro=1, min_len=256, seed=2)
+C3_WORKLOAD = ("BLOOM-7b1-architecture fine-tune step, random init, on one GPU: batch 4 x seq 512 (2048 tokens/step), right padding "
+               "with lengths U[256,512], seed 2; fp16 weights/activations, fp32 master weights + Adam")
+PREFILL = dict(hidden=4096, heads=32, vocab=VOCAB, n_layers=30, batch=1, tokens=2048, n_micro=8, min_len=2048, seed=4)
+PREFILL_WORKLOAD = ("BLOOM-7b1-architecture forward-only long-context prefill, fp16: batch 8 x seq 2048 (16384 tokens/pass), no "
+                    "padding, ALiBi causal, per-token NLL against the shifted inputs over the 250880-way head, seed 4; one "
+                    "sequence per micro-batch through contiguous pipeline stages")
+
+
 def load_tensor_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -397,7 +408,8 @@ def run_finetune(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    cfg = dict(FT)
+    cfg = dict(C3 if args.workload == "c3" else FT)
+    workload_text = C3_WORKLOAD if args.workload == "c3" else FT_WORKLOAD
     if args.layers:
         cfg["n_layers"] = args.layers
     if args.micro:
@@ -405,7 +417,7 @@ def run_finetune(args):
 
     # the HBM-bound operator microbench first (its buffers are released before the model is built)
     ops_line = None
-    if not args.skip_ops and world == 1:
+    if not args.skip_ops and world == 1 and args.workload == "finetune":
         ops_args = argparse.Namespace(steps=50, warmup=3)
         ops_line = run_ops(ops_args, emit=False)
 
@@ -509,7 +521,7 @@ def run_finetune(args):
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate, f32 master weights",
             "data": "synthetic",
-            "config": {"workload": FT_WORKLOAD, "layers": cfg["n_layers"], "micro_batches": cfg["n_micro"],
+            "config": {"workload": workload_text, "layers": cfg["n_layers"], "micro_batches": cfg["n_micro"],
                        "tokens_per_step": tokens_per_step, "valid_tokens_per_step": valid_per_step,
                        "parallelism": "pp%d" % world, "stage_layers": tr.counts, "schedule": schedule_name, "slots": tr.n_slots,
                        "l2": "inputs larger than L2: per step every kernel streams >= 14 GB of weights and activations between re-uses"},
@@ -531,6 +543,108 @@ def run_finetune(args):
             "cpu_baseline": cpu_baseline_finetune() if world == 1 else None, "loss": None if loss is None else round(loss, 4),
         }
         emit_line(out)
+    tr.close()
+    if world > 1:
+        host.collective_shutdown()
+        dist.destroy_process_group()
+
+
+def run_prefill(args):
+    """Forward-only scoring of 8 x 2048 tokens: one pass = every sequence through all stages and the head, per-token NLL
+    read back on the rank that holds the head."""
+    import torch
+    import torch.distributed as dist
+    from blackriver_b200 import finetune, host
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = dict(PREFILL)
+    if args.layers:
+        cfg["n_layers"] = args.layers
+    host.context_boot(local, torch.cuda.current_stream().cuda_stream, 512 << 20)
+    if world > 1:
+        box = [host.collective_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        host.collective_boot(rank, world, box[0])
+    else:
+        host.collective_boot_local(0, 1)
+    tr = finetune.Trainer(cfg["hidden"], cfg["heads"], cfg["vocab"], cfg["n_layers"], cfg["batch"], cfg["tokens"], cfg["n_micro"],
+                          rank=rank, world=world, seed=cfg["seed"], logits_rows=cfg["batch"] * cfg["tokens"],
+                          overlap=not args.no_overlap, n_slots=4)
+    mbs = finetune.make_microbatches(cfg["n_micro"], cfg["batch"], cfg["tokens"], cfg["vocab"], cfg["min_len"], cfg["seed"])
+    tokens_per_pass = cfg["n_micro"] * cfg["batch"] * cfg["tokens"]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    out = None
+    for _ in range(args.warmup):
+        out = tr.score(mbs)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    t0w = time.time()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = tr.score(mbs)
+    tr.sync()
+    e1.record()
+    barrier()
+    t1w = time.time()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop(t0w, t1w) if rank == 0 else None
+    host.profile_start()
+    tr.score(mbs)
+    prof = host.profile_stop()
+    barrier()
+    mean_nll = float(sum(m for _, m in out) / len(out)) if out else None
+    if world > 1:
+        t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t[0])
+        box = [mean_nll]
+        dist.broadcast_object_list(box, src=world - 1)
+        mean_nll = box[0]
+    if rank == 0:
+        ms = ms_total / args.steps
+        value = tokens_per_pass / (ms * 1e-3)
+        peak_tf, peak_src = load_tensor_peak()
+        n, H, V = cfg["batch"] * cfg["tokens"], cfg["hidden"], cfg["vocab"]
+        flops = cfg["n_micro"] * (tr.counts[0] * 2 * n * 12 * H * H + (2 * n * H * V if world == 1 else 0))
+        gemm_ms = prof.get("gemm_f16", {}).get("ms", 0.0)
+        achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+        # the scoring pass reads every micro-batch's per-token NLL back, so the timed region already is the end-to-end one
+        h2d = sum(finetune.pack_inputs(m).nbytes for m in mbs)
+        d2h = tokens_per_pass * 4
+        emit_line({
+            "metric": "tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+            "config": {"workload": PREFILL_WORKLOAD, "layers": cfg["n_layers"], "micro_batches": cfg["n_micro"],
+                       "tokens_per_step": tokens_per_pass, "parallelism": "pp%d" % world, "stage_layers": tr.counts,
+                       "l2": "inputs larger than L2: every pass streams the stage's weights (>= 1.7 GB per GPU) between re-uses"},
+            "clocks": clocks, "gpu_launches": sum(v["calls"] for v in prof.values()) * args.steps,
+            "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "roofline": {"kernel": "gemm_tc_pair_kernel (forward GEMMs of rank 0's stage in one pass)", "bound": "tensor",
+                         "achieved": None if achieved is None else round(achieved, 1), "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": None if achieved is None else round(achieved / peak_tf, 3), "peak_source": peak_src, "traffic": None},
+            "step_profile_ms": {k: {"ms": round(v["ms"], 3), "calls": v["calls"]} for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"])},
+            "cpu_baseline": None, "mean_nll": None if mean_nll is None else round(mean_nll, 4),
+        })
     tr.close()
     if world > 1:
         host.collective_shutdown()
@@ -583,6 +697,7 @@ def cpu_head_seconds_per_token(np, orc, rng, tokens=2):
 def cpu_baseline_finetune():
     import numpy as np
     from oracle import oracle as orc
+    orc.use_all_cores()
     rng = np.random.default_rng(FT["seed"])
     parts = cpu_finetune_parts(np, orc, FT_CPU_LAYER_TOKENS, rng)
     t_layer = min(cpu_layer_seconds(orc, parts) for _ in range(2))
@@ -726,6 +841,7 @@ def run_reference(args):
         return
     import numpy as np
     from oracle import oracle as orc
+    orc.use_all_cores()          # the launcher of a multi-rank run exports OMP_NUM_THREADS=1; the CPU arm uses every core
     if args.workload == "ops":
         rng = np.random.default_rng(SEED)
         inputs = cpu_inputs(np, CPU_SAMPLE_TOKENS, rng)
@@ -789,7 +905,9 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="finetune", choices=["finetune", "ops"])
+    ap.add_argument("--workload", default="finetune", choices=["finetune", "ops", "c3", "prefill"],
+                    help="finetune: the headline step (16 micro-batches of 2 x 1024); ops: the operator microbench; c3: one "
+                         "micro-batch of 4 x 512 on one GPU; prefill: forward-only scoring of 8 x 2048 tokens")
     ap.add_argument("--layers", type=int, default=0, help="fine-tune workload with fewer layers (development aid)")
     ap.add_argument("--micro", type=int, default=0, help="fine-tune workload with fewer micro-batches (development aid)")
     ap.add_argument("--no-overlap", action="store_true",
@@ -800,7 +918,7 @@ def main():
     ap.add_argument("--rows", type=int, default=1024, help="rows of the --case run")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = 5 if args.workload == "finetune" else 200
+        args.steps = 200 if args.workload == "ops" else 5
     if args.case:
         return run_case(args)
     if args.warmup < 3 and args.impl == "ours":
@@ -809,6 +927,8 @@ def main():
         run_reference(args)
     elif args.workload == "ops":
         run_ops(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_finetune(args)
 

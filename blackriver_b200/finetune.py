@@ -208,6 +208,18 @@ class Trainer:
                 out.append((nll, host.last_loss()))
         return out
 
+    def save(self, prefix):
+        """Checkpoint of this stage: fp32 master weights in the reference's per-tensor raw files plus the Adam moments
+        (the words save_model writes them); the step count goes to <prefix>step.<rank>.txt."""
+        self.env.execute(f'op.sync "{prefix}" save_model op.sync')
+        with open(f"{prefix}step.{self.rank}.txt", "w") as f:
+            f.write(str(self.step_no))
+
+    def load(self, prefix):
+        self.env.execute(f'op.sync "{prefix}" load_model op.sync')
+        with open(f"{prefix}step.{self.rank}.txt") as f:
+            self.step_no = int(f.read().strip())
+
     def sync(self):
         self.env.run(self.p_sync)
 

@@ -291,7 +291,7 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w("%def create_layer_fused")      # runs inside a layer's hash table, so sizes and types are spelled out
     for suffix, dt in (("", dtype), ("_g", dtype), (".master", "float"), (".m", "float"), (".v", "float")):
         w(f'    {flat} 1 "cuda" "{dt}" op.create "_flat{suffix}" !')
-    for suffix in ("", "_g"):
+    for suffix in ("", "_g", ".master"):          # the fp32 master views are what a checkpoint stores, tensor by tensor
         for name, shape, off, cnt in layout:
             dims = " ".join(str(d) for d in shape)
             w(f'    "_flat{suffix}" @ {off} {dims} {len(shape)} op.view "{name}{suffix}" !')
@@ -646,6 +646,35 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         if prev_rank is not None:
             w(f'    0 # "stage_in_g" @ {prev_rank} io.nccl.send')
         w("%end")
+    # ---- checkpoint: ( prefix -- ) save_model / load_model ----
+    # Weights go out as the reference stores them, one raw fp32 file per tensor named <prefix>h<layer>.<tensor>.bin and
+    # <prefix><tensor>.bin (bloomz-7b/init.words:120-235, bloomz-7b/dump_weights.py:105-133; the fused QKV weight keeps this build's [q rows | k rows | v rows]
+    # order), taken from the fp32 master copies; the Adam moments follow as <prefix>h<layer>._flat.m.bin / .v.bin and
+    # <prefix><tensor>.m.bin / .v.bin.  Loading fills master, moments and the fp16 working copy.  The tied table is
+    # written by the first stage only and read by both of its holders.
+    for word, io in (("save_model", "io.save"), ("load_model", "io.load")):
+        w(f"%def {word}")
+        w('    0 # "ckpt_" !')
+        for name, _ in main_params:
+            if word == "save_model" and name == "word_embeddings.weight" and not first_stage:
+                continue
+            for suffix, ext in ((".master", ""), (".m", ".m"), (".v", ".v")):
+                w(f'    "{name}{suffix}" @ "ckpt_" @ "{name}{ext}.bin" | {io}')
+            if word == "load_model":
+                w(f'    "{name}" @ "{name}.master" @ op.copy')
+        for i in range(1, n_layers + 1):
+            gi = layer_offset + i - 1
+            w(f'    0 # "ckpt_" @ {i} # "ckpt_" !')
+            for name, shape, off, cnt in layout:
+                w(f'    "{name}.master" @ "ckpt_" @ "h{gi}.{name}.bin" | {io}')
+            for ext in ("m", "v"):
+                w(f'    "_flat.{ext}" @ "ckpt_" @ "h{gi}._flat.{ext}.bin" | {io}')
+            if word == "load_model":
+                w('    "_flat" @ "_flat.master" @ op.copy')
+            w('    "ckpt_" !!')
+        w('    0 # "ckpt_" !!')
+        w("%end")
+
     # ( peer -- )  both holders of the tied embedding / LM-head table sum their gradients
     w("%def sync_tied_grads")
     w('    0 # "peer_" !')

@@ -46,6 +46,15 @@ ORC_API int orc_num_threads(void) {
 #endif
 }
 
+/* Threads for the timed CPU baseline: a launcher may have exported OMP_NUM_THREADS=1 for its workers. */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------------- */
 /* LayerNorm.  cuda_tensor.cpp:236-255 -> normalize_kernels.cu:40-85.          */
 /* y = (x-mu)*rsqrt(v)*gamma+beta, mean[row]=mu, var[row]=sigma^2+eps.          */

@@ -41,6 +41,14 @@ def num_threads():
     return int(lib().orc_num_threads())
 
 
+def use_all_cores():
+    """OpenMP threads = the cores this process may run on, whatever OMP_NUM_THREADS a launcher exported
+    (torch.distributed.run sets it to 1 for its workers).  Returns the count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads(C.c_int(n))
+    return num_threads()
+
+
 def _f(a):
     a = np.ascontiguousarray(a, dtype=np.float32)
     return a

@@ -292,3 +292,39 @@ def test_embedding_scatter_add():
     ddx, dids = torch.from_numpy(dx).cuda(), torch.from_numpy(ids).cuda()      # keep both alive across the call
     brk.call("brk_embedding_scatter_add", ddx.data_ptr(), dids.data_ptr(), tg.data_ptr(), n, H, V, brk.F32, ops.stream())
     np.testing.assert_allclose(tg.cpu().numpy(), ref, rtol=1e-5, atol=1e-5)
+
+
+def test_checkpoint_resume_continues_the_same_run(host, tmp_path):
+    """save_model / load_model: master weights in the reference's per-tensor raw fp32 files plus the Adam moments.
+    Two steps, save, one more step -- against a differently initialised trainer that loads the checkpoint and takes
+    the same third step: same loss, same weights."""
+    from blackriver_b200 import finetune
+    H, heads, V, L, B, T, M = 128, 2, 512, 2, 2, 64, 2
+    mbs = finetune.make_microbatches(M, B, T, V, 20, seed=3)
+    prefix = str(tmp_path) + "/ck_"
+    a = finetune.Trainer(H, heads, V, L, B, T, n_micro=M, seed=31, init_std=0.05, lr=1e-3)
+    try:
+        a.step(mbs); a.step(mbs)
+        a.save(prefix)
+        loss_a = a.step(mbs)
+        a.sync()
+        a.env.change(2); wa = a.env.read("_flat.master").copy(); ma = a.env.read("_flat.m").copy()
+        a.env.change(0); ta = a.env.read("word_embeddings.weight").copy()
+    finally:
+        a.close()
+    # the files carry the reference's names and plain fp32 contents
+    w = np.fromfile(prefix + "h1.dense_h_to_4h.weight.bin", np.float32)
+    assert w.size == 4 * H * H and abs(w.std() - 0.05) < 0.01
+    assert np.fromfile(prefix + "word_embeddings.weight.bin", np.float32).size == V * H
+    b = finetune.Trainer(H, heads, V, L, B, T, n_micro=M, seed=77, init_std=0.02, lr=1e-3)
+    try:
+        b.load(prefix)
+        assert b.step_no == 2
+        loss_b = b.step(mbs)
+        b.sync()
+        b.env.change(2); wb = b.env.read("_flat.master").copy(); mb_ = b.env.read("_flat.m").copy()
+        b.env.change(0); tb = b.env.read("word_embeddings.weight").copy()
+    finally:
+        b.close()
+    assert loss_a == loss_b
+    assert np.array_equal(wa, wb) and np.array_equal(ma, mb_) and np.array_equal(ta, tb)
