@@ -457,8 +457,10 @@ def run_finetune(args):
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
+    trace = []
     for _ in range(args.steps):
         loss = tr.step(mbs)
+        trace.append(loss)
     e1.record()
     barrier()
     t1w = time.time()
@@ -489,9 +491,9 @@ def run_finetune(args):
         t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total, ms_e2e = float(t[0]), float(t[1])
-        box = [loss]
+        box = [loss, trace]
         dist.broadcast_object_list(box, src=world - 1)
-        loss = box[0]
+        loss, trace = box
 
     if world == 1:
         schedule_name = "forward + backward per micro-batch"
@@ -541,6 +543,8 @@ def run_finetune(args):
             "ops_microbench": None if ops_line is None else {"value": ops_line["value"], "unit": "tokens/s",
                                                              "roofline": ops_line["roofline"]},
             "cpu_baseline": cpu_baseline_finetune() if world == 1 else None, "loss": None if loss is None else round(loss, 4),
+            # mean loss of every timed step (they follow the warm-up steps): equal across GPU counts for equal --warmup / --steps
+            "loss_trace": [None if v is None else round(v, 4) for v in trace],
         }
         emit_line(out)
     tr.close()

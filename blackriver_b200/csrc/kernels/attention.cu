@@ -13,11 +13,14 @@
 //   warp 0     TMA producer (Q once, then K / V tiles of 128 keys through 2-stage rings);
 //   warp 1     issues tcgen05.mma: S = Q K_j^T into one of two TMEM score buffers, O += P V_j;
 //   warps 2-5  one thread per query row: tcgen05.ld the scores, mask, exponentiate, write P as
-//              fp16 into shared memory in the tensor core's swizzled operand layout.
-// Softmax is two-sweep: sweep A accumulates the row maximum and normaliser over all key blocks,
-// sweep B recomputes the scores and feeds normalised probabilities to the second contraction, so
-// the output accumulator in TMEM never needs rescaling.  The score contraction runs twice; it is
-// a third of the attention FLOPs, which are a few per cent of a decoder layer.
+//              fp16 into one of two shared-memory tiles in the tensor core's swizzled operand layout.
+// Softmax is online, in one sweep over the key blocks: each score and each exponential is computed
+// once.  Probabilities are taken relative to a per-row reference maximum that moves only when the
+// running maximum has run ahead of it by 2^8; only then is the output accumulator in tensor memory
+// rescaled (read, multiplied, written back between two P V products), which after the first blocks
+// of a row is rare.  The normaliser is applied once, in the epilogue.  With two score buffers and
+// two probability tiles the tensor core computes S(j+1) and O += P(j-1) V while the row owners
+// exponentiate block j.
 // Every mbarrier wait is bounded (see brk_ptx.cuh); a give-up raises g_attn_error.
 #include <mutex>
 
@@ -51,14 +54,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     constexpr uint32_t TMEM_COLS = 512;                   // S0 [0,128) S1 [128,256) O [256,256+D)
     constexpr uint32_t IDESC_S = make_idesc_f16_f32(128, AT_BKV, 0, 0);
     constexpr uint32_t IDESC_PV = make_idesc_f16_f32(128, D, 0, 1);
+    constexpr float RESCALE_STEP = 8.0f;                  // log2 units the row maximum may run ahead of the reference
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = base;
     unsigned char* sK = sQ + TILE_BYTES;
     unsigned char* sV = sK + KSTAGES * TILE_BYTES;
-    unsigned char* sP = sV + VSTAGES * TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+    unsigned char* sP = sV + VSTAGES * TILE_BYTES;        // two probability tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * P_BYTES);
     uint64_t* q_full = bars;                 // 1
     uint64_t* k_full = bars + 1;             // KSTAGES
     uint64_t* k_empty = k_full + KSTAGES;
@@ -66,9 +70,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     uint64_t* v_empty = v_full + VSTAGES;
     uint64_t* s_full = v_empty + VSTAGES;    // 2
     uint64_t* s_empty = s_full + 2;          // 2
-    uint64_t* p_full = s_empty + 2;          // 1
-    uint64_t* p_empty = p_full + 1;          // 1
-    uint64_t* o_full = p_empty + 1;          // 1
+    uint64_t* p_full = s_empty + 2;          // 2
+    uint64_t* p_empty = p_full + 2;          // 2
+    uint64_t* o_full = p_empty + 2;          // 1
     uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(o_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -86,9 +90,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         mbar_init(q_full, 1);
         for (int s = 0; s < KSTAGES; s++) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
         for (int s = 0; s < VSTAGES; s++) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-        for (int s = 0; s < 2; s++) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128); }
-        mbar_init(p_full, 128);
-        mbar_init(p_empty, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&s_full[s], 1);
+            mbar_init(&s_empty[s], 128);
+            mbar_init(&p_full[s], 128);
+            mbar_init(&p_empty[s], 1);
+        }
         mbar_init(o_full, 1);
         fence_barrier_init();
         prefetch_tensormap(&tmap_q);
@@ -113,30 +120,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 mbar_arrive_expect_tx(q_full, TILE_BYTES);
 #pragma unroll
                 for (int a = 0; a < D / 64; a++) tma_load_2d(sQ + a * 16384, &tmap_q, q_full, col + a * 64, row_base + q0);
-                uint32_t kit = 0, vit = 0;
-                for (int sweep = 0; sweep < 2 && ok; sweep++) {
-                    for (int j = 0; j < nkb && ok; j++) {
-                        {
-                            const int s = kit % KSTAGES;
-                            ok = mbar_wait(&k_empty[s], ((kit / KSTAGES) & 1) ^ 1);
-                            if (!ok) break;
-                            mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
+                for (int j = 0; j < nkb && ok; j++) {
+                    const int s = j % KSTAGES;
+                    ok = mbar_wait(&k_empty[s], ((j / KSTAGES) & 1) ^ 1);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&k_full[s], TILE_BYTES);
 #pragma unroll
-                            for (int a = 0; a < D / 64; a++)
-                                tma_load_2d(sK + s * TILE_BYTES + a * 16384, &tmap_k, &k_full[s], col + a * 64, row_base + j * AT_BKV);
-                            kit++;
-                        }
-                        if (sweep == 1) {
-                            const int s = vit % VSTAGES;
-                            ok = mbar_wait(&v_empty[s], ((vit / VSTAGES) & 1) ^ 1);
-                            if (!ok) break;
-                            mbar_arrive_expect_tx(&v_full[s], TILE_BYTES);
+                    for (int a = 0; a < D / 64; a++)
+                        tma_load_2d(sK + s * TILE_BYTES + a * 16384, &tmap_k, &k_full[s], col + a * 64, row_base + j * AT_BKV);
+                    const int sv = j % VSTAGES;
+                    ok = mbar_wait(&v_empty[sv], ((j / VSTAGES) & 1) ^ 1);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&v_full[sv], TILE_BYTES);
 #pragma unroll
-                            for (int a = 0; a < D / 64; a++)
-                                tma_load_2d(sV + s * TILE_BYTES + a * 16384, &tmap_v, &v_full[s], col + a * 64, row_base + j * AT_BKV);
-                            vit++;
-                        }
-                    }
+                    for (int a = 0; a < D / 64; a++)
+                        tma_load_2d(sV + sv * TILE_BYTES + a * 16384, &tmap_v, &v_full[sv], col + a * 64, row_base + j * AT_BKV);
                 }
                 if (!ok) atomicExch(&g_attn_error, 1);
             }
@@ -147,11 +145,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 tcgen05_fence_after();
                 const uint32_t q_addr = smem_u32(sQ);
                 const uint32_t p_addr = smem_u32(sP);
-                uint32_t kit = 0, vit = 0, sit = 0;   // K tiles consumed, V tiles consumed, score tiles produced
-                auto issue_scores = [&](void) -> bool {
-                    const int s = kit % KSTAGES, sb = sit & 1;
-                    if (!mbar_wait(&s_empty[sb], ((sit >> 1) & 1) ^ 1)) return false;
-                    if (!mbar_wait(&k_full[s], (kit / KSTAGES) & 1)) return false;
+                // S(j) = Q K_j^T into score buffer j & 1 (free once the row owners have read S(j-2))
+                auto issue_scores = [&](int j) -> bool {
+                    const int s = j % KSTAGES, sb = j & 1;
+                    if (!mbar_wait(&s_empty[sb], ((j >> 1) & 1) ^ 1)) return false;
+                    if (!mbar_wait(&k_full[s], (j / KSTAGES) & 1)) return false;
                     tcgen05_fence_after();
                     const uint32_t k_addr = smem_u32(sK + s * TILE_BYTES);
 #pragma unroll
@@ -162,90 +160,91 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     }
                     umma_commit(&k_empty[s]);
                     umma_commit(&s_full[sb]);
-                    kit++;
-                    sit++;
                     return true;
                 };
-                // sweep A: scores only
-                for (int j = 0; j < nkb && ok; j++) ok = issue_scores();
-                // sweep B: scores one block ahead of the P V contraction
-                if (ok) ok = issue_scores();
+                if (ok) ok = issue_scores(0);
                 for (int j = 0; j < nkb && ok; j++) {
-                    if (j + 1 < nkb) ok = issue_scores();
+                    if (j + 1 < nkb) ok = issue_scores(j + 1);      // the next scores run while the row owners work on S(j)
                     if (!ok) break;
-                    const int s = vit % VSTAGES;
-                    ok = mbar_wait(&v_full[s], (vit / VSTAGES) & 1) && mbar_wait(p_full, j & 1);
+                    const int s = j % VSTAGES, pb = j & 1;
+                    ok = mbar_wait(&v_full[s], (j / VSTAGES) & 1) && mbar_wait(&p_full[pb], (j >> 1) & 1);
                     if (!ok) break;
                     tcgen05_fence_after();
                     const uint32_t v_addr = smem_u32(sV + s * TILE_BYTES);
+                    const uint32_t pj = p_addr + pb * P_BYTES;
 #pragma unroll
                     for (int kk = 0; kk < AT_BKV / 16; kk++) {
                         // A = P [128 q x 128 keys], K-major; B = V [128 keys x D], d contiguous (MN-major)
-                        const uint64_t da = make_smem_desc_sw128(p_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+                        const uint64_t da = make_smem_desc_sw128(pj + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
                         const uint64_t db = make_smem_desc_sw128(v_addr + kk * 2048, 16384, 1024);
                         umma_f16_ss(tmem_o, da, db, IDESC_PV, (j | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit(&v_empty[s]);
-                    umma_commit(p_empty);
-                    vit++;
+                    umma_commit(&p_empty[pb]);
                 }
                 if (ok) umma_commit(o_full);
                 if (!ok) atomicExch(&g_attn_error, 2);
             }
         } else {
             // ---------------- softmax / epilogue: one thread per query row ----------------
+            // Online softmax in one sweep over the key blocks: probabilities are taken relative to a reference maximum
+            // m_ref that is only moved (and the output accumulator rescaled) when the running maximum has run ahead of it
+            // by more than RESCALE_STEP, so P stays within 2^RESCALE_STEP -- far inside fp16 -- and rescaling is rare.
             const int quarter = warp & 3;
             const int r = quarter * 32 + lane;          // row inside the tile == TMEM lane
             const int qi = q0 + r;                       // query position in the sequence
             const int klimit = min(qi + 1, len);         // keys [0, klimit) are visible to this row
             const float slope2 = p.slopes ? p.slopes[head] * 1.4426950408889634f : 0.0f;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            float m = -INFINITY, l = 0.0f;
-            uint32_t sit = 0;
+            float m_ref = -INFINITY, l = 0.0f;
             bool ok = true;
-            // sweep A
-            for (int j = 0; j < nkb && ok; j++, sit++) {
-                const int sb = sit & 1;
-                ok = mbar_wait(&s_full[sb], (sit >> 1) & 1);
+            for (int j = 0; j < nkb && ok; j++) {
+                const int sb = j & 1;
+                ok = mbar_wait(&s_full[sb], (j >> 1) & 1);
                 if (!ok) break;
                 tcgen05_fence_after();
+                // pass 1: the block's maximum for this row
+                float bm = -INFINITY;
 #pragma unroll 1
                 for (int c0 = 0; c0 < AT_BKV; c0 += 32) {
                     uint32_t v[32];
                     tmem_ld_32x32b_x32(lane_addr + sb * 128 + c0, v);
                     tmem_ld_wait();
                     const int kbase = j * AT_BKV + c0;
-                    float t[32];
-                    float cm = m;
 #pragma unroll
                     for (int e = 0; e < 32; e++) {
                         const int kj = kbase + e;
-                        t[e] = kj < klimit ? fmaf(__uint_as_float(v[e]), p.scale_log2, slope2 * (float)kj) : -INFINITY;
-                        cm = fmaxf(cm, t[e]);
-                    }
-                    if (cm > m) {
-                        l *= fast_exp2(m - cm);
-                        m = cm;
-                    }
-                    if (m > -INFINITY) {
-#pragma unroll
-                        for (int e = 0; e < 32; e++) l += fast_exp2(t[e] - m);
+                        if (kj < klimit) bm = fmaxf(bm, fmaf(__uint_as_float(v[e]), p.scale_log2, slope2 * (float)kj));
                     }
                 }
-                tcgen05_fence_before();
-                mbar_arrive(&s_empty[sb]);
-            }
-            const float lse2 = (l > 0.0f) ? m + __log2f(l) : 0.0f;
-            if (ok && qi < p.tokens && p.lse)
-                p.lse[((int64_t)b * p.heads + head) * p.tokens + qi] = lse2 * 0.6931471805599453f;
-            // sweep B
-            for (int j = 0; j < nkb && ok; j++, sit++) {
-                const int sb = sit & 1;
-                ok = mbar_wait(&s_full[sb], (sit >> 1) & 1);
+                const bool move = bm > m_ref + RESCALE_STEP;          // also the first visible key of the row (m_ref = -inf)
+                float factor = 1.0f;
+                if (move) {
+                    factor = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - bm);
+                    m_ref = bm;
+                    l *= factor;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, move)) {
+                    // the accumulator may only be touched between two P V products: wait for the previous one
+                    ok = mbar_wait(&p_empty[(j - 1) & 1], ((j - 1) >> 1) & 1);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(lane_addr + 256 + c0, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; e++) v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
+                        tmem_st_32x32b_x32(lane_addr + 256 + c0, v);
+                    }
+                    tmem_st_wait();
+                    tcgen05_fence_before();
+                }
+                if (j >= 2) ok = mbar_wait(&p_empty[sb], ((j - 2) >> 1) & 1);   // P tile j & 1 consumed by the tensor core
                 if (!ok) break;
-                if (j > 0) ok = mbar_wait(p_empty, (j - 1) & 1);   // previous P consumed by the tensor core
-                if (!ok) break;
-                tcgen05_fence_after();
+                unsigned char* pt = sP + sb * P_BYTES;
+                // pass 2: probabilities relative to m_ref
 #pragma unroll 1
                 for (int c0 = 0; c0 < AT_BKV; c0 += 32) {
                     uint32_t v[32];
@@ -259,22 +258,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
                             const int k0 = kbase + g * 8 + e * 2;
-                            float p0 = k0 < klimit ? fast_exp2(fmaf(__uint_as_float(v[g * 8 + e * 2]), p.scale_log2, slope2 * (float)k0) - lse2) : 0.0f;
-                            float p1 = k0 + 1 < klimit ? fast_exp2(fmaf(__uint_as_float(v[g * 8 + e * 2 + 1]), p.scale_log2, slope2 * (float)(k0 + 1)) - lse2) : 0.0f;
+                            const float p0 = k0 < klimit ? fast_exp2(fmaf(__uint_as_float(v[g * 8 + e * 2]), p.scale_log2, slope2 * (float)k0) - m_ref) : 0.0f;
+                            const float p1 = k0 + 1 < klimit ? fast_exp2(fmaf(__uint_as_float(v[g * 8 + e * 2 + 1]), p.scale_log2, slope2 * (float)(k0 + 1)) - m_ref) : 0.0f;
+                            l += p0 + p1;
                             h2[e] = __floats2half2_rn(p0, p1);
                         }
-                        *reinterpret_cast<uint4*>(sP + sw128_offset(r, c0 + g * 8)) = pk;
+                        *reinterpret_cast<uint4*>(pt + sw128_offset(r, c0 + g * 8)) = pk;
                     }
                 }
                 tcgen05_fence_before();
                 mbar_arrive(&s_empty[sb]);
                 fence_proxy_async();          // make the generic-proxy writes of P visible to the tensor core
-                mbar_arrive(p_full);
+                mbar_arrive(&p_full[sb]);
             }
-            // epilogue: O -> fp16 -> global, token-major
+            // epilogue: O / l -> fp16 -> global, token-major; log-sum-exp for the backward
             if (ok) ok = mbar_wait(o_full, 0);
             if (ok) {
                 tcgen05_fence_after();
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+                if (qi < p.tokens && p.lse)
+                    p.lse[((int64_t)b * p.heads + head) * p.tokens + qi] = l > 0.0f ? (m_ref + __log2f(l)) * 0.6931471805599453f : 0.0f;
                 __half* orow = p.out + (int64_t)(row_base + qi) * p.ld_out + col;
                 const bool vec = (p.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
 #pragma unroll 1
@@ -288,11 +291,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                             for (int g = 0; g < 4; g++) {
                                 Vec<__half> o;
 #pragma unroll
-                                for (int e = 0; e < 8; e++) o.v[e] = __uint_as_float(v[g * 8 + e]);
+                                for (int e = 0; e < 8; e++) o.v[e] = __uint_as_float(v[g * 8 + e]) * inv;
                                 o.store(orow + c0 + g * 8);
                             }
                         } else {
-                            for (int e = 0; e < 32; e++) orow[c0 + e] = __float2half_rn(__uint_as_float(v[e]));
+#pragma unroll
+                            for (int e = 0; e < 32; e++) orow[c0 + e] = __float2half_rn(__uint_as_float(v[e]) * inv);
                         }
                     }
                 }
@@ -319,7 +323,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
 template <int D>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnFwdParams& p, cudaStream_t st) {
-    constexpr size_t smem = 1024 + (size_t)128 * D * 2 * 5 + 128 * AT_BKV * 2 + 256;
+    constexpr size_t smem = 1024 + (size_t)128 * D * 2 * 5 + 2 * 128 * AT_BKV * 2 + 256;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] { attr_err = cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });

@@ -13,26 +13,19 @@ import numpy as np
 
 from . import host, schedule, words
 
-LM_HEAD_COST_IN_LAYERS = 5.9      # measured step time of final LayerNorm + 250880-way head + loss, in 7b1 decoder layers (5.1 by FLOPs)
+LM_HEAD_COST_IN_LAYERS = 4.1      # measured step time of final LayerNorm + 250880-way head + loss, in 7b1 decoder layers
 
 
-def partition_layers(n_layers, world, head_cost=LM_HEAD_COST_IN_LAYERS):
-    """Contiguous layer counts per stage.  The last stage also carries the final LayerNorm, the LM
-    head and the loss, worth `head_cost` layers, so it gets correspondingly fewer layers -- none at
-    all when the head alone already fills a stage's share (7b1 on 8 GPUs).  Picks the split whose
-    most loaded stage is lightest; every stage but the last keeps at least one layer."""
+def partition_layers(n_layers, world, head_cost=LM_HEAD_COST_IN_LAYERS, n_micro=16):
+    """Contiguous layer counts per stage.  The last stage also carries the final LayerNorm, the LM head and the loss,
+    worth `head_cost` layers, so it gets correspondingly fewer layers -- none at all when the head alone already fills
+    a stage's share (7b1 on 8 GPUs).  Among the near-even splits the one with the shortest simulated step of the
+    overlapped schedule is taken (schedule.choose_partition); every stage but the last keeps at least one layer."""
     if world == 1:
         return [n_layers]
-    best = None
-    for last in range(0, n_layers - (world - 1) + 1):
-        rest = n_layers - last
-        heaviest = max(-(-rest // (world - 1)), last + head_cost)
-        if best is None or heaviest <= best[0] + 1e-9:      # ties: more layers next to the head, fewer elsewhere
-            best = (heaviest, last)
-    last = best[1]
-    rest = n_layers - last
-    counts = [rest // (world - 1) + (1 if i < rest % (world - 1) else 0) for i in range(world - 1)]
-    return counts + [last]
+    unit = sum(schedule.LAYER_COST) * head_cost / sum(schedule.HEAD_COST)
+    head = tuple(c * unit for c in schedule.HEAD_COST)
+    return schedule.choose_partition(n_layers, world, n_micro, head_cost=head)
 
 
 def make_microbatches(n_micro, batch, tokens, vocab, min_len, seed, pad_id=3):

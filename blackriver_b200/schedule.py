@@ -24,7 +24,7 @@ from dataclasses import dataclass
 # attention backward + LayerNorm / GELU backward; weight-gradient GEMMs + column sums.  The head's forward part
 # (logits GEMM + log-softmax) is counted with its B task because it runs there.
 LAYER_COST = (0.90, 1.05, 0.80)
-HEAD_COST = (0.1, 8.6, 4.5)
+HEAD_COST = (0.1, 7.3, 3.8)
 
 
 @dataclass(frozen=True)
@@ -185,3 +185,26 @@ def n_slots_for(world, n_micro, layers_per_rank, bytes_per_layer_slot, budget_by
         return 1
     per_slot = max(1, max(layers_per_rank)) * bytes_per_layer_slot
     return int(max(2, min(n_micro, budget_bytes // max(per_slot, 1))))
+
+
+def choose_partition(n_layers, world, n_micro, n_slots=None, layer_cost=LAYER_COST, head_cost=HEAD_COST):
+    """Contiguous layer counts per rank (the last rank also carries final LayerNorm + LM head + loss and may hold no
+    layer at all) with the shortest simulated step.  Candidates: every number of layers next to the head up to an even
+    share, the other layers spread as evenly as whole layers allow, the fuller stages anywhere among the ranks."""
+    if world == 1:
+        return [n_layers]
+    from itertools import combinations
+    best = None
+    for last in range(0, n_layers // world + 2):
+        rest = n_layers - last
+        if rest < world - 1:
+            continue
+        lo, extra = divmod(rest, world - 1)
+        for where in combinations(range(world - 1), extra):
+            counts = [lo + (1 if i in where else 0) for i in range(world - 1)] + [last]
+            costs = stage_costs(counts, layer_cost, head_cost)
+            _, span = build(world, n_micro, costs, n_slots)
+            key = (round(span, 6), [-c for c in counts])          # ties: the fuller stages first
+            if best is None or key < best[0]:
+                best = (key, counts)
+    return best[1]
