@@ -511,8 +511,8 @@ def run_finetune(args):
         h2d = sum(finetune.pack_inputs(mbs[k]).nbytes for _, k in tr.tasks if k is not None)
         d2h = cfg["n_micro"] * 4 + 8
         peak_tf, peak_src = load_tensor_peak()
-        my_layers = tr.counts[0]
-        flops = cfg["n_micro"] * finetune.gemm_flops_per_microbatch(cfg["hidden"], cfg["vocab"], my_layers, cfg["batch"] * cfg["tokens"],
+        # rank 0's GEMM work in whole-layer equivalents (a stage may end between a layer's attention and MLP halves)
+        flops = cfg["n_micro"] * finetune.gemm_flops_per_microbatch(cfg["hidden"], cfg["vocab"], tr.gemm_layers, cfg["batch"] * cfg["tokens"],
                                                                   with_head=(world == 1))
         gemm_ms = prof.get("gemm_f16", {}).get("ms", 0.0)
         achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
@@ -628,7 +628,7 @@ def run_prefill(args):
         value = tokens_per_pass / (ms * 1e-3)
         peak_tf, peak_src = load_tensor_peak()
         n, H, V = cfg["batch"] * cfg["tokens"], cfg["hidden"], cfg["vocab"]
-        flops = cfg["n_micro"] * (tr.counts[0] * 2 * n * 12 * H * H + (2 * n * H * V if world == 1 else 0))
+        flops = cfg["n_micro"] * (tr.gemm_layers * 2 * n * 12 * H * H + (2 * n * H * V if world == 1 else 0))
         gemm_ms = prof.get("gemm_f16", {}).get("ms", 0.0)
         achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
         # the scoring pass reads every micro-batch's per-token NLL back, so the timed region already is the end-to-end one

@@ -52,37 +52,49 @@ class Trainer:
 
     world == 1: every micro-batch forward then backward.  world > 1 with overlap (the default): the stage's work is cut
     into forward / input-gradient / weight-gradient tasks per micro-batch, executed in the static order that
-    schedule.build lays out for this rank, with one-sided hand-offs between neighbours (io.link.*); with overlap=False
-    the plain order (all forwards, then all backwards) over NCCL send / receive on the compute stream.
+    schedule.build lays out for this rank, with one-sided hand-offs between neighbours (io.link.*), and stages may end
+    between the attention half and the MLP half of a layer (split_layers) so that the ranks carry equal shares; with
+    overlap=False the plain order (all forwards, then all backwards) over NCCL send / receive on the compute stream
+    and whole layers per stage.
     Nothing in a step waits for the device except one check before the optimizer: the status words of the tensor-core
     kernels are read (an update computed from a kernel that gave up a wait is refused) together with the losses."""
 
     def __init__(self, hidden, heads, vocab, n_layers, batch, tokens, n_micro, rank=0, world=1, dtype="half", seed=0,
                  loss_scale=1024.0, lr=1e-4, logits_rows=None, init_std=0.02, verbose=False, head_cost=LM_HEAD_COST_IN_LAYERS,
-                 overlap=None, n_slots=None, activation_budget=56 << 30, play_all_ranks=False):
+                 overlap=None, n_slots=None, activation_budget=56 << 30, play_all_ranks=False, split_layers=True):
         self.rank, self.world, self.n_micro = rank, world, n_micro
         self.batch, self.tokens = batch, tokens
         self.loss_scale, self.lr = float(loss_scale), float(lr)
-        self.counts = partition_layers(n_layers, world, head_cost)
         self.first, self.last = rank == 0, rank == world - 1
-        self.overlap = (world > 1) if overlap is None else (bool(overlap) and world > 1)
-        my_layers = self.counts[rank]
+        self.overlap = ((world > 1) if overlap is None else (bool(overlap) and world > 1)) and n_micro > 1
+        # stage boundaries in half-layer units (2 per layer); the plain schedule keeps whole layers
+        unit = sum(schedule.LAYER_COST) * head_cost / sum(schedule.HEAD_COST)
+        head = tuple(c * unit for c in schedule.HEAD_COST)
+        self.bounds = schedule.choose_partition_units(n_layers, world, n_micro, head_cost=head,
+                                                      whole_layers=not (self.overlap and split_layers))
+        self.counts = [(self.bounds[r + 1] - self.bounds[r]) / 2 for r in range(world)]      # layers per stage, halves count 0.5
+        u0, u1 = self.bounds[rank], self.bounds[rank + 1]
+        first_layer = u0 // 2
+        kinds = []
+        for layer in range(first_layer, (u1 + 1) // 2 if u1 > u0 else first_layer):
+            kinds.append(("A" if u0 <= 2 * layer < u1 else "") + ("M" if u0 <= 2 * layer + 1 < u1 else ""))
+        self.kinds = kinds
+        # share of a whole layer's GEMM FLOPs in each half: QKV + dense are 4 of the 12 h x h blocks
+        self.gemm_layers = sum((4 if "A" in k else 0) + (8 if "M" in k else 0) for k in kinds) / 12.0
+        my_layers = len(kinds)
         if world == 1:
             self.n_slots = 1
+        elif not self.overlap:
+            self.n_slots = n_micro        # all forwards run before the first backward: every micro-batch stays alive
         elif n_slots is not None:
-            self.n_slots = max(2, min(int(n_slots), n_micro)) if n_micro > 1 else 1
+            self.n_slots = max(2, min(int(n_slots), n_micro))
         else:
             act = batch * tokens * hidden * (2 if dtype == "half" else 4)
-            per_layer = (23 if self.overlap else 14) * act
-            self.n_slots = schedule.n_slots_for(world, n_micro, self.counts, per_layer, activation_budget) if n_micro > 1 else 1
-        if self.n_slots < 2:
-            self.overlap = False
-        if world > 1 and not self.overlap:
-            self.n_slots = n_micro        # all forwards run before the first backward: every micro-batch stays alive
+            self.n_slots = schedule.n_slots_for(world, n_micro, [int(c + 0.5) for c in self.counts], 23 * act, activation_budget)
         self.env = host.Env(my_layers + 1)
         kw = dict(hidden=hidden, heads=heads, vocab=vocab, n_layers=my_layers, batch=batch, tokens=tokens, dtype=dtype,
                   first_stage=self.first, last_stage=self.last, logits_rows=logits_rows, init_std=init_std, seed=seed,
-                  layer_offset=sum(self.counts[:rank]), n_slots=self.n_slots, n_micro=n_micro,
+                  layer_offset=first_layer, n_slots=self.n_slots, n_micro=n_micro, kinds=kinds,
                   prev_rank=None if self.first else rank - 1, next_rank=None if self.last else rank + 1)
         # play_all_ranks: this single-rank process holds the Trainers of every rank of the pipeline (a test on one GPU
         # that interleaves their task lists itself); the links then keep one block per played rank
@@ -114,7 +126,7 @@ class Trainer:
             for k in range(n_micro):
                 self.tasks.append((prog(f'slot_{k % S} "loss@{k}" stage_backward_async'), k))
         else:
-            costs = schedule.stage_costs(self.counts)
+            costs = self.stage_costs = schedule.stage_costs_units(self.bounds, head_cost=head)
             orders, self.simulated_step = schedule.build(world, n_micro, costs, S)
             schedule.check(orders, n_micro, S)          # raises on a dependency or slot conflict before anything is queued
             self.order = orders[rank]
@@ -231,4 +243,4 @@ def gemm_flops_per_microbatch(hidden, vocab, n_layers, tokens_total, with_head=T
     backward has two GEMMs per forward GEMM)."""
     per_layer_fwd = 2 * tokens_total * 12 * hidden * hidden
     head_fwd = 2 * tokens_total * hidden * vocab
-    return 3 * n_layers * per_layer_fwd + (3 * head_fwd if with_head else 0)
+    return int(3 * n_layers * per_layer_fwd) + (3 * head_fwd if with_head else 0)

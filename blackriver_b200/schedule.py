@@ -208,3 +208,95 @@ def choose_partition(n_layers, world, n_micro, n_slots=None, layer_cost=LAYER_CO
             if best is None or key < best[0]:
                 best = (key, counts)
     return best[1]
+
+
+# ---- stages cut at half-layer boundaries -----------------------------------------------------------------------------
+# A decoder layer is two units: "A" = input LayerNorm, QKV projection, attention, dense projection + residual;
+# "M" = post-attention LayerNorm, h -> 4h + GELU, 4h -> h + residual.  The tensor between them (the residual stream after
+# attention) has the same shape as a layer's output, so a stage boundary may fall there too, which lets 30 layers be
+# spread over 7 ranks in pieces of 4.3 layers instead of 5 and 4.  Costs (F, B, W) in the unit of LAYER_COST, from the
+# same measured profile: A carries a third of the layer's GEMM FLOPs plus the attention kernels, M two thirds.
+UNIT_COST = {"A": (0.36, 0.545, 0.286), "M": (0.473, 0.537, 0.546)}
+
+
+def unit_kind(u):
+    return "A" if u % 2 == 0 else "M"
+
+
+def stage_costs_units(bounds, unit_cost=None, head_cost=HEAD_COST):
+    """bounds = [u_0 = 0, u_1, ..., u_world = 2 * layers]: rank r owns units [u_r, u_r+1).  (F, B, W) per micro-batch and rank."""
+    unit_cost = unit_cost or UNIT_COST
+    out = []
+    world = len(bounds) - 1
+    for r in range(world):
+        f = b = w = 0.0
+        for u in range(bounds[r], bounds[r + 1]):
+            c = unit_cost[unit_kind(u)]
+            f, b, w = f + c[0], b + c[1], w + c[2]
+        if r == world - 1:
+            f, b, w = f + head_cost[0], b + head_cost[1], w + head_cost[2]
+        out.append((max(f, 1e-3), max(b, 1e-3), max(w, 1e-3)))
+    return out
+
+
+def choose_partition_units(n_layers, world, n_micro, n_slots=None, unit_cost=None, head_cost=HEAD_COST, whole_layers=False):
+    """Stage boundaries in units (2 per layer) with the shortest simulated step.  Candidates come from an exact search
+    (dynamic programme over contiguous splits) for the split that minimises the largest of
+    n_micro x (work of the stage) + alpha x (forward time of everything before it), for several alpha: the second term
+    is the time a stage has to wait for its first micro-batch, which later stages cannot get back.  Every rank but the
+    last owns at least one unit; the last may own none (head only).  whole_layers=True allows boundaries between layers only."""
+    unit_cost = unit_cost or UNIT_COST
+    n_units = 2 * n_layers
+    if world == 1:
+        return [0, n_units]
+    step = 2 if whole_layers else 1
+    cost = [sum(unit_cost[unit_kind(u)]) for u in range(n_units)]
+    fwd = [unit_cost[unit_kind(u)][0] for u in range(n_units)]
+    pre_c = [0.0]
+    pre_f = [0.0]
+    for u in range(n_units):
+        pre_c.append(pre_c[-1] + cost[u])
+        pre_f.append(pre_f[-1] + fwd[u])
+    head = sum(head_cost)
+    points = list(range(0, n_units + 1, step))
+    best = None
+    seen = set()
+    for alpha in (0.0, 0.5, 1.0, 1.5, 2.0, 3.0):
+        def stage(a, b, is_last):
+            return n_micro * (pre_c[b] - pre_c[a] + (head if is_last else 0.0)) + alpha * pre_f[a]
+        INF = float("inf")
+        # dp[r][i]: best (smallest) largest-stage value when the first r ranks own units [0, points[i])
+        dp = [[INF] * len(points) for _ in range(world + 1)]
+        arg = [[-1] * len(points) for _ in range(world + 1)]
+        dp[0][0] = 0.0
+        for r in range(1, world + 1):
+            last = r == world
+            for i in range(len(points)):
+                if last and points[i] != n_units:
+                    continue
+                for k in range(len(points)):
+                    if k > i or dp[r - 1][k] == INF:
+                        continue
+                    if not last and k == i:
+                        continue                      # every rank but the last owns something
+                    v = max(dp[r - 1][k], stage(points[k], points[i], last))
+                    if v < dp[r][i]:
+                        dp[r][i], arg[r][i] = v, k
+        i = len(points) - 1
+        if dp[world][i] == INF:
+            continue
+        bounds = [n_units]
+        for r in range(world, 0, -1):
+            i = arg[r][i]
+            bounds.append(points[i])
+        bounds.reverse()
+        if tuple(bounds) in seen:
+            continue
+        seen.add(tuple(bounds))
+        costs = stage_costs_units(bounds, unit_cost, head_cost)
+        _, span = build(world, n_micro, costs, n_slots)
+        if best is None or span < best[0] - 1e-9:
+            best = (span, bounds)
+    if best is None:
+        raise ValueError("more ranks than units to give them")
+    return best[1]

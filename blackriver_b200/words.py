@@ -240,9 +240,21 @@ def layer_param_elements(hidden):
     return _layer_param_layout(hidden)[1]
 
 
+# tensors of the two halves of a layer: "A" = input LayerNorm, QKV, attention, dense (+ residual); "M" = post-attention
+# LayerNorm, h -> 4h (+ GELU), 4h -> h (+ residual)
+HALF_PARAMS = {
+    "A": ("input_layernorm.weight", "input_layernorm.bias", "query_key_value.weight", "query_key_value.bias", "dense.weight", "dense.bias"),
+    "M": ("post_attention_layernorm.weight", "post_attention_layernorm.bias", "dense_h_to_4h.weight", "dense_h_to_4h.bias",
+          "dense_4h_to_h.weight", "dense_4h_to_h.bias"),
+}
+# saved activations (per slot) and gradients kept for a deferred weight-gradient pass (per slot, overlap only)
+HALF_SAVED = {"A": (("xattn_in", 1), ("qkv", 3), ("attn_out", 1)), "M": (("xb", 1), ("x4a", 4), ("x4b", 4))}
+HALF_STATS = {"A": ("input_ln_var",), "M": ("post_ln_var",)}
+
+
 def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps=1e-5, first_stage=True, last_stage=True,
                 logits_rows=None, init_std=0.02, seed=0, layer_offset=0, n_slots=1, prev_rank=None, next_rank=None,
-                overlap=False, n_micro=1):
+                overlap=False, n_micro=1, kinds=None):
     """Script text defining the whole stage.  After executing it:
          build_model            allocates everything (call once)
          init_model             seeded random initialisation (weights N(0, init_std), biases 0, LN 1/0)
@@ -264,12 +276,18 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
          ( name -- ) stage_b   input gradients only (the micro-batch's mean loss goes to the view of "loss_all" called
                       name, "loss@j"); send to the previous rank
          stage_w      weight gradients of the slot's micro-batch from the kept dy tensors; releases the gradient window
-       The stage's incoming tensors are then the link windows themselves (no copy on arrival)."""
+       The stage's incoming tensors are then the link windows themselves (no copy on arrival).
+
+       kinds (overlap only): one entry per layer hash of the stage, "AM" for a whole layer, "M" when only the MLP half
+       of the stage's first layer is here (its attention half closes the previous stage) and "A" when only the
+       attention half of the last layer is here.  layer_offset is the model-wide index of the stage's first layer."""
     assert n_layers >= 1 or (last_stage and not first_stage)
     assert not overlap or (n_slots > 1 and not (first_stage and last_stage))
-    SLOTTED = ("xattn_in", "qkv", "attn_out", "xb", "x4a", "x4b", "lse", "input_ln_var", "post_ln_var")
-    # gradients a deferred weight-gradient pass reads: kept per slot instead of living in shared scratch
-    KEPT_DY = ("d4", "dqkv", "dh2") if overlap else ()
+    kinds = list(kinds) if kinds is not None else ["AM"] * n_layers
+    assert len(kinds) == n_layers and all(k in ("AM", "A", "M") for k in kinds)
+    assert all(k == "AM" for k in kinds[1:-1]) and (n_layers < 2 or ("A" in kinds[-1] and "M" in kinds[0]))
+    assert overlap or all(k == "AM" for k in kinds), "half layers exist in the overlapped pipeline only"
+    assert not (first_stage and kinds and "A" not in kinds[0]) and not (last_stage and kinds and "M" not in kinds[-1])
 
     def slot_names(name):
         return [name] if n_slots == 1 else [f"{name}@{k}" for k in range(n_slots)]
@@ -287,77 +305,121 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w(f"{batch} $batch !  {tokens} $tokens !")
     BTH = f'{batch} {tokens} "HIDDEN_SIZE" @ 3'
 
-    # ---- per-layer allocation (run inside the layer's hash) ----
-    w("%def create_layer_fused")      # runs inside a layer's hash table, so sizes and types are spelled out
-    for suffix, dt in (("", dtype), ("_g", dtype), (".master", "float"), (".m", "float"), (".v", "float")):
-        w(f'    {flat} 1 "cuda" "{dt}" op.create "_flat{suffix}" !')
-    for suffix in ("", "_g", ".master"):          # the fp32 master views are what a checkpoint stores, tensor by tensor
-        for name, shape, off, cnt in layout:
-            dims = " ".join(str(d) for d in shape)
-            w(f'    "_flat{suffix}" @ {off} {dims} {len(shape)} op.view "{name}{suffix}" !')
-    for name, cols in (("xattn_in", 1), ("qkv", 3), ("attn_out", 1), ("xa", 1), ("xb", 1), ("x4a", 4), ("x4b", 4), ("xout", 1)):
-        for nm in (slot_names(name) if name in SLOTTED else [name]):
-            w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "{dtype}" op.create "{nm}" !')
-    for name, cols in (("d4", 4), ("dqkv", 3), ("dh2", 1), ("yout_g", 1)):
-        if overlap:
-            for nm in slot_names(name):
-                w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "{dtype}" op.create "{nm}" !')
-    for nm in slot_names("lse"):
-        w(f'    {batch} {heads} {tokens} 3 "cuda" "float" op.create "{nm}" !')
-    w(f'    {n} 1 "cuda" "float" op.create "ln_mean" !')
-    for name in ("input_ln_var", "post_ln_var"):
-        for nm in slot_names(name):
-            w(f'    {n} 1 "cuda" "float" op.create "{nm}" !')
-    w("%end")
-
-    # ---- layer math (run inside the layer's hash; xinput / yout_g / xin_g and the scratch are bound there) ----
     def g(*names):
         return " ".join(_get(x) for x in names)
 
-    w("%def layer_forward_fused")
-    w(f'    {g("xinput", "ln_mean", "input_ln_var", "input_layernorm.weight", "input_layernorm.bias", "xattn_in", "LN_EPS")} op.layernorm')
-    w(f'    {g("xattn_in", "query_key_value.weight", "query_key_value.bias", "qkv")} op.linear')
-    w(f'    {g("qkv", "lens_", "attn_out", "lse", "HEADS_NUM")} op.flash_attn')
-    w(f'    {g("attn_out", "dense.weight", "dense.bias", "xinput", "xa")} op.linear_residual')
-    w(f'    {g("xa", "ln_mean", "post_ln_var", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "xb", "LN_EPS")} op.layernorm')
-    w(f'    {g("xb", "dense_h_to_4h.weight", "dense_h_to_4h.bias", "x4a", "x4b")} op.linear_gelu')
-    w(f'    {g("x4b", "dense_4h_to_h.weight", "dense_4h_to_h.bias", "xa", "xout")} op.linear_residual')
-    w("%end")
+    def act(name, cols, slotted):
+        for nm in (slot_names(name) if slotted else [name]):
+            w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "{dtype}" op.create "{nm}" !')
 
-    w("%def layer_backward_fused")
-    w(f'    {g("yout_g", "x4b", "dense_4h_to_h.weight", "dense_4h_to_h.bias", "d4", "dense_4h_to_h.weight_g", "dense_4h_to_h.bias_g")} op.linear_backward')
-    w(f'    {g("d4", "x4a", "d4")} op.gelu_backward')
-    w(f'    {g("d4", "xb", "dense_h_to_4h.weight", "dense_h_to_4h.bias", "dh1", "dense_h_to_4h.weight_g", "dense_h_to_4h.bias_g")} op.linear_backward')
-    w(f'    {g("dh1", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "post_ln_var", "xb", "post_attention_layernorm.weight_g", "post_attention_layernorm.bias_g", "dh2", "LN_EPS")} op.layernorm_backward')
-    w(f'    {g("yout_g", "dh2", "dh2")} op.add')
-    w(f'    {g("dh2", "attn_out", "dense.weight", "dense.bias", "dh1", "dense.weight_g", "dense.bias_g")} op.linear_backward')
-    w(f'    {g("dh1", "qkv", "attn_out", "lse", "lens_", "dqkv", "HEADS_NUM")} op.flash_attn_backward')
-    w(f'    {g("dqkv", "xattn_in", "query_key_value.weight", "query_key_value.bias", "dh1", "query_key_value.weight_g", "query_key_value.bias_g")} op.linear_backward')
-    w(f'    {g("dh1", "input_layernorm.weight", "input_layernorm.bias", "input_ln_var", "xattn_in", "input_layernorm.weight_g", "input_layernorm.bias_g", "dh3", "LN_EPS")} op.layernorm_backward')
-    w(f'    {g("dh3", "dh2", "xin_g")} op.add')
-    w("%end")
+    # names a layer of a given kind reads / writes at its two ends
+    def in_name(kind):
+        return "xinput" if "A" in kind else "xa"
 
-    # the same backward in two passes: input gradients (what the previous stage waits for), then weight gradients
-    w("%def layer_backward_x")
-    w(f'    {g("yout_g", "dense_4h_to_h.weight", "d4")} op.linear_backward_x')
-    w(f'    {g("d4", "x4a", "d4")} op.gelu_backward')
-    w(f'    {g("d4", "dense_h_to_4h.weight", "dh1")} op.linear_backward_x')
-    w(f'    {g("dh1", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "post_ln_var", "xb", "post_attention_layernorm.weight_g", "post_attention_layernorm.bias_g", "dh2", "LN_EPS")} op.layernorm_backward')
-    w(f'    {g("yout_g", "dh2", "dh2")} op.add')
-    w(f'    {g("dh2", "dense.weight", "dh1")} op.linear_backward_x')
-    w(f'    {g("dh1", "qkv", "attn_out", "lse", "lens_", "dqkv", "HEADS_NUM")} op.flash_attn_backward')
-    w(f'    {g("dqkv", "query_key_value.weight", "dh1")} op.linear_backward_x')
-    w(f'    {g("dh1", "input_layernorm.weight", "input_layernorm.bias", "input_ln_var", "xattn_in", "input_layernorm.weight_g", "input_layernorm.bias_g", "dh3", "LN_EPS")} op.layernorm_backward')
-    w(f'    {g("dh3", "dh2", "xin_g")} op.add')
-    w("%end")
-    w("%def layer_backward_w")
-    w(f'    {g("yout_g", "x4b", "dense_4h_to_h.weight_g", "dense_4h_to_h.bias_g")} op.linear_backward_w')
-    w(f'    {g("d4", "xb", "dense_h_to_4h.weight_g", "dense_h_to_4h.bias_g")} op.linear_backward_w')
-    w(f'    {g("dh2", "attn_out", "dense.weight_g", "dense.bias_g")} op.linear_backward_w')
-    w(f'    {g("dqkv", "xattn_in", "query_key_value.weight_g", "query_key_value.bias_g")} op.linear_backward_w')
-    w("%end")
+    def out_name(kind):
+        return "xout" if "M" in kind else "xa"
 
-    # ---- ( seed -- ) seeded initialisation of one layer ----
+    def gin_name(kind):          # gradient arriving from the layer (or stage) after it
+        return "yout_g" if "M" in kind else "dh2"
+
+    def gout_name(kind):         # gradient handed to the layer (or stage) before it
+        return "xin_g" if "A" in kind else "dh2"
+
+    # ---- per-kind words (run inside the layer's hash table, so sizes and types are spelled out) ----
+    for kind in sorted(set(kinds)) or ["AM"]:
+        tag = "fused" if kind == "AM" else kind
+        w(f"%def create_layer_{tag}")
+        # the parameter buffers are whole-layer sized for every kind (one optimizer launch per layer hash; the half
+        # that lives on another rank just never receives a gradient)
+        for suffix, dt in (("", dtype), ("_g", dtype), (".master", "float"), (".m", "float"), (".v", "float")):
+            w(f'    {flat} 1 "cuda" "{dt}" op.create "_flat{suffix}" !')
+        for suffix in ("", "_g", ".master", ".m", ".v"):     # fp32 master / moment views are what a checkpoint stores
+            for name, shape, off, cnt in layout:
+                dims = " ".join(str(d) for d in shape)
+                w(f'    "_flat{suffix}" @ {off} {dims} {len(shape)} op.view "{name}{suffix}" !')
+        for half in "AM":
+            if half not in kind:
+                continue
+            for name, cols in HALF_SAVED[half]:
+                act(name, cols, True)
+            for name in HALF_STATS[half]:
+                for nm in slot_names(name):
+                    w(f'    {n} 1 "cuda" "float" op.create "{nm}" !')
+        if "A" in kind:
+            for nm in slot_names("lse"):
+                w(f'    {batch} {heads} {tokens} 3 "cuda" "float" op.create "{nm}" !')
+            if overlap:
+                act("dqkv", 3, True)
+                if "M" in kind:
+                    act("dh2", 1, True)          # an "A" layer's dh2 is the gradient that arrives from the next stage
+        if "M" in kind and overlap:
+            act("d4", 4, True)
+            act("yout_g", 1, True)               # what the layer after this one writes (bound as its outgoing gradient)
+        if kind == "AM" or kind == "A":
+            act("xa", 1, False)                  # for "M" the stage's incoming window plays this part
+        if "M" in kind:
+            act("xout", 1, False)
+        w(f'    {n} 1 "cuda" "float" op.create "ln_mean" !')
+        w("%end")
+
+        def forward_A():
+            w(f'    {g("xinput", "ln_mean", "input_ln_var", "input_layernorm.weight", "input_layernorm.bias", "xattn_in", "LN_EPS")} op.layernorm')
+            w(f'    {g("xattn_in", "query_key_value.weight", "query_key_value.bias", "qkv")} op.linear')
+            w(f'    {g("qkv", "lens_", "attn_out", "lse", "HEADS_NUM")} op.flash_attn')
+            w(f'    {g("attn_out", "dense.weight", "dense.bias", "xinput", "xa")} op.linear_residual')
+
+        def forward_M():
+            w(f'    {g("xa", "ln_mean", "post_ln_var", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "xb", "LN_EPS")} op.layernorm')
+            w(f'    {g("xb", "dense_h_to_4h.weight", "dense_h_to_4h.bias", "x4a", "x4b")} op.linear_gelu')
+            w(f'    {g("x4b", "dense_4h_to_h.weight", "dense_4h_to_h.bias", "xa", "xout")} op.linear_residual')
+
+        w(f"%def layer_forward_{tag}")
+        if "A" in kind:
+            forward_A()
+        if "M" in kind:
+            forward_M()
+        w("%end")
+
+        if kind == "AM":
+            w("%def layer_backward_fused")
+            w(f'    {g("yout_g", "x4b", "dense_4h_to_h.weight", "dense_4h_to_h.bias", "d4", "dense_4h_to_h.weight_g", "dense_4h_to_h.bias_g")} op.linear_backward')
+            w(f'    {g("d4", "x4a", "d4")} op.gelu_backward')
+            w(f'    {g("d4", "xb", "dense_h_to_4h.weight", "dense_h_to_4h.bias", "dh1", "dense_h_to_4h.weight_g", "dense_h_to_4h.bias_g")} op.linear_backward')
+            w(f'    {g("dh1", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "post_ln_var", "xb", "post_attention_layernorm.weight_g", "post_attention_layernorm.bias_g", "dh2", "LN_EPS")} op.layernorm_backward')
+            w(f'    {g("yout_g", "dh2", "dh2")} op.add')
+            w(f'    {g("dh2", "attn_out", "dense.weight", "dense.bias", "dh1", "dense.weight_g", "dense.bias_g")} op.linear_backward')
+            w(f'    {g("dh1", "qkv", "attn_out", "lse", "lens_", "dqkv", "HEADS_NUM")} op.flash_attn_backward')
+            w(f'    {g("dqkv", "xattn_in", "query_key_value.weight", "query_key_value.bias", "dh1", "query_key_value.weight_g", "query_key_value.bias_g")} op.linear_backward')
+            w(f'    {g("dh1", "input_layernorm.weight", "input_layernorm.bias", "input_ln_var", "xattn_in", "input_layernorm.weight_g", "input_layernorm.bias_g", "dh3", "LN_EPS")} op.layernorm_backward')
+            w(f'    {g("dh3", "dh2", "xin_g")} op.add')
+            w("%end")
+
+        # the same backward in two passes: input gradients (what the previous stage waits for), then weight gradients
+        w(f"%def layer_backward_x_{tag}")
+        if "M" in kind:
+            w(f'    {g("yout_g", "dense_4h_to_h.weight", "d4")} op.linear_backward_x')
+            w(f'    {g("d4", "x4a", "d4")} op.gelu_backward')
+            w(f'    {g("d4", "dense_h_to_4h.weight", "dh1")} op.linear_backward_x')
+            w(f'    {g("dh1", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "post_ln_var", "xb", "post_attention_layernorm.weight_g", "post_attention_layernorm.bias_g", "dh2", "LN_EPS")} op.layernorm_backward')
+            w(f'    {g("yout_g", "dh2", "dh2")} op.add')
+        if "A" in kind:
+            w(f'    {g("dh2", "dense.weight", "dh1")} op.linear_backward_x')
+            w(f'    {g("dh1", "qkv", "attn_out", "lse", "lens_", "dqkv", "HEADS_NUM")} op.flash_attn_backward')
+            w(f'    {g("dqkv", "query_key_value.weight", "dh1")} op.linear_backward_x')
+            w(f'    {g("dh1", "input_layernorm.weight", "input_layernorm.bias", "input_ln_var", "xattn_in", "input_layernorm.weight_g", "input_layernorm.bias_g", "dh3", "LN_EPS")} op.layernorm_backward')
+            w(f'    {g("dh3", "dh2", "xin_g")} op.add')
+        w("%end")
+        w(f"%def layer_backward_w_{tag}")
+        if "M" in kind:
+            w(f'    {g("yout_g", "x4b", "dense_4h_to_h.weight_g", "dense_4h_to_h.bias_g")} op.linear_backward_w')
+            w(f'    {g("d4", "xb", "dense_h_to_4h.weight_g", "dense_h_to_4h.bias_g")} op.linear_backward_w')
+        if "A" in kind:
+            w(f'    {g("dh2", "attn_out", "dense.weight_g", "dense.bias_g")} op.linear_backward_w')
+            w(f'    {g("dqkv", "xattn_in", "query_key_value.weight_g", "query_key_value.bias_g")} op.linear_backward_w')
+        w("%end")
+
+    # ---- ( seed -- ) seeded initialisation of one layer (every tensor, whichever half is used here: the two ranks that
+    # share a layer then hold the same values as a single-stage model) ----
     w("%def init_layer_fused")
     w('    "seed_" !')
     w('    "_flat" @ op.zero')
@@ -369,6 +431,9 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w('    "_flat.master" @ "_flat" @ op.copy  "_flat.m" @ op.zero  "_flat.v" @ op.zero  "_flat_g" @ op.zero')
     w('    "seed_" !!')
     w("%end")
+
+    def tag_of(i):
+        return "fused" if kinds[i - 1] == "AM" else kinds[i - 1]
 
     # ---- whole stage ----
     act_bytes = batch * tokens * hidden * (2 if dtype == "half" else 4)
@@ -428,15 +493,16 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     if (first_stage != last_stage) and (prev_rank is not None or next_rank is not None):
         w(f'    "VOCAB_SIZE" @ "HIDDEN_SIZE" @ 2 "cuda" "DTYPE" @ op.create "tied_recv" !')
     for i in range(1, n_layers + 1):
-        w(f"    {i} # create_layer_fused")
+        w(f"    {i} # create_layer_{tag_of(i)}")
     # bindings: scratch and inputs into every layer hash; activations chained layer to layer
     shared = ("dh1", "dh3", "lens_", "LN_EPS", "HEADS_NUM") + (() if overlap else ("d4", "dqkv", "dh2"))
     for i in range(1, n_layers + 1):
+        kind = kinds[i - 1]
         for name in shared:
             w(f'    0 # "{name}" @ {i} # "{name}" !')
-        src = (f'{i - 1} # "xout" @' if i > 1 else ('0 # "emb_out" @' if first_stage else '0 # "stage_in" @'))
+        src = (f'{i - 1} # "{out_name(kinds[i - 2])}" @' if i > 1 else ('0 # "emb_out" @' if first_stage else '0 # "stage_in" @'))
         if not (i == 1 and n_slots > 1 and (first_stage or overlap)):      # with slots the stage input is bound by slot_k
-            w(f'    {src} {i} # "xinput" !')
+            w(f'    {src} {i} # "{in_name(kind)}" !')
         if not overlap:
             # gradient buffers alternate so a layer never reads and writes the same one
             gin, gout = ("gA", "gB") if (n_layers - i) % 2 == 0 else ("gB", "gA")
@@ -446,7 +512,7 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         # every layer keeps its incoming gradient per slot (bound by slot_k); the first layer's outgoing gradient
         # is a shared buffer, consumed at once (embedding backward) or copied out by the link before it is reused
         if n_layers >= 1:
-            w(f'    "gA" @ 1 # "xin_g" !  0 #  "gA" @ "stage_in_g" !  {n_layers} # "xout" @ 0 # "stage_out" !')
+            w(f'    "gA" @ 1 # "{gout_name(kinds[0])}" !  0 #  "gA" @ "stage_in_g" !  {n_layers} # "{out_name(kinds[-1])}" @ 0 # "stage_out" !')
         else:
             w('    "gA" @ "stage_in_g" !')
     elif n_layers >= 1:
@@ -456,6 +522,21 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w("%end")
 
     # ---- slot selection: which micro-batch's saved activations the layer words see ----
+    def slotted_of(kind):
+        names = []
+        for half in "AM":
+            if half in kind:
+                names += [nm for nm, _ in HALF_SAVED[half]] + list(HALF_STATS[half])
+        if "A" in kind:
+            names.append("lse")
+            if overlap:
+                names.append("dqkv")
+                if "M" in kind:
+                    names.append("dh2")
+        if "M" in kind and overlap:
+            names.append("d4")
+        return names
+
     for k in range(n_slots):
         w(f"%def slot_{k}")
         if n_slots > 1:
@@ -475,14 +556,18 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
             if first_stage:
                 w(f'    "emb_out" @ 1 # "xinput" ! 0 #')
             elif overlap and n_layers >= 1:
-                w(f'    "stage_in" @ 1 # "xinput" ! 0 #')
+                w(f'    "stage_in" @ 1 # "{in_name(kinds[0])}" ! 0 #')
             for i in range(1, n_layers + 1):
-                w(f"    {i} #  " + "  ".join(f'"{name}@{k}" @ "{name}" !' for name in SLOTTED + KEPT_DY))
+                kind = kinds[i - 1]
+                w(f"    {i} #  " + "  ".join(f'"{name}@{k}" @ "{name}" !' for name in slotted_of(kind)))
                 if overlap:
                     # layer i reads the gradient the layer after it (or the stage's successor) produced for this slot
-                    w(f'    "yout_g@{k}" @ "yout_g" !' if i < n_layers else f'    0 # "stage_out_g" @ {i} # "yout_g" !')
+                    if i < n_layers:
+                        w(f'    "yout_g@{k}" @ "yout_g" !')
+                    else:
+                        w(f'    0 # "stage_out_g" @ {i} # "{gin_name(kind)}" !')
                     if i > 1:
-                        w(f'    {i - 1} # "yout_g@{k}" @ {i} # "xin_g" !')
+                        w(f'    {i - 1} # "yout_g@{k}" @ {i} # "{gout_name(kind)}" !')
         w("    0 #")
         w("%end")
 
@@ -517,7 +602,7 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         w(f'    {g("ids_", "word_embeddings.weight", "emb_raw")} op.embed')
         w(f'    {g("emb_raw", "ln_mean", "emb_ln_var", "word_embeddings_layernorm.weight", "word_embeddings_layernorm.bias", "emb_out", "LN_EPS")} op.layernorm')
     for i in range(1, n_layers + 1):
-        w(f"    {i} # layer_forward_fused")
+        w(f"    {i} # layer_forward_{tag_of(i)}")
     w("    0 #")
     if last_stage:
         w(f'    {g("stage_out", "ln_mean", "ln_f_var", "ln_f.weight", "ln_f.bias", "xf", "LN_EPS")} op.layernorm')
@@ -530,35 +615,37 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         w(f'    {g("xf", "ids_", "mask_", "word_embeddings.weight", "all_logits", "token_nll")} op.token_nll')
     w("%end")
 
-    w("%def model_backward")
-    w("    0 #")
-    if last_stage:
-        w(f'    {g("xf", "ids_", "mask_", "word_embeddings.weight", "all_logits", "xf_g", "word_embeddings.weight_g")} op.loss_backward')
-        w(f'    {g("xf_g", "ln_f.weight", "ln_f.bias", "ln_f_var", "xf", "ln_f.weight_g", "ln_f.bias_g", "stage_out_g", "LN_EPS")} op.layernorm_backward')
-    for i in range(n_layers, 0, -1):
-        w(f"    {i} # layer_backward_fused")
-    w("    0 #")
-    if first_stage:
+    def embedding_backward():
         w(f'    {g("stage_in_g", "word_embeddings_layernorm.weight", "word_embeddings_layernorm.bias", "emb_ln_var", "emb_out", "word_embeddings_layernorm.weight_g", "word_embeddings_layernorm.bias_g", "emb_raw", "LN_EPS")} op.layernorm_backward')
         w(f'    {g("emb_raw", "ids_", "word_embeddings.weight_g")} op.embed_backward')
-    w("%end")
 
-    # ( name -- ) the same backward queued without any host round trip; name = the one-element view of "loss_all"
-    # that receives this micro-batch's mean loss ("loss@j")
-    w("%def model_backward_async")
-    w('    0 # @ "loss_" !')
-    if last_stage:
-        w(f'    {g("xf", "ids_", "mask_", "word_embeddings.weight", "all_logits", "xf_g", "word_embeddings.weight_g", "loss_")} 0 op.loss_backward_async')
-        w(f'    {g("xf_g", "ln_f.weight", "ln_f.bias", "ln_f_var", "xf", "ln_f.weight_g", "ln_f.bias_g", "stage_out_g", "LN_EPS")} op.layernorm_backward')
     if not overlap:
+        w("%def model_backward")
+        w("    0 #")
+        if last_stage:
+            w(f'    {g("xf", "ids_", "mask_", "word_embeddings.weight", "all_logits", "xf_g", "word_embeddings.weight_g")} op.loss_backward')
+            w(f'    {g("xf_g", "ln_f.weight", "ln_f.bias", "ln_f_var", "xf", "ln_f.weight_g", "ln_f.bias_g", "stage_out_g", "LN_EPS")} op.layernorm_backward')
         for i in range(n_layers, 0, -1):
             w(f"    {i} # layer_backward_fused")
         w("    0 #")
         if first_stage:
-            w(f'    {g("stage_in_g", "word_embeddings_layernorm.weight", "word_embeddings_layernorm.bias", "emb_ln_var", "emb_out", "word_embeddings_layernorm.weight_g", "word_embeddings_layernorm.bias_g", "emb_raw", "LN_EPS")} op.layernorm_backward')
-            w(f'    {g("emb_raw", "ids_", "word_embeddings.weight_g")} op.embed_backward')
-    w('    0 # "loss_" !!')
-    w("%end")
+            embedding_backward()
+        w("%end")
+
+        # ( name -- ) the same backward queued without any host round trip; name = the one-element view of "loss_all"
+        # that receives this micro-batch's mean loss ("loss@j")
+        w("%def model_backward_async")
+        w('    0 # @ "loss_" !')
+        if last_stage:
+            w(f'    {g("xf", "ids_", "mask_", "word_embeddings.weight", "all_logits", "xf_g", "word_embeddings.weight_g", "loss_")} 0 op.loss_backward_async')
+            w(f'    {g("xf_g", "ln_f.weight", "ln_f.bias", "ln_f_var", "xf", "ln_f.weight_g", "ln_f.bias_g", "stage_out_g", "LN_EPS")} op.layernorm_backward')
+        for i in range(n_layers, 0, -1):
+            w(f"    {i} # layer_backward_fused")
+        w("    0 #")
+        if first_stage:
+            embedding_backward()
+        w('    0 # "loss_" !!')
+        w("%end")
 
     # ( lr step grad_scale -- )
     w("%def optimizer_step")
@@ -588,7 +675,7 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         w("%def stage_score")
         w("    stage_f model_score")
         w("%end")
-        w("%def stage_b")                            # ( name -- )  name as for model_backward_async
+        w("%def stage_b")                            # ( name -- )  name = the view of "loss_all" for this micro-batch
         w('    0 # @ "loss_" !')
         if next_rank is not None:
             w('    1 "slot_" @ io.link.wait')
@@ -601,11 +688,10 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
             dst = "stage_out_g" if n_layers >= 1 else "stage_in_g"
             w(f'    {g("xf_g", "ln_f.weight", "ln_f.bias", "ln_f_var", "xf", "ln_f.weight_g", "ln_f.bias_g", dst, "LN_EPS")} op.layernorm_backward')
         for i in range(n_layers, 0, -1):
-            w(f"    {i} # layer_backward_x")
+            w(f"    {i} # layer_backward_x_{tag_of(i)}")
         w("    0 #")
         if first_stage:
-            w(f'    {g("stage_in_g", "word_embeddings_layernorm.weight", "word_embeddings_layernorm.bias", "emb_ln_var", "emb_out", "word_embeddings_layernorm.weight_g", "word_embeddings_layernorm.bias_g", "emb_raw", "LN_EPS")} op.layernorm_backward')
-            w(f'    {g("emb_raw", "ids_", "word_embeddings.weight_g")} op.embed_backward')
+            embedding_backward()
         if prev_rank is not None:
             w('    "stage_in_g" @ 0 "slot_" @ io.link.send')
         w('    "loss_" !!')
@@ -615,7 +701,7 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         if last_stage:
             w(f'    {g("all_logits", "xf", "word_embeddings.weight_g")} op.loss_backward_w')
         for i in range(n_layers, 0, -1):
-            w(f"    {i} # layer_backward_w")
+            w(f"    {i} # layer_backward_w_{tag_of(i)}")
         w("    0 #")
         if next_rank is not None:
             w('    1 "slot_" @ io.link.release')
@@ -646,12 +732,13 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         if prev_rank is not None:
             w(f'    0 # "stage_in_g" @ {prev_rank} io.nccl.send')
         w("%end")
+
     # ---- checkpoint: ( prefix -- ) save_model / load_model ----
     # Weights go out as the reference stores them, one raw fp32 file per tensor named <prefix>h<layer>.<tensor>.bin and
-    # <prefix><tensor>.bin (bloomz-7b/init.words:120-235, bloomz-7b/dump_weights.py:105-133; the fused QKV weight keeps this build's [q rows | k rows | v rows]
-    # order), taken from the fp32 master copies; the Adam moments follow as <prefix>h<layer>._flat.m.bin / .v.bin and
-    # <prefix><tensor>.m.bin / .v.bin.  Loading fills master, moments and the fp16 working copy.  The tied table is
-    # written by the first stage only and read by both of its holders.
+    # <prefix><tensor>.bin (bloomz-7b/init.words:120-235, bloomz-7b/dump_weights.py:105-133; the fused QKV weight keeps this
+    # build's [q rows | k rows | v rows] order), taken from the fp32 master copies; the Adam moments follow with .m.bin /
+    # .v.bin in place of .bin.  Loading fills master, moments and the fp16 working copy.  A rank writes the tensors of the
+    # layer halves it owns; the tied table is written by the first stage only and read by both of its holders.
     for word, io in (("save_model", "io.save"), ("load_model", "io.load")):
         w(f"%def {word}")
         w('    0 # "ckpt_" !')
@@ -664,13 +751,13 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
                 w(f'    "{name}" @ "{name}.master" @ op.copy')
         for i in range(1, n_layers + 1):
             gi = layer_offset + i - 1
+            owned = [nm for half in "AM" if half in kinds[i - 1] for nm in HALF_PARAMS[half]]
             w(f'    0 # "ckpt_" @ {i} # "ckpt_" !')
-            for name, shape, off, cnt in layout:
-                w(f'    "{name}.master" @ "ckpt_" @ "h{gi}.{name}.bin" | {io}')
-            for ext in ("m", "v"):
-                w(f'    "_flat.{ext}" @ "ckpt_" @ "h{gi}._flat.{ext}.bin" | {io}')
-            if word == "load_model":
-                w('    "_flat" @ "_flat.master" @ op.copy')
+            for name in owned:
+                for suffix, ext in ((".master", ""), (".m", ".m"), (".v", ".v")):
+                    w(f'    "{name}{suffix}" @ "ckpt_" @ "h{gi}.{name}{ext}.bin" | {io}')
+                if word == "load_model":
+                    w(f'    "{name}" @ "{name}.master" @ op.copy')
             w('    "ckpt_" !!')
         w('    0 # "ckpt_" !!')
         w("%end")

@@ -63,23 +63,27 @@ def train_single(host, mbs, n_micro, steps):
     return losses, w, table
 
 
-@pytest.mark.parametrize("world,head_cost,n_micro,n_slots", [(2, 0.5, 4, 4), (3, 2.5, 6, 3), (4, 0.5, 5, 2)])
-def test_emulated_ranks_match_single_stage(host, world, head_cost, n_micro, n_slots):
+@pytest.mark.parametrize("world,head_cost,n_micro,n_slots,split", [(2, 0.5, 4, 4, True), (3, 2.5, 6, 3, True), (4, 0.5, 5, 2, True),
+                                                                      (3, 0.2, 4, 4, True), (2, 0.5, 4, 2, False)])
+def test_emulated_ranks_match_single_stage(host, world, head_cost, n_micro, n_slots, split):
     from blackriver_b200 import finetune
     mbs = finetune.make_microbatches(n_micro, CFG["batch"], CFG["tokens"], CFG["vocab"], 20, seed=5)
     ref_losses, ref_w, ref_table = train_single(host, mbs, n_micro, steps=2)
 
     trs = [finetune.Trainer(CFG["hidden"], CFG["heads"], CFG["vocab"], CFG["n_layers"], CFG["batch"], CFG["tokens"], n_micro,
                             rank=r, world=world, seed=9, lr=1e-3, init_std=0.05, head_cost=head_cost, n_slots=n_slots,
-                            play_all_ranks=True)
+                            play_all_ranks=True, split_layers=split)
            for r in range(world)]
     try:
         assert all(t.overlap and t.n_slots == n_slots for t in trs)
         if head_cost > 2:
             assert trs[0].counts[-1] == 0            # a head-only last stage
+        if not split:
+            assert all(c == int(c) for c in trs[0].counts)
+        if world == 3 and head_cost < 0.3:
+            assert any(c != int(c) for c in trs[0].counts)      # 4 layers over 3 ranks: some layer is shared by two ranks
         from blackriver_b200 import schedule as S
-        costs = S.stage_costs(trs[0].counts)
-        orders, _ = S.build(world, n_micro, costs, n_slots)
+        orders, _ = S.build(world, n_micro, trs[0].stage_costs, n_slots)
         assert [list(o) for o in orders] == [list(t.order) for t in trs]      # every rank derives the same lists
         seq = global_order([t.order for t in trs], n_micro, n_slots)
         losses = []
