@@ -343,12 +343,16 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
 //   P_ij  = exp(s_ij - lse_i)  (0 where masked)   recomputed from Q, K and the saved lse
 //   dV_j  = sum_i P_ij dO_i            dP_ij = dO_i . V_j          dS_ij = P_ij (dP_ij - delta_i)
 //   dQ_i  = (1/sqrt d) sum_j dS_ij K_j            dK_j = (1/sqrt d) sum_i dS_ij Q_i
-// Two kernels, both with the forward's structure (TMA producer warp, one MMA-issuing thread,
-// 128 row-owner threads): the first owns a 128-key block and walks the query blocks at or after
-// it, accumulating dK and dV in tensor memory; the second owns a 128-query block and walks the
-// key blocks before it, accumulating dQ.  P and dS are written to shared memory once per tile
-// pair and reach the tensor core either as K-major operands (dQ) or, transposed for free through
-// the MN-major descriptor, as the A operand of dV = P^T dO and dK = dS^T Q.
+// Two kernels with the forward's roles (TMA producer warp, one MMA-issuing thread, 128 row-owner threads), both
+// software-pipelined over sub-blocks of 64 so that the tensor core always has the next scores to compute while the
+// row owners exponentiate the current ones:
+//   * the dK / dV kernel owns a 128-key block and walks the 64-query sub-blocks at or after it.  It works on the
+//     TRANSPOSED scores, S^T = K Q^T and dP^T = V dO^T (keys on the tensor-memory lanes, 64 query columns), so a row
+//     owner is a key: it writes P^T and dS^T rows, which are K-major A operands of dV += P^T dO and dK += dS^T Q as
+//     they stand; the 64 queries' lse and delta come from shared memory;
+//   * the dQ kernel owns a 128-query block and walks the 64-key sub-blocks before it: S = Q K^T, dP = dO V^T
+//     (64 key columns), dS rows to shared memory, dQ += dS K.
+// Both keep two score / dP buffers in tensor memory and two tiles of each shared-memory operand in flight.
 // ==========================================================================================
 struct AttnBwdParams {
     const float* lse;      // [B,h,T] natural log, from the forward
@@ -363,6 +367,8 @@ struct AttnBwdParams {
     float scale_log2;      // log2(e)/sqrt(d)
     float scale;           // 1/sqrt(d)
 };
+
+constexpr int AT_SUB = 64;      // rows of the walked operand per pipeline step of the backward kernels
 
 // one warp per (token row, head): delta = sum_d dO * O
 __global__ void __launch_bounds__(256)
@@ -398,53 +404,61 @@ __device__ __forceinline__ void store_tile_chunk(unsigned char* tile, int r, int
     }
 }
 
+__device__ __forceinline__ void owners_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 template <int D>
 __global__ void __launch_bounds__(AT_THREADS, 1)
-attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do, AttnBwdParams p) {
-    constexpr uint32_t TILE_BYTES = 128 * D * 2;
-    constexpr uint32_t PT_BYTES = 128 * 128 * 2;
-    constexpr uint32_t TMEM_COLS = 512;   // S [0,128) dP [128,256) dV [256,256+D) dK [256+D,256+2D)
-    constexpr uint32_t IDESC_S = make_idesc_f16_f32(128, 128, 0, 0);
-    constexpr uint32_t IDESC_ACC = make_idesc_f16_f32(128, D, 1, 1);
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do64, AttnBwdParams p) {
+    constexpr uint32_t KV_BYTES = 128 * D * 2;            // this block's K and V tiles
+    constexpr uint32_t SUB_BYTES = AT_SUB * D * 2;        // a 64-query tile of Q or dO
+    constexpr uint32_t PT_BYTES = 128 * AT_SUB * 2;       // P^T / dS^T tile: 128 keys x 64 queries
+    constexpr uint32_t SUB_ATOM = AT_SUB * 128;           // bytes between the 64-column atoms of a 64-row tile
+    constexpr uint32_t TMEM_COLS = 512;   // S^T x2 [0,128)  dP^T x2 [128,256)  dV [256,256+D)  dK [256+D,256+2D)
+    constexpr uint32_t IDESC_ST = make_idesc_f16_f32(128, AT_SUB, 0, 0);
+    constexpr uint32_t IDESC_ACC = make_idesc_f16_f32(128, D, 0, 1);
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* sK = base;
-    unsigned char* sV = sK + TILE_BYTES;
-    unsigned char* sQ = sV + TILE_BYTES;
-    unsigned char* sDO = sQ + TILE_BYTES;
-    unsigned char* sP = sDO + TILE_BYTES;
-    unsigned char* sDS = sP + PT_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + PT_BYTES);
+    unsigned char* sV = sK + KV_BYTES;
+    unsigned char* sQ = sV + KV_BYTES;                    // 2 tiles
+    unsigned char* sDO = sQ + 2 * SUB_BYTES;              // 2 tiles
+    unsigned char* sPT = sDO + 2 * SUB_BYTES;             // 2 tiles
+    unsigned char* sDST = sPT + 2 * PT_BYTES;             // 2 tiles
+    float* stat = reinterpret_cast<float*>(sDST + 2 * PT_BYTES);      // [2][lse2 x 64 | delta x 64]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(stat + 2 * 128);
     uint64_t* kv_full = bars;
-    uint64_t* qdo_full = bars + 1;
-    uint64_t* qdo_empty = bars + 2;
-    uint64_t* sdp_full = bars + 3;
-    uint64_t* sdp_empty = bars + 4;
-    uint64_t* pds_full = bars + 5;
-    uint64_t* pds_empty = bars + 6;
-    uint64_t* acc_full = bars + 7;
-    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 8);
+    uint64_t* qdo_full = bars + 1;     // 2
+    uint64_t* qdo_empty = bars + 3;    // 2
+    uint64_t* s_full = bars + 5;       // 2
+    uint64_t* s_empty = bars + 7;      // 2
+    uint64_t* p_full = bars + 9;       // 2
+    uint64_t* p_empty = bars + 11;     // 2
+    uint64_t* acc_full = bars + 13;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 14);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int jblk = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
     const int k0 = jblk * AT_BKV;
     const int len = p.lens ? min(max(p.lens[b], 0), p.tokens) : p.tokens;
-    const int nqb = (p.tokens + AT_BQ - 1) / AT_BQ;
+    const int nsub = (p.tokens + AT_SUB - 1) / AT_SUB;
+    const int sub0 = k0 / AT_SUB;             // first query sub-block that can see a key of this block
     const int row_base = b * p.tokens;
     const int col = head * D;
     const bool active = k0 < len;           // otherwise no query sees any key of this block
-    const int niter = active ? nqb - jblk : 0;
+    const int niter = active ? nsub - sub0 : 0;
 
     if (threadIdx.x == 0) {
         mbar_init(kv_full, 1);
-        mbar_init(qdo_full, 1);
-        mbar_init(qdo_empty, 1);
-        mbar_init(sdp_full, 1);
-        mbar_init(sdp_empty, 128);
-        mbar_init(pds_full, 128);
-        mbar_init(pds_empty, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&qdo_full[i], 1);
+            mbar_init(&qdo_empty[i], 1);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&s_empty[i], 128);
+            mbar_init(&p_full[i], 128);
+            mbar_init(&p_empty[i], 1);
+        }
         mbar_init(acc_full, 1);
         fence_barrier_init();
     }
@@ -461,21 +475,22 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (warp == 0) {
             if (lane == 0) {
                 bool ok = true;
-                mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+                mbar_arrive_expect_tx(kv_full, 2 * KV_BYTES);
 #pragma unroll
                 for (int a = 0; a < D / 64; a++) {
                     tma_load_2d(sK + a * 16384, &tmap_k, kv_full, col + a * 64, row_base + k0);
                     tma_load_2d(sV + a * 16384, &tmap_v, kv_full, col + a * 64, row_base + k0);
                 }
                 for (int it = 0; it < niter && ok; it++) {
-                    ok = mbar_wait(qdo_empty, (it & 1) ^ 1);
+                    const int sb = it & 1;
+                    ok = mbar_wait(&qdo_empty[sb], ((it >> 1) & 1) ^ 1);
                     if (!ok) break;
-                    const int q0 = (jblk + it) * AT_BQ;
-                    mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
+                    const int q0 = (sub0 + it) * AT_SUB;
+                    mbar_arrive_expect_tx(&qdo_full[sb], 2 * SUB_BYTES);
 #pragma unroll
                     for (int a = 0; a < D / 64; a++) {
-                        tma_load_2d(sQ + a * 16384, &tmap_q, qdo_full, col + a * 64, row_base + q0);
-                        tma_load_2d(sDO + a * 16384, &tmap_do, qdo_full, col + a * 64, row_base + q0);
+                        tma_load_2d(sQ + sb * SUB_BYTES + a * SUB_ATOM, &tmap_q64, &qdo_full[sb], col + a * 64, row_base + q0);
+                        tma_load_2d(sDO + sb * SUB_BYTES + a * SUB_ATOM, &tmap_do64, &qdo_full[sb], col + a * 64, row_base + q0);
                     }
                 }
                 if (!ok) atomicExch(&g_attn_error, 11);
@@ -483,89 +498,106 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         } else if (warp == 1) {
             if (lane == 0) {
                 bool ok = mbar_wait(kv_full, 0);
-                const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
-                const uint32_t p_addr = smem_u32(sP), ds_addr = smem_u32(sDS);
-                for (int it = 0; it < niter && ok; it++) {
-                    ok = mbar_wait(qdo_full, it & 1) && mbar_wait(sdp_empty, (it & 1) ^ 1);
-                    if (!ok) break;
-                    tcgen05_fence_after();
+                const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+                // step `it` issues the transposed scores of sub-block it and then the accumulations of sub-block it - 1,
+                // whose P^T / dS^T the row owners produced while the scores of it were being computed
+                for (int it = 0; it <= niter && ok; it++) {
+                    if (it < niter) {
+                        const int sb = it & 1;
+                        ok = mbar_wait(&qdo_full[sb], (it >> 1) & 1) && mbar_wait(&s_empty[sb], ((it >> 1) & 1) ^ 1);
+                        if (!ok) break;
+                        tcgen05_fence_after();
+                        const uint32_t q_addr = smem_u32(sQ + sb * SUB_BYTES), do_addr = smem_u32(sDO + sb * SUB_BYTES);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; kk++) {
-                        const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-                        umma_f16_ss(tmem_base, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
-                                    IDESC_S, kk != 0 ? 1u : 0u);
-                    }
+                        for (int kk = 0; kk < D / 16; kk++)      // S^T = K Q^T : [128 keys x 64 queries]
+                            umma_f16_ss(tmem_base + sb * AT_SUB, make_smem_desc_sw128(k_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                                        make_smem_desc_sw128(q_addr + (kk >> 2) * SUB_ATOM + (kk & 3) * 32, 16, 1024), IDESC_ST, kk != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; kk++) {
-                        const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-                        umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(do_addr + off, 16, 1024), make_smem_desc_sw128(v_addr + off, 16, 1024),
-                                    IDESC_S, kk != 0 ? 1u : 0u);
+                        for (int kk = 0; kk < D / 16; kk++)      // dP^T = V dO^T
+                            umma_f16_ss(tmem_base + 128 + sb * AT_SUB, make_smem_desc_sw128(v_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                                        make_smem_desc_sw128(do_addr + (kk >> 2) * SUB_ATOM + (kk & 3) * 32, 16, 1024), IDESC_ST, kk != 0 ? 1u : 0u);
+                        umma_commit(&s_full[sb]);
                     }
-                    umma_commit(sdp_full);
-                    ok = mbar_wait(pds_full, it & 1);
-                    if (!ok) break;
-                    tcgen05_fence_after();
+                    if (it >= 1) {
+                        const int j = it - 1, sb = j & 1;
+                        ok = mbar_wait(&p_full[sb], (j >> 1) & 1);
+                        if (!ok) break;
+                        tcgen05_fence_after();
+                        const uint32_t q_addr = smem_u32(sQ + sb * SUB_BYTES), do_addr = smem_u32(sDO + sb * SUB_BYTES);
+                        const uint32_t pt_addr = smem_u32(sPT + sb * PT_BYTES), dst_addr = smem_u32(sDST + sb * PT_BYTES);
 #pragma unroll
-                    for (int kk = 0; kk < AT_BQ / 16; kk++) {
-                        // dV += P^T dO ; dK += dS^T Q   (contraction over the 128 query rows)
-                        umma_f16_ss(tmem_base + 256, make_smem_desc_sw128(p_addr + kk * 2048, 16384, 1024),
-                                    make_smem_desc_sw128(do_addr + kk * 2048, 16384, 1024), IDESC_ACC, (it | kk) != 0 ? 1u : 0u);
-                    }
+                        for (int kk = 0; kk < AT_SUB / 16; kk++)      // dV += P^T dO  (contraction over the 64 queries)
+                            umma_f16_ss(tmem_base + 256, make_smem_desc_sw128(pt_addr + kk * 32, 16, 1024),
+                                        make_smem_desc_sw128(do_addr + kk * 2048, SUB_ATOM, 1024), IDESC_ACC, (j | kk) != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < AT_BQ / 16; kk++) {
-                        umma_f16_ss(tmem_base + 256 + D, make_smem_desc_sw128(ds_addr + kk * 2048, 16384, 1024),
-                                    make_smem_desc_sw128(q_addr + kk * 2048, 16384, 1024), IDESC_ACC, (it | kk) != 0 ? 1u : 0u);
+                        for (int kk = 0; kk < AT_SUB / 16; kk++)      // dK += dS^T Q
+                            umma_f16_ss(tmem_base + 256 + D, make_smem_desc_sw128(dst_addr + kk * 32, 16, 1024),
+                                        make_smem_desc_sw128(q_addr + kk * 2048, SUB_ATOM, 1024), IDESC_ACC, (j | kk) != 0 ? 1u : 0u);
+                        umma_commit(&qdo_empty[sb]);
+                        umma_commit(&p_empty[sb]);
                     }
-                    umma_commit(qdo_empty);
-                    umma_commit(pds_empty);
                 }
                 if (ok) umma_commit(acc_full);
                 if (!ok) atomicExch(&g_attn_error, 12);
             }
         } else {
+            // ---------------- row owners: one thread per key ----------------
             const int quarter = warp & 3;
             const int r = quarter * 32 + lane;
+            const int kj = k0 + r;                               // this thread's key
+            const bool k_ok = kj < len;
             const float slope2 = p.slopes ? p.slopes[head] * 1.4426950408889634f : 0.0f;
+            const float bias2 = slope2 * (float)kj;              // the ALiBi term is constant along a key's row
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
             const int64_t stat_base = ((int64_t)b * p.heads + head) * p.tokens;
             bool ok = true;
-            for (int it = 0; it < niter && ok; it++) {
-                const int qi = (jblk + it) * AT_BQ + r;
-                const bool q_ok = qi < p.tokens;
-                const float lse2 = q_ok ? p.lse[stat_base + qi] * 1.4426950408889634f : 0.0f;
-                const float dlt = q_ok ? p.delta[stat_base + qi] : 0.0f;
-                const int klimit = q_ok ? min(qi + 1, len) : 0;
-                ok = mbar_wait(sdp_full, it & 1);
-                if (!ok) break;
-                if (it > 0) ok = mbar_wait(pds_empty, (it - 1) & 1);
-                if (!ok) break;
+            for (int it = 0; it < niter; it++) {
+                const int sb = it & 1;
+                const int q0 = (sub0 + it) * AT_SUB;
+                {
+                    // the sub-block's 64 lse (in log2 units) and 64 delta values, one per thread
+                    const int qi = q0 + (r & 63);
+                    float v = 0.0f;
+                    if (qi < p.tokens) v = r < 64 ? p.lse[stat_base + qi] * 1.4426950408889634f : p.delta[stat_base + qi];
+                    stat[sb * 128 + r] = v;
+                }
+                // Orders this step's writes after every thread's reads two steps ago.  Every owner warp reaches it in
+                // every step, also one whose bounded wait gave up (it only skips the work), so nobody is left waiting.
+                owners_barrier();
+                if (ok) ok = mbar_wait(&s_full[sb], (it >> 1) & 1);
+                if (ok && it >= 2) ok = mbar_wait(&p_empty[sb], ((it - 2) >> 1) & 1);
+                if (!ok) continue;
                 tcgen05_fence_after();
+                const float* lse2 = stat + sb * 128;
+                const float* dlt = lse2 + 64;
+                unsigned char* pt = sPT + sb * PT_BYTES;
+                unsigned char* dst = sDST + sb * PT_BYTES;
 #pragma unroll 1
-                for (int c0 = 0; c0 < AT_BKV; c0 += 32) {
+                for (int c0 = 0; c0 < AT_SUB; c0 += 32) {
                     uint32_t sv[32], dv[32];
-                    tmem_ld_32x32b_x32(lane_addr + c0, sv);
-                    tmem_ld_32x32b_x32(lane_addr + 128 + c0, dv);
+                    tmem_ld_32x32b_x32(lane_addr + sb * AT_SUB + c0, sv);
+                    tmem_ld_32x32b_x32(lane_addr + 128 + sb * AT_SUB + c0, dv);
                     tmem_ld_wait();
                     float pr[32], ds[32];
 #pragma unroll
                     for (int e = 0; e < 32; e++) {
-                        const int kj = k0 + c0 + e;
-                        const float pe = kj < klimit ? fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, slope2 * (float)kj) - lse2) : 0.0f;
+                        const int qi = q0 + c0 + e;
+                        const bool vis = k_ok && kj <= qi && qi < p.tokens;
+                        const float pe = vis ? fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, bias2) - lse2[c0 + e]) : 0.0f;
                         pr[e] = pe;
-                        ds[e] = pe * (__uint_as_float(dv[e]) - dlt);
+                        ds[e] = pe * (__uint_as_float(dv[e]) - dlt[c0 + e]);
                     }
-                    store_tile_chunk(sP, r, c0, pr);
-                    store_tile_chunk(sDS, r, c0, ds);
+                    store_tile_chunk(pt, r, c0, pr);
+                    store_tile_chunk(dst, r, c0, ds);
                 }
                 tcgen05_fence_before();
-                mbar_arrive(sdp_empty);
+                mbar_arrive(&s_empty[sb]);
                 fence_proxy_async();
-                mbar_arrive(pds_full);
+                mbar_arrive(&p_full[sb]);
             }
             if (ok) ok = mbar_wait(acc_full, 0);
             if (ok) {
                 tcgen05_fence_after();
-                const int kj = k0 + r;
                 __half* dvrow = p.dv + (int64_t)(row_base + kj) * p.ld_g + col;
                 __half* dkrow = p.dk + (int64_t)(row_base + kj) * p.ld_g + col;
 #pragma unroll 1
@@ -613,31 +645,33 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
 template <int D>
 __global__ void __launch_bounds__(AT_THREADS, 1)
-attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do, AttnBwdParams p) {
-    constexpr uint32_t TILE_BYTES = 128 * D * 2;
-    constexpr uint32_t PT_BYTES = 128 * 128 * 2;
-    constexpr uint32_t TMEM_COLS = 512;   // S [0,128) dP [128,256) dQ [256,256+D)
-    constexpr uint32_t IDESC_S = make_idesc_f16_f32(128, 128, 0, 0);
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k64,
+                   const __grid_constant__ CUtensorMap tmap_v64, const __grid_constant__ CUtensorMap tmap_do, AttnBwdParams p) {
+    constexpr uint32_t Q_BYTES = 128 * D * 2;             // this block's Q and dO tiles
+    constexpr uint32_t SUB_BYTES = AT_SUB * D * 2;        // a 64-key tile of K or V
+    constexpr uint32_t DS_BYTES = 128 * AT_SUB * 2;       // dS tile: 128 queries x 64 keys
+    constexpr uint32_t SUB_ATOM = AT_SUB * 128;
+    constexpr uint32_t TMEM_COLS = 512;   // S x2 [0,128)  dP x2 [128,256)  dQ [256,256+D)
+    constexpr uint32_t IDESC_S = make_idesc_f16_f32(128, AT_SUB, 0, 0);
     constexpr uint32_t IDESC_DQ = make_idesc_f16_f32(128, D, 0, 1);
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = base;
-    unsigned char* sDO = sQ + TILE_BYTES;
-    unsigned char* sK = sDO + TILE_BYTES;
-    unsigned char* sV = sK + TILE_BYTES;
-    unsigned char* sDS = sV + TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + PT_BYTES);
+    unsigned char* sDO = sQ + Q_BYTES;
+    unsigned char* sK = sDO + Q_BYTES;                    // 2 tiles
+    unsigned char* sV = sK + 2 * SUB_BYTES;               // 2 tiles
+    unsigned char* sDS = sV + 2 * SUB_BYTES;              // 2 tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * DS_BYTES);
     uint64_t* qdo_full = bars;
-    uint64_t* kv_full = bars + 1;
-    uint64_t* kv_empty = bars + 2;
-    uint64_t* sdp_full = bars + 3;
-    uint64_t* sdp_empty = bars + 4;
-    uint64_t* ds_full = bars + 5;
-    uint64_t* ds_empty = bars + 6;
-    uint64_t* acc_full = bars + 7;
-    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 8);
+    uint64_t* kv_full = bars + 1;      // 2
+    uint64_t* kv_empty = bars + 3;     // 2
+    uint64_t* s_full = bars + 5;       // 2
+    uint64_t* s_empty = bars + 7;      // 2
+    uint64_t* ds_full = bars + 9;      // 2
+    uint64_t* ds_empty = bars + 11;    // 2
+    uint64_t* acc_full = bars + 13;
+    uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(bars + 14);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qblk = (int)gridDim.x - 1 - (int)blockIdx.x;
@@ -645,18 +679,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int q0 = qblk * AT_BQ;
     const int len = p.lens ? min(max(p.lens[b], 0), p.tokens) : p.tokens;
     const int key_end = min(q0 + AT_BQ, len);
-    const int nkb = key_end > 0 ? (key_end + AT_BKV - 1) / AT_BKV : 0;
+    const int niter = key_end > 0 ? (key_end + AT_SUB - 1) / AT_SUB : 0;      // 64-key sub-blocks any row of the tile sees
     const int row_base = b * p.tokens;
     const int col = head * D;
 
     if (threadIdx.x == 0) {
         mbar_init(qdo_full, 1);
-        mbar_init(kv_full, 1);
-        mbar_init(kv_empty, 1);
-        mbar_init(sdp_full, 1);
-        mbar_init(sdp_empty, 128);
-        mbar_init(ds_full, 128);
-        mbar_init(ds_empty, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&kv_full[i], 1);
+            mbar_init(&kv_empty[i], 1);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&s_empty[i], 128);
+            mbar_init(&ds_full[i], 128);
+            mbar_init(&ds_empty[i], 1);
+        }
         mbar_init(acc_full, 1);
         fence_barrier_init();
     }
@@ -669,24 +705,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_base_smem;
 
-    if (nkb > 0) {
+    if (niter > 0) {
         if (warp == 0) {
             if (lane == 0) {
                 bool ok = true;
-                mbar_arrive_expect_tx(qdo_full, 2 * TILE_BYTES);
+                mbar_arrive_expect_tx(qdo_full, 2 * Q_BYTES);
 #pragma unroll
                 for (int a = 0; a < D / 64; a++) {
                     tma_load_2d(sQ + a * 16384, &tmap_q, qdo_full, col + a * 64, row_base + q0);
                     tma_load_2d(sDO + a * 16384, &tmap_do, qdo_full, col + a * 64, row_base + q0);
                 }
-                for (int j = 0; j < nkb && ok; j++) {
-                    ok = mbar_wait(kv_empty, (j & 1) ^ 1);
+                for (int it = 0; it < niter && ok; it++) {
+                    const int sb = it & 1;
+                    ok = mbar_wait(&kv_empty[sb], ((it >> 1) & 1) ^ 1);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(kv_full, 2 * TILE_BYTES);
+                    mbar_arrive_expect_tx(&kv_full[sb], 2 * SUB_BYTES);
 #pragma unroll
                     for (int a = 0; a < D / 64; a++) {
-                        tma_load_2d(sK + a * 16384, &tmap_k, kv_full, col + a * 64, row_base + j * AT_BKV);
-                        tma_load_2d(sV + a * 16384, &tmap_v, kv_full, col + a * 64, row_base + j * AT_BKV);
+                        tma_load_2d(sK + sb * SUB_BYTES + a * SUB_ATOM, &tmap_k64, &kv_full[sb], col + a * 64, row_base + it * AT_SUB);
+                        tma_load_2d(sV + sb * SUB_BYTES + a * SUB_ATOM, &tmap_v64, &kv_full[sb], col + a * 64, row_base + it * AT_SUB);
                     }
                 }
                 if (!ok) atomicExch(&g_attn_error, 21);
@@ -694,36 +731,37 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         } else if (warp == 1) {
             if (lane == 0) {
                 bool ok = mbar_wait(qdo_full, 0);
-                const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
-                const uint32_t ds_addr = smem_u32(sDS);
-                for (int j = 0; j < nkb && ok; j++) {
-                    ok = mbar_wait(kv_full, j & 1) && mbar_wait(sdp_empty, (j & 1) ^ 1);
-                    if (!ok) break;
-                    tcgen05_fence_after();
+                const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
+                for (int it = 0; it <= niter && ok; it++) {
+                    if (it < niter) {
+                        const int sb = it & 1;
+                        ok = mbar_wait(&kv_full[sb], (it >> 1) & 1) && mbar_wait(&s_empty[sb], ((it >> 1) & 1) ^ 1);
+                        if (!ok) break;
+                        tcgen05_fence_after();
+                        const uint32_t k_addr = smem_u32(sK + sb * SUB_BYTES), v_addr = smem_u32(sV + sb * SUB_BYTES);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; kk++) {
-                        const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-                        umma_f16_ss(tmem_base, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
-                                    IDESC_S, kk != 0 ? 1u : 0u);
-                    }
+                        for (int kk = 0; kk < D / 16; kk++)      // S = Q K^T : [128 queries x 64 keys]
+                            umma_f16_ss(tmem_base + sb * AT_SUB, make_smem_desc_sw128(q_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                                        make_smem_desc_sw128(k_addr + (kk >> 2) * SUB_ATOM + (kk & 3) * 32, 16, 1024), IDESC_S, kk != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; kk++) {
-                        const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-                        umma_f16_ss(tmem_base + 128, make_smem_desc_sw128(do_addr + off, 16, 1024), make_smem_desc_sw128(v_addr + off, 16, 1024),
-                                    IDESC_S, kk != 0 ? 1u : 0u);
+                        for (int kk = 0; kk < D / 16; kk++)      // dP = dO V^T
+                            umma_f16_ss(tmem_base + 128 + sb * AT_SUB, make_smem_desc_sw128(do_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                                        make_smem_desc_sw128(v_addr + (kk >> 2) * SUB_ATOM + (kk & 3) * 32, 16, 1024), IDESC_S, kk != 0 ? 1u : 0u);
+                        umma_commit(&s_full[sb]);
                     }
-                    umma_commit(sdp_full);
-                    ok = mbar_wait(ds_full, j & 1);
-                    if (!ok) break;
-                    tcgen05_fence_after();
+                    if (it >= 1) {
+                        const int j = it - 1, sb = j & 1;
+                        ok = mbar_wait(&ds_full[sb], (j >> 1) & 1);
+                        if (!ok) break;
+                        tcgen05_fence_after();
+                        const uint32_t k_addr = smem_u32(sK + sb * SUB_BYTES), ds_addr = smem_u32(sDS + sb * DS_BYTES);
 #pragma unroll
-                    for (int kk = 0; kk < AT_BKV / 16; kk++) {
-                        // dQ += dS K_j : A = dS [q x keys] K-major, B = K_j [keys x d], d contiguous (MN-major)
-                        umma_f16_ss(tmem_base + 256, make_smem_desc_sw128(ds_addr + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
-                                    make_smem_desc_sw128(k_addr + kk * 2048, 16384, 1024), IDESC_DQ, (j | kk) != 0 ? 1u : 0u);
+                        for (int kk = 0; kk < AT_SUB / 16; kk++)      // dQ += dS K : A = dS [q x 64 keys] K-major, B = K [64 keys x d], d contiguous
+                            umma_f16_ss(tmem_base + 256, make_smem_desc_sw128(ds_addr + kk * 32, 16, 1024),
+                                        make_smem_desc_sw128(k_addr + kk * 2048, SUB_ATOM, 1024), IDESC_DQ, (j | kk) != 0 ? 1u : 0u);
+                        umma_commit(&kv_empty[sb]);
+                        umma_commit(&ds_empty[sb]);
                     }
-                    umma_commit(kv_empty);
-                    umma_commit(ds_empty);
                 }
                 if (ok) umma_commit(acc_full);
                 if (!ok) atomicExch(&g_attn_error, 22);
@@ -740,31 +778,33 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const float dlt = q_ok ? p.delta[stat_base + qi] : 0.0f;
             const int klimit = q_ok ? min(qi + 1, len) : 0;
             bool ok = true;
-            for (int j = 0; j < nkb && ok; j++) {
-                ok = mbar_wait(sdp_full, j & 1);
+            for (int it = 0; it < niter && ok; it++) {
+                const int sb = it & 1;
+                ok = mbar_wait(&s_full[sb], (it >> 1) & 1);
                 if (!ok) break;
-                if (j > 0) ok = mbar_wait(ds_empty, (j - 1) & 1);
+                if (it >= 2) ok = mbar_wait(&ds_empty[sb], ((it - 2) >> 1) & 1);
                 if (!ok) break;
                 tcgen05_fence_after();
+                unsigned char* dst = sDS + sb * DS_BYTES;
 #pragma unroll 1
-                for (int c0 = 0; c0 < AT_BKV; c0 += 32) {
+                for (int c0 = 0; c0 < AT_SUB; c0 += 32) {
                     uint32_t sv[32], dv[32];
-                    tmem_ld_32x32b_x32(lane_addr + c0, sv);
-                    tmem_ld_32x32b_x32(lane_addr + 128 + c0, dv);
+                    tmem_ld_32x32b_x32(lane_addr + sb * AT_SUB + c0, sv);
+                    tmem_ld_32x32b_x32(lane_addr + 128 + sb * AT_SUB + c0, dv);
                     tmem_ld_wait();
                     float ds[32];
 #pragma unroll
                     for (int e = 0; e < 32; e++) {
-                        const int kj = j * AT_BKV + c0 + e;
+                        const int kj = it * AT_SUB + c0 + e;
                         const float pe = kj < klimit ? fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, slope2 * (float)kj) - lse2) : 0.0f;
                         ds[e] = pe * (__uint_as_float(dv[e]) - dlt);
                     }
-                    store_tile_chunk(sDS, r, c0, ds);
+                    store_tile_chunk(dst, r, c0, ds);
                 }
                 tcgen05_fence_before();
-                mbar_arrive(sdp_empty);
+                mbar_arrive(&s_empty[sb]);
                 fence_proxy_async();
-                mbar_arrive(ds_full);
+                mbar_arrive(&ds_full[sb]);
             }
             if (ok) ok = mbar_wait(acc_full, 0);
             if (ok) {
@@ -806,9 +846,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 
 template <int D>
 static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                           const CUtensorMap& tq64, const CUtensorMap& tk64, const CUtensorMap& tv64, const CUtensorMap& tdo64,
                            const AttnBwdParams& p, cudaStream_t st) {
-    constexpr size_t smem_dkv = 1024 + (size_t)128 * D * 2 * 4 + 2 * 128 * 128 * 2 + 256;
-    constexpr size_t smem_dq = 1024 + (size_t)128 * D * 2 * 4 + 128 * 128 * 2 + 256;
+    // K, V + two 64-row tiles each of Q, dO, P^T, dS^T + the lse / delta staging; Q, dO + two 64-row tiles each of K, V, dS
+    constexpr size_t smem_dkv = 1024 + (size_t)2 * 128 * D * 2 + 4 * (size_t)AT_SUB * D * 2 + 4 * (size_t)128 * AT_SUB * 2 + 1024 + 256;
+    constexpr size_t smem_dq = 1024 + (size_t)2 * 128 * D * 2 + 4 * (size_t)AT_SUB * D * 2 + 2 * (size_t)128 * AT_SUB * 2 + 256;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
@@ -821,10 +863,10 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
         return BRK_CUDA_ERROR;
     }
     dim3 grid((unsigned)((p.tokens + AT_BQ - 1) / AT_BQ), (unsigned)p.heads, (unsigned)p.batch);
-    attn_bwd_dkv_kernel<D><<<grid, AT_THREADS, smem_dkv, st>>>(tq, tk, tv, tdo, p);
+    attn_bwd_dkv_kernel<D><<<grid, AT_THREADS, smem_dkv, st>>>(tq64, tk, tv, tdo64, p);
     int rc = launch_status("attn_bwd_dkv_kernel");
     if (rc) return rc;
-    attn_bwd_dq_kernel<D><<<grid, AT_THREADS, smem_dq, st>>>(tq, tk, tv, tdo, p);
+    attn_bwd_dq_kernel<D><<<grid, AT_THREADS, smem_dq, st>>>(tq, tk64, tv64, tdo, p);
     return launch_status("attn_bwd_dq_kernel");
 }
 
@@ -899,9 +941,11 @@ extern "C" int brk_flash_attn_bwd(const void* q, const void* k, const void* v, i
         if (rc) return rc;
     }
     const uint64_t rows = (uint64_t)batch * tokens, cols = (uint64_t)hd;
-    CUtensorMap tq, tk, tv, tdo;
+    CUtensorMap tq, tk, tv, tdo, tq64, tk64, tv64, tdo64;      // boxes of 128 rows for the owned block, of 64 rows for the walked operand
     if (!make_tmap_2d_f16(&tq, q, rows, cols, (uint64_t)ld_qkv, 64, 128) || !make_tmap_2d_f16(&tk, k, rows, cols, (uint64_t)ld_qkv, 64, 128) ||
-        !make_tmap_2d_f16(&tv, v, rows, cols, (uint64_t)ld_qkv, 64, 128) || !make_tmap_2d_f16(&tdo, d_out, rows, cols, (uint64_t)ld_out, 64, 128)) {
+        !make_tmap_2d_f16(&tv, v, rows, cols, (uint64_t)ld_qkv, 64, 128) || !make_tmap_2d_f16(&tdo, d_out, rows, cols, (uint64_t)ld_out, 64, 128) ||
+        !make_tmap_2d_f16(&tq64, q, rows, cols, (uint64_t)ld_qkv, 64, AT_SUB) || !make_tmap_2d_f16(&tk64, k, rows, cols, (uint64_t)ld_qkv, 64, AT_SUB) ||
+        !make_tmap_2d_f16(&tv64, v, rows, cols, (uint64_t)ld_qkv, 64, AT_SUB) || !make_tmap_2d_f16(&tdo64, d_out, rows, cols, (uint64_t)ld_out, 64, AT_SUB)) {
         set_error_message("brk_flash_attn_bwd: could not encode a tensor map (pointers must be 16-byte aligned)");
         return BRK_CUDA_ERROR;
     }
@@ -919,6 +963,6 @@ extern "C" int brk_flash_attn_bwd(const void* q, const void* k, const void* v, i
     p.heads = heads;
     p.scale = (float)(1.0 / sqrt((double)head_dim));
     p.scale_log2 = (float)(1.4426950408889634 / sqrt((double)head_dim));
-    if (head_dim == 128) return launch_attn_bwd<128>(tq, tk, tv, tdo, p, st);
-    return launch_attn_bwd<64>(tq, tk, tv, tdo, p, st);
+    if (head_dim == 128) return launch_attn_bwd<128>(tq, tk, tv, tdo, tq64, tk64, tv64, tdo64, p, st);
+    return launch_attn_bwd<64>(tq, tk, tv, tdo, tq64, tk64, tv64, tdo64, p, st);
 }
