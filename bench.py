@@ -768,6 +768,13 @@ def run_case(args):
         for _ in range(reps):
             brk.call("brk_flash_attn_fwd", base, base + 2 * H, base + 4 * H, 3 * H, out.data_ptr(), H, lse.data_ptr(), 0, 0,
                      B, T, heads, d, ops.stream())
+        dout = torch.randn(B * T, H, generator=g, device=dev).half()
+        grads = torch.empty(B * T, 3 * H, device=dev).half()
+        ws = torch.empty(brk.lib().brk_flash_attn_bwd_workspace_bytes(B, T, heads), dtype=torch.uint8, device=dev)
+        gb = grads.data_ptr()
+        for _ in range(reps):
+            brk.call("brk_flash_attn_bwd", base, base + 2 * H, base + 4 * H, 3 * H, out.data_ptr(), dout.data_ptr(), H, lse.data_ptr(),
+                     gb, gb + 2 * H, gb + 4 * H, 3 * H, 0, 0, B, T, heads, d, ws.data_ptr(), ws.numel(), ops.stream())
     else:
         x = torch.randn(TOKENS, HIDDEN4, generator=g, device=dev).half()
         dy = torch.randn(TOKENS, HIDDEN4, generator=g, device=dev).half()

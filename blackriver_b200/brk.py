@@ -59,6 +59,7 @@ SIGNATURES = {
     "brk_xmask_build": (i32, [p, p, i32, i32, p]),
     "brk_gemm": (i32, [p, p, p, i64, i64, i64, i32, i32, i64, i64, i64, i64, i64, i64, i64, f32, f32, p, i32, p]),
     "brk_adam_step": (i32, [p, p, p, p, i32, p, i64, f32, f32, f32, f32, i32, f32, p]),
+    "brk_adam_status": (i32, []),
     "brk_embedding_scatter_add": (i32, [p, p, p, i64, i64, i64, i32, p]),
     "brk_init_normal": (i32, [p, i64, f32, f32, C.c_uint64, i32, p]),
     "brk_gemm_f16_supported": (i32, [i64, i64, i64, i32, i32, i64, i64, p, p]),

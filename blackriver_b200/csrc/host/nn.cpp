@@ -285,13 +285,13 @@ BR_WORD(LossBackwardW, {
     auto t = pop_tensors<3>(stack);
     t[0]->op_loss_backward_w(t[0], t[1], t[2]);
 })
-// ( -- code )  waits for the device; 0 when no tensor-core kernel gave up a bounded wait since the last query,
-// else 16 * (GEMM status) + (attention status)
+// ( -- code )  waits for the device; 0 when no tensor-core kernel gave up a bounded wait and no optimizer launch met a
+// non-finite gradient since the last query, else 256 * (Adam status) + 16 * (GEMM status) + (attention status)
 BR_WORD(KernelStatus, {
     int code = 0;
     if (ComputingContext::booted) {
         BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::cuda_stream));
-        code = 16 * brk_gemm_f16_status() + brk_flash_attn_status();
+        code = 256 * brk_adam_status() + 16 * brk_gemm_f16_status() + brk_flash_attn_status();
     }
     stack.push_number((double)code);
 })

@@ -234,6 +234,7 @@ int main(int argc, char** argv) {
             // the one wait of the step: no update is applied on top of a tensor-core kernel that gave up a wait
             env.run(status);
             const int code = (int)env.stack().pop_number();
+            br_assert(code < 256, "the previous optimizer step met non-finite gradients: lower --loss-scale");
             br_assert(code == 0, "a tensor-core kernel gave up a bounded wait; the optimizer step was not applied");
             double loss_sum = 0.0;
             int loss_n = 0;

@@ -15,6 +15,8 @@
 namespace brk {
 namespace ptx {
 
+// Waiting roles back off with nanosleep after a few attempts: idle warps that poll flat out take issue slots and power
+// from the roles that work (measured: the GEMM family lost 12 % with 65536 attempts before the first sleep).
 constexpr uint32_t WAIT_LIMIT = 20u * 1000u * 1000u;  // polls with back-off, about a second
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -10,7 +10,12 @@ namespace brk {
 //   g = grad * grad_scale;  m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g^2
 //   w -= lr/(1-b1^t) * m / (sqrt(v)/sqrt(1-b2^t) + eps);  w16 = fp16(w)
 // 28 bytes of traffic per parameter (2 grad + 12 read + 12 write + 2 fp16 weight).
+// An element whose scaled gradient is not finite (an fp16 gradient that overflowed under the loss scale) is left
+// untouched -- weight and moments keep their values instead of turning NaN for good -- and raises g_adam_nonfinite,
+// which brk_adam_status() reports.
 // ------------------------------------------------------------------------------------------
+__device__ int g_adam_nonfinite = 0;
+
 template <typename G>
 __global__ void __launch_bounds__(256)
 adam_kernel(float* w, float* m, float* v, const G* g, __half* w16, int64_t n, float step_size, float inv_bc2_sqrt, float beta1,
@@ -23,12 +28,18 @@ adam_kernel(float* w, float* m, float* v, const G* g, __half* w16, int64_t n, fl
 #pragma unroll
             for (int e = 0; e < 4; e++) gg[e] = to_f32(g[i + e]) * grad_scale;
             float* wp = &wv.x; float* mp = &mv.x; float* vp = &vv.x;
+            bool bad = false;
 #pragma unroll
             for (int e = 0; e < 4; e++) {
+                if (!isfinite(gg[e])) {
+                    bad = true;
+                    continue;
+                }
                 mp[e] = beta1 * mp[e] + (1.0f - beta1) * gg[e];
                 vp[e] = beta2 * vp[e] + (1.0f - beta2) * gg[e] * gg[e];
                 wp[e] -= step_size * mp[e] / (sqrtf(vp[e]) * inv_bc2_sqrt + eps);
             }
+            if (bad) g_adam_nonfinite = 1;
             *reinterpret_cast<float4*>(w + i) = wv;
             *reinterpret_cast<float4*>(m + i) = mv;
             *reinterpret_cast<float4*>(v + i) = vv;
@@ -40,6 +51,10 @@ adam_kernel(float* w, float* m, float* v, const G* g, __half* w16, int64_t n, fl
         } else {
             for (int64_t j = i; j < n; j++) {
                 float gj = to_f32(g[j]) * grad_scale;
+                if (!isfinite(gj)) {
+                    g_adam_nonfinite = 1;
+                    continue;
+                }
                 float mj = beta1 * m[j] + (1.0f - beta1) * gj;
                 float vj = beta2 * v[j] + (1.0f - beta2) * gj * gj;
                 m[j] = mj;
@@ -161,4 +176,12 @@ extern "C" int brk_init_normal(void* x, int64_t n, float mean, float std, uint64
     else if (dtype == BRK_F32) init_normal_kernel<float><<<grid, 256, 0, st>>>((float*)x, n, mean, std, seed);
     else return BRK_ATTR_ERROR;
     return launch_status("init_normal_kernel");
+}
+
+// Synchronous: 1 if an Adam launch since the last query skipped elements whose gradient was not finite.
+extern "C" int brk_adam_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, brk::g_adam_nonfinite, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(brk::g_adam_nonfinite, &zero, sizeof(int));
+    return v;
 }

@@ -171,6 +171,8 @@ class Trainer:
         e = self.env
         e.run(self.p_status)
         code = int(e.pop_number())
+        if code >= 256:
+            raise RuntimeError("the previous optimizer step met non-finite gradients (those elements were skipped): lower the loss scale")
         if code != 0:
             raise RuntimeError(f"a tensor-core kernel gave up a bounded wait (status {code}); the optimizer step was not applied")
         self.losses = []

@@ -174,6 +174,10 @@ BRK_API int brk_xmask_build(const int32_t* mask, float* xmask, int batch, int to
  * the fp16 working copy.  step counts from 1.  Pointers 16-byte aligned. */
 BRK_API int brk_adam_step(void* master_w, void* m, void* v, const void* grad, int grad_dtype, void* w16, int64_t n, float lr,
                   float beta1, float beta2, float eps, int step, float grad_scale, void* stream);
+/* Elements whose scaled gradient is not finite (an fp16 gradient that overflowed under the loss scale) are skipped by
+ * brk_adam_step -- weight and moments keep their values -- and remembered: brk_adam_status() (synchronous) returns 1
+ * if that happened since the last query, so that a driver can lower its loss scale. */
+BRK_API int brk_adam_status(void);
 /* table_g[ids[r], :] += dx[r, :]: gradient of brk_embedding_gather (atomic adds). */
 BRK_API int brk_embedding_scatter_add(const void* dx, const int32_t* ids, void* table_g, int64_t n, int64_t hidden, int64_t vocab,
                               int dtype, void* stream);

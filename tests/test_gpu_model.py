@@ -332,3 +332,21 @@ def test_checkpoint_resume_continues_the_same_run(host, tmp_path):
     assert np.abs(wa - wb).max() <= 2.5e-3 and np.median(np.abs(wa - wb)) <= 1e-6      # at most one Adam step apart anywhere
     assert np.abs(ma - mb_).max() <= 1e-2 * np.abs(ma).max()
     assert np.abs(ta.astype(np.float32) - tb.astype(np.float32)).max() <= 2.5e-3
+
+
+def test_adam_skips_non_finite_gradients():
+    """An overflowed fp16 gradient (inf under the loss scale) must not poison the weight or the moments."""
+    from blackriver_b200 import brk, ops
+    n = 1001
+    w = torch.ones(n, device="cuda"); m = torch.zeros(n, device="cuda"); v = torch.zeros(n, device="cuda")
+    g = torch.full((n,), 0.5, dtype=torch.float16, device="cuda")
+    g[7] = float("inf"); g[1000] = float("nan")
+    w16 = torch.empty(n, dtype=torch.float16, device="cuda")
+    assert brk.lib().brk_adam_status() == 0
+    brk.call("brk_adam_step", w.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), brk.F16, w16.data_ptr(), n, 1e-2, 0.9, 0.999, 1e-8, 1, 1.0,
+             ops.stream())
+    torch.cuda.synchronize()
+    assert brk.lib().brk_adam_status() == 1 and brk.lib().brk_adam_status() == 0      # reported once, then cleared
+    wn = w.cpu().numpy()
+    assert np.isfinite(wn).all() and wn[7] == 1.0 and wn[1000] == 1.0 and wn[0] < 1.0
+    assert float(m[7]) == 0.0 and float(v[1000]) == 0.0
