@@ -34,6 +34,11 @@ using namespace ptx;
 
 __device__ int g_attn_error = 0;
 
+// Two row-owner warps per scheduler (warps 2..9): warps w and w + 4 own the same 32 tensor-memory lanes and split
+// the columns of every tile between them; a single owner warp per scheduler cannot hide the latency of its own
+// tensor-memory loads and exponentials.
+constexpr int AT_FWD_THREADS = 64 + 256;
+
 struct AttnFwdParams {
     __half* out;
     float* lse;            // [batch, heads, tokens], natural log
@@ -45,7 +50,7 @@ struct AttnFwdParams {
 };
 
 template <int D>
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __launch_bounds__(AT_FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, AttnFwdParams p) {
     constexpr uint32_t TILE_BYTES = 128 * D * 2;          // Q, K, V tiles: 128 rows x D
@@ -74,6 +79,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     uint64_t* p_empty = p_full + 2;          // 2
     uint64_t* o_full = p_empty + 2;          // 1
     uint32_t* tmem_base_smem = reinterpret_cast<uint32_t*>(o_full + 1);
+    float* xch = reinterpret_cast<float*>(tmem_base_smem + 2);     // [2 halves][128 rows]: what the two owners of a row tell each other
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heavy (late) query blocks are scheduled first
@@ -92,8 +98,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int s = 0; s < VSTAGES; s++) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
         for (int s = 0; s < 2; s++) {
             mbar_init(&s_full[s], 1);
-            mbar_init(&s_empty[s], 128);
-            mbar_init(&p_full[s], 128);
+            mbar_init(&s_empty[s], 256);
+            mbar_init(&p_full[s], 256);
             mbar_init(&p_empty[s], 1);
         }
         mbar_init(o_full, 1);
@@ -186,37 +192,63 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 if (!ok) atomicExch(&g_attn_error, 2);
             }
         } else {
-            // ---------------- softmax / epilogue: one thread per query row ----------------
+            // ---------------- softmax / epilogue: two threads per query row, 64 of the 128 key columns each ----------------
             // Online softmax in one sweep over the key blocks: probabilities are taken relative to a reference maximum
             // m_ref that is only moved (and the output accumulator rescaled) when the running maximum has run ahead of it
             // by more than RESCALE_STEP, so P stays within 2^RESCALE_STEP -- far inside fp16 -- and rescaling is rare.
             const int quarter = warp & 3;
+            const int half = (warp - 2) >> 2;
             const int r = quarter * 32 + lane;          // row inside the tile == TMEM lane
             const int qi = q0 + r;                       // query position in the sequence
             const int klimit = min(qi + 1, len);         // keys [0, klimit) are visible to this row
             const float slope2 = p.slopes ? p.slopes[head] * 1.4426950408889634f : 0.0f;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const int cbase = half * 64;                 // this thread's columns of a 128-key block
             float m_ref = -INFINITY, l = 0.0f;
             bool ok = true;
-            for (int j = 0; j < nkb && ok; j++) {
+            // both owners of a row run the same number of steps and meet at the pair barrier in each of them, also after a
+            // bounded wait gave up (the work is skipped, the barrier is not), so neither is left waiting for the other
+            auto pair_barrier = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(quarter + 1) : "memory"); };
+            for (int j = 0; j < nkb; j++) {
                 const int sb = j & 1;
-                ok = mbar_wait(&s_full[sb], (j >> 1) & 1);
-                if (!ok) break;
-                tcgen05_fence_after();
-                // pass 1: the block's maximum for this row
+                if (ok) ok = mbar_wait(&s_full[sb], (j >> 1) & 1);
+                float t[64];
                 float bm = -INFINITY;
-#pragma unroll 1
-                for (int c0 = 0; c0 < AT_BKV; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(lane_addr + sb * 128 + c0, v);
-                    tmem_ld_wait();
-                    const int kbase = j * AT_BKV + c0;
+                const int kbase = j * AT_BKV + cbase;
+                if (ok) {
+                    tcgen05_fence_after();
+                    // pass 1: scaled scores + ALiBi of this thread's 64 columns into registers, and their maximum;
+                    // key kbase + e gets slope2 * (kbase + e) as one fused multiply-add on constants
+                    const float base2 = slope2 * (float)kbase;
+                    const bool plain = __all_sync(0xffffffffu, kbase + 64 <= klimit);     // no key of the chunk is masked for any row
 #pragma unroll
-                    for (int e = 0; e < 32; e++) {
-                        const int kj = kbase + e;
-                        if (kj < klimit) bm = fmaxf(bm, fmaf(__uint_as_float(v[e]), p.scale_log2, slope2 * (float)kj));
+                    for (int c = 0; c < 2; c++) {
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(lane_addr + sb * 128 + cbase + c * 32, v);
+                        tmem_ld_wait();
+                        if (plain) {
+#pragma unroll
+                            for (int e = 0; e < 32; e++) {
+                                t[c * 32 + e] = fmaf(__uint_as_float(v[e]), p.scale_log2, fmaf(slope2, (float)(c * 32 + e), base2));
+                                bm = fmaxf(bm, t[c * 32 + e]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 32; e++) {
+                                const float x = fmaf(__uint_as_float(v[e]), p.scale_log2, fmaf(slope2, (float)(c * 32 + e), base2));
+                                t[c * 32 + e] = kbase + c * 32 + e < klimit ? x : -INFINITY;
+                                bm = fmaxf(bm, t[c * 32 + e]);
+                            }
+                        }
                     }
+                    tcgen05_fence_before();
+                    mbar_arrive(&s_empty[sb]);         // the scores are in registers: the tensor core may refill the buffer
                 }
+                xch[half * 128 + r] = bm;
+                pair_barrier();
+                bm = fmaxf(bm, xch[(half ^ 1) * 128 + r]);
+                pair_barrier();               // the partner has read this thread's cell before it is written again
+                if (!ok) continue;
                 const bool move = bm > m_ref + RESCALE_STEP;          // also the first visible key of the row (m_ref = -inf)
                 float factor = 1.0f;
                 if (move) {
@@ -227,61 +259,55 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 if (j > 0 && __any_sync(0xffffffffu, move)) {
                     // the accumulator may only be touched between two P V products: wait for the previous one
                     ok = mbar_wait(&p_empty[(j - 1) & 1], ((j - 1) >> 1) & 1);
-                    if (!ok) break;
+                    if (!ok) continue;
                     tcgen05_fence_after();
 #pragma unroll 1
-                    for (int c0 = 0; c0 < D; c0 += 32) {
+                    for (int d0 = half * (D / 2); d0 < (half + 1) * (D / 2); d0 += 32) {
                         uint32_t v[32];
-                        tmem_ld_32x32b_x32(lane_addr + 256 + c0, v);
+                        tmem_ld_32x32b_x32(lane_addr + 256 + d0, v);
                         tmem_ld_wait();
 #pragma unroll
                         for (int e = 0; e < 32; e++) v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
-                        tmem_st_32x32b_x32(lane_addr + 256 + c0, v);
+                        tmem_st_32x32b_x32(lane_addr + 256 + d0, v);
                     }
                     tmem_st_wait();
                     tcgen05_fence_before();
                 }
                 if (j >= 2) ok = mbar_wait(&p_empty[sb], ((j - 2) >> 1) & 1);   // P tile j & 1 consumed by the tensor core
-                if (!ok) break;
+                if (!ok) continue;
                 unsigned char* pt = sP + sb * P_BYTES;
-                // pass 2: probabilities relative to m_ref
-#pragma unroll 1
-                for (int c0 = 0; c0 < AT_BKV; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(lane_addr + sb * 128 + c0, v);
-                    tmem_ld_wait();
-                    const int kbase = j * AT_BKV + c0;
+                // pass 2: probabilities relative to m_ref (a masked score is -inf and gives exactly 0)
 #pragma unroll
-                    for (int g = 0; g < 4; g++) {
-                        uint4 pk;
-                        __half2* h2 = reinterpret_cast<__half2*>(&pk);
+                for (int g = 0; g < 8; g++) {
+                    uint4 pk;
+                    __half2* h2 = reinterpret_cast<__half2*>(&pk);
 #pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const int k0 = kbase + g * 8 + e * 2;
-                            const float p0 = k0 < klimit ? fast_exp2(fmaf(__uint_as_float(v[g * 8 + e * 2]), p.scale_log2, slope2 * (float)k0) - m_ref) : 0.0f;
-                            const float p1 = k0 + 1 < klimit ? fast_exp2(fmaf(__uint_as_float(v[g * 8 + e * 2 + 1]), p.scale_log2, slope2 * (float)(k0 + 1)) - m_ref) : 0.0f;
-                            l += p0 + p1;
-                            h2[e] = __floats2half2_rn(p0, p1);
-                        }
-                        *reinterpret_cast<uint4*>(pt + sw128_offset(r, c0 + g * 8)) = pk;
+                    for (int e = 0; e < 4; e++) {
+                        const float p0 = fast_exp2(t[g * 8 + e * 2] - m_ref);
+                        const float p1 = fast_exp2(t[g * 8 + e * 2 + 1] - m_ref);
+                        l += p0 + p1;
+                        h2[e] = __floats2half2_rn(p0, p1);
                     }
+                    *reinterpret_cast<uint4*>(pt + sw128_offset(r, cbase + g * 8)) = pk;
                 }
-                tcgen05_fence_before();
-                mbar_arrive(&s_empty[sb]);
                 fence_proxy_async();          // make the generic-proxy writes of P visible to the tensor core
                 mbar_arrive(&p_full[sb]);
             }
+            // the row's normaliser is the sum of its two owners' partial sums
+            xch[half * 128 + r] = l;
+            pair_barrier();
+            l += xch[(half ^ 1) * 128 + r];
             // epilogue: O / l -> fp16 -> global, token-major; log-sum-exp for the backward
             if (ok) ok = mbar_wait(o_full, 0);
             if (ok) {
                 tcgen05_fence_after();
                 const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-                if (qi < p.tokens && p.lse)
+                if (half == 0 && qi < p.tokens && p.lse)
                     p.lse[((int64_t)b * p.heads + head) * p.tokens + qi] = l > 0.0f ? (m_ref + __log2f(l)) * 0.6931471805599453f : 0.0f;
                 __half* orow = p.out + (int64_t)(row_base + qi) * p.ld_out + col;
                 const bool vec = (p.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
+                for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
                     uint32_t v[32];
                     tmem_ld_32x32b_x32(lane_addr + 256 + c0, v);
                     tmem_ld_wait();
@@ -303,7 +329,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             }
             if (!ok && lane == 0) atomicExch(&g_attn_error, 3);
         }
-    } else if (warp >= 2) {
+    } else if (warp >= 2 && warp < 6) {
         // no visible key for any row of this tile (len == 0): zero output, lse 0
         const int r = (warp & 3) * 32 + lane, qi = q0 + r;
         if (qi < p.tokens) {
@@ -323,7 +349,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
 template <int D>
 static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnFwdParams& p, cudaStream_t st) {
-    constexpr size_t smem = 1024 + (size_t)128 * D * 2 * 5 + 2 * 128 * AT_BKV * 2 + 256;
+    constexpr size_t smem = 1024 + (size_t)128 * D * 2 * 5 + 2 * 128 * AT_BKV * 2 + 176 + 2 * 128 * sizeof(float);
+    static_assert(smem <= 232448, "the forward attention tile set must fit the 227 KB a CTA can have");
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] { attr_err = cudaFuncSetAttribute(attn_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
@@ -332,7 +359,7 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
         return BRK_CUDA_ERROR;
     }
     dim3 grid((unsigned)((p.tokens + AT_BQ - 1) / AT_BQ), (unsigned)p.heads, (unsigned)p.batch);
-    attn_fwd_kernel<D><<<grid, AT_THREADS, smem, st>>>(tq, tk, tv, p);
+    attn_fwd_kernel<D><<<grid, AT_FWD_THREADS, smem, st>>>(tq, tk, tv, p);
     return launch_status("attn_fwd_kernel");
 }
 
@@ -404,10 +431,14 @@ __device__ __forceinline__ void store_tile_chunk(unsigned char* tile, int r, int
     }
 }
 
-__device__ __forceinline__ void owners_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// The backward kernels run two row-owner warps per scheduler (one warp alone cannot hide the latency of its own
+// tensor-memory loads and exponentials): warps 2..9, where warps w and w + 4 own the same 32 tensor-memory lanes (a warp
+// may only touch lanes 32 * (warp % 4) ...) and split the 64 columns of a sub-block between them.
+constexpr int AT_BWD_THREADS = 64 + 256;
+__device__ __forceinline__ void owners_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <int D>
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __launch_bounds__(AT_BWD_THREADS, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do64, AttnBwdParams p) {
     constexpr uint32_t KV_BYTES = 128 * D * 2;            // this block's K and V tiles
@@ -455,8 +486,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_c
             mbar_init(&qdo_full[i], 1);
             mbar_init(&qdo_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&s_empty[i], 128);
-            mbar_init(&p_full[i], 128);
+            mbar_init(&s_empty[i], 256);
+            mbar_init(&p_full[i], 256);
             mbar_init(&p_empty[i], 1);
         }
         mbar_init(acc_full, 1);
@@ -541,8 +572,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_c
                 if (!ok) atomicExch(&g_attn_error, 12);
             }
         } else {
-            // ---------------- row owners: one thread per key ----------------
+            // ---------------- row owners: two threads per key, 32 of the 64 query columns each ----------------
             const int quarter = warp & 3;
+            const int half = (warp - 2) >> 2;
             const int r = quarter * 32 + lane;
             const int kj = k0 + r;                               // this thread's key
             const bool k_ok = kj < len;
@@ -550,12 +582,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_c
             const float bias2 = slope2 * (float)kj;              // the ALiBi term is constant along a key's row
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
             const int64_t stat_base = ((int64_t)b * p.heads + head) * p.tokens;
+            const int c0 = half * 32;
             bool ok = true;
             for (int it = 0; it < niter; it++) {
                 const int sb = it & 1;
                 const int q0 = (sub0 + it) * AT_SUB;
-                {
-                    // the sub-block's 64 lse (in log2 units) and 64 delta values, one per thread
+                if (half == 0) {
+                    // the sub-block's 64 lse (in log2 units) and 64 delta values, one per thread of the first four warps
                     const int qi = q0 + (r & 63);
                     float v = 0.0f;
                     if (qi < p.tokens) v = r < 64 ? p.lse[stat_base + qi] * 1.4426950408889634f : p.delta[stat_base + qi];
@@ -568,28 +601,44 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_c
                 if (ok && it >= 2) ok = mbar_wait(&p_empty[sb], ((it - 2) >> 1) & 1);
                 if (!ok) continue;
                 tcgen05_fence_after();
-                const float* lse2 = stat + sb * 128;
-                const float* dlt = lse2 + 64;
-                unsigned char* pt = sPT + sb * PT_BYTES;
-                unsigned char* dst = sDST + sb * PT_BYTES;
-#pragma unroll 1
-                for (int c0 = 0; c0 < AT_SUB; c0 += 32) {
-                    uint32_t sv[32], dv[32];
-                    tmem_ld_32x32b_x32(lane_addr + sb * AT_SUB + c0, sv);
-                    tmem_ld_32x32b_x32(lane_addr + 128 + sb * AT_SUB + c0, dv);
-                    tmem_ld_wait();
-                    float pr[32], ds[32];
+                const float4* lse4 = reinterpret_cast<const float4*>(stat + sb * 128 + c0);
+                const float4* dlt4 = reinterpret_cast<const float4*>(stat + sb * 128 + 64 + c0);
+                uint32_t sv[32], dv[32];
+                tmem_ld_32x32b_x32(lane_addr + sb * AT_SUB + c0, sv);
+                tmem_ld_32x32b_x32(lane_addr + 128 + sb * AT_SUB + c0, dv);
+                tmem_ld_wait();
+                float pr[32], ds[32];
+                // a sub-block strictly below the diagonal, inside the sequence, needs no predicate at all
+                const bool plain = __all_sync(0xffffffffu, k_ok && kj <= q0) && q0 + AT_SUB <= p.tokens;
+                if (plain) {
 #pragma unroll
-                    for (int e = 0; e < 32; e++) {
-                        const int qi = q0 + c0 + e;
-                        const bool vis = k_ok && kj <= qi && qi < p.tokens;
-                        const float pe = vis ? fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, bias2) - lse2[c0 + e]) : 0.0f;
-                        pr[e] = pe;
-                        ds[e] = pe * (__uint_as_float(dv[e]) - dlt[c0 + e]);
+                    for (int g = 0; g < 8; g++) {
+                        const float4 l4 = lse4[g], d4 = dlt4[g];
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float pe = fast_exp2(fmaf(__uint_as_float(sv[g * 4 + e]), p.scale_log2, bias2 - ls[e]));
+                            pr[g * 4 + e] = pe;
+                            ds[g * 4 + e] = pe * (__uint_as_float(dv[g * 4 + e]) - dd[e]);
+                        }
                     }
-                    store_tile_chunk(pt, r, c0, pr);
-                    store_tile_chunk(dst, r, c0, ds);
+                } else {
+#pragma unroll
+                    for (int g = 0; g < 8; g++) {
+                        const float4 l4 = lse4[g], d4 = dlt4[g];
+                        const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, dd[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const int qi = q0 + c0 + g * 4 + e;
+                            const bool vis = k_ok && kj <= qi && qi < p.tokens;
+                            const float pe = vis ? fast_exp2(fmaf(__uint_as_float(sv[g * 4 + e]), p.scale_log2, bias2 - ls[e])) : 0.0f;
+                            pr[g * 4 + e] = pe;
+                            ds[g * 4 + e] = pe * (__uint_as_float(dv[g * 4 + e]) - dd[e]);
+                        }
+                    }
                 }
+                store_tile_chunk(sPT + sb * PT_BYTES, r, c0, pr);
+                store_tile_chunk(sDST + sb * PT_BYTES, r, c0, ds);
                 tcgen05_fence_before();
                 mbar_arrive(&s_empty[sb]);
                 fence_proxy_async();
@@ -601,10 +650,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_c
                 __half* dvrow = p.dv + (int64_t)(row_base + kj) * p.ld_g + col;
                 __half* dkrow = p.dk + (int64_t)(row_base + kj) * p.ld_g + col;
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
+                for (int d0 = half * (D / 2); d0 < (half + 1) * (D / 2); d0 += 32) {
                     uint32_t a[32], c[32];
-                    tmem_ld_32x32b_x32(lane_addr + 256 + c0, a);
-                    tmem_ld_32x32b_x32(lane_addr + 256 + D + c0, c);
+                    tmem_ld_32x32b_x32(lane_addr + 256 + d0, a);
+                    tmem_ld_32x32b_x32(lane_addr + 256 + D + d0, c);
                     tmem_ld_wait();
                     if (kj < p.tokens) {
 #pragma unroll
@@ -615,15 +664,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_c
                                 o1.v[e] = __uint_as_float(a[g * 8 + e]);
                                 o2.v[e] = __uint_as_float(c[g * 8 + e]) * p.scale;
                             }
-                            o1.store(dvrow + c0 + g * 8);
-                            o2.store(dkrow + c0 + g * 8);
+                            o1.store(dvrow + d0 + g * 8);
+                            o2.store(dkrow + d0 + g * 8);
                         }
                     }
                 }
             }
             if (!ok && lane == 0) atomicExch(&g_attn_error, 13);
         }
-    } else if (warp >= 2) {
+    } else if (warp >= 2 && warp < 6) {
         const int kj = k0 + (warp & 3) * 32 + lane;
         if (kj < p.tokens) {
             __half* dvrow = p.dv + (int64_t)(row_base + kj) * p.ld_g + col;
@@ -644,7 +693,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q64, const __grid_c
 }
 
 template <int D>
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __launch_bounds__(AT_BWD_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k64,
                    const __grid_constant__ CUtensorMap tmap_v64, const __grid_constant__ CUtensorMap tmap_do, AttnBwdParams p) {
     constexpr uint32_t Q_BYTES = 128 * D * 2;             // this block's Q and dO tiles
@@ -689,8 +738,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             mbar_init(&kv_full[i], 1);
             mbar_init(&kv_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&s_empty[i], 128);
-            mbar_init(&ds_full[i], 128);
+            mbar_init(&s_empty[i], 256);
+            mbar_init(&ds_full[i], 256);
             mbar_init(&ds_empty[i], 1);
         }
         mbar_init(acc_full, 1);
@@ -767,7 +816,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 if (!ok) atomicExch(&g_attn_error, 22);
             }
         } else {
+            // two threads per query row, 32 of the 64 key columns each
             const int quarter = warp & 3;
+            const int half = (warp - 2) >> 2;
             const int r = quarter * 32 + lane;
             const int qi = q0 + r;
             const bool q_ok = qi < p.tokens;
@@ -777,6 +828,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const float lse2 = q_ok ? p.lse[stat_base + qi] * 1.4426950408889634f : 0.0f;
             const float dlt = q_ok ? p.delta[stat_base + qi] : 0.0f;
             const int klimit = q_ok ? min(qi + 1, len) : 0;
+            const int c0 = half * 32;
             bool ok = true;
             for (int it = 0; it < niter && ok; it++) {
                 const int sb = it & 1;
@@ -785,22 +837,29 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 if (it >= 2) ok = mbar_wait(&ds_empty[sb], ((it - 2) >> 1) & 1);
                 if (!ok) break;
                 tcgen05_fence_after();
-                unsigned char* dst = sDS + sb * DS_BYTES;
-#pragma unroll 1
-                for (int c0 = 0; c0 < AT_SUB; c0 += 32) {
-                    uint32_t sv[32], dv[32];
-                    tmem_ld_32x32b_x32(lane_addr + sb * AT_SUB + c0, sv);
-                    tmem_ld_32x32b_x32(lane_addr + 128 + sb * AT_SUB + c0, dv);
-                    tmem_ld_wait();
-                    float ds[32];
+                uint32_t sv[32], dv[32];
+                tmem_ld_32x32b_x32(lane_addr + sb * AT_SUB + c0, sv);
+                tmem_ld_32x32b_x32(lane_addr + 128 + sb * AT_SUB + c0, dv);
+                tmem_ld_wait();
+                float ds[32];
+                const int kbase = it * AT_SUB + c0;
+                // ALiBi + log-sum-exp term of key kbase + e as one fused multiply-add on constants (no int -> float per element)
+                const float base2 = fmaf(slope2, (float)kbase, -lse2);
+                const bool plain = __all_sync(0xffffffffu, kbase + 32 <= klimit);      // every key of the chunk visible to every row
+                if (plain) {
 #pragma unroll
                     for (int e = 0; e < 32; e++) {
-                        const int kj = it * AT_SUB + c0 + e;
-                        const float pe = kj < klimit ? fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, slope2 * (float)kj) - lse2) : 0.0f;
+                        const float pe = fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, fmaf(slope2, (float)e, base2)));
                         ds[e] = pe * (__uint_as_float(dv[e]) - dlt);
                     }
-                    store_tile_chunk(dst, r, c0, ds);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; e++) {
+                        const float pe = kbase + e < klimit ? fast_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2, fmaf(slope2, (float)e, base2))) : 0.0f;
+                        ds[e] = pe * (__uint_as_float(dv[e]) - dlt);
+                    }
                 }
+                store_tile_chunk(sDS + sb * DS_BYTES, r, c0, ds);
                 tcgen05_fence_before();
                 mbar_arrive(&s_empty[sb]);
                 fence_proxy_async();
@@ -811,9 +870,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 tcgen05_fence_after();
                 __half* dqrow = p.dq + (int64_t)(row_base + qi) * p.ld_g + col;
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
+                for (int d0 = half * (D / 2); d0 < (half + 1) * (D / 2); d0 += 32) {
                     uint32_t a[32];
-                    tmem_ld_32x32b_x32(lane_addr + 256 + c0, a);
+                    tmem_ld_32x32b_x32(lane_addr + 256 + d0, a);
                     tmem_ld_wait();
                     if (q_ok) {
 #pragma unroll
@@ -821,14 +880,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                             Vec<__half> o;
 #pragma unroll
                             for (int e = 0; e < 8; e++) o.v[e] = __uint_as_float(a[g * 8 + e]) * p.scale;
-                            o.store(dqrow + c0 + g * 8);
+                            o.store(dqrow + d0 + g * 8);
                         }
                     }
                 }
             }
             if (!ok && lane == 0) atomicExch(&g_attn_error, 23);
         }
-    } else if (warp >= 2) {
+    } else if (warp >= 2 && warp < 6) {
         const int qi = q0 + (warp & 3) * 32 + lane;
         if (qi < p.tokens) {
             __half* dqrow = p.dq + (int64_t)(row_base + qi) * p.ld_g + col;
@@ -863,10 +922,10 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
         return BRK_CUDA_ERROR;
     }
     dim3 grid((unsigned)((p.tokens + AT_BQ - 1) / AT_BQ), (unsigned)p.heads, (unsigned)p.batch);
-    attn_bwd_dkv_kernel<D><<<grid, AT_THREADS, smem_dkv, st>>>(tq64, tk, tv, tdo64, p);
+    attn_bwd_dkv_kernel<D><<<grid, AT_BWD_THREADS, smem_dkv, st>>>(tq64, tk, tv, tdo64, p);
     int rc = launch_status("attn_bwd_dkv_kernel");
     if (rc) return rc;
-    attn_bwd_dq_kernel<D><<<grid, AT_THREADS, smem_dq, st>>>(tq, tk64, tv64, tdo, p);
+    attn_bwd_dq_kernel<D><<<grid, AT_BWD_THREADS, smem_dq, st>>>(tq, tk64, tv64, tdo, p);
     return launch_status("attn_bwd_dq_kernel");
 }
 
