@@ -374,13 +374,40 @@ void PipeLinks::open(size_t bytes_per_slot, int nslots) {
         BR_CUDA_CHECK(cudaMemcpyAsync(all.data(), table, (size_t)world * 64, cudaMemcpyDeviceToHost, st));
         BR_CUDA_CHECK(cudaStreamSynchronize(st));
         BR_CUDA_CHECK(cudaFree(table));
+        unsigned char mine_ok = 1;
         for (int d = 0; d < 2; d++) {
             const int nb = d == 0 ? rank - 1 : rank + 1;
             if (nb < 0 || nb >= world) continue;
             void* p = nullptr;
-            BR_CUDA_CHECK(cudaIpcOpenMemHandle(&p, all[nb], cudaIpcMemLazyEnablePeerAccess));
+            if (cudaIpcOpenMemHandle(&p, all[nb], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                cudaGetLastError();            // clear the error: the failure is reported below, by every rank alike
+                mine_ok = 0;
+                continue;
+            }
             e.peer[d] = static_cast<unsigned char*>(p);
             e.mapped[d] = true;
+        }
+        // all ranks or none: a rank that could not map a neighbour makes every rank give up together, so that a caller
+        // can fall back to another transport without the ranks disagreeing
+        unsigned char* flags = nullptr;
+        BR_CUDA_CHECK(cudaMalloc(&flags, (size_t)world));
+        BR_CUDA_CHECK(cudaMemcpyAsync(flags + rank, &mine_ok, 1, cudaMemcpyHostToDevice, st));
+        BR_NCCL_CHECK(ncclAllGather(flags + rank, flags, 1, ncclChar, CollectiveContext::nccl_comm, st));
+        std::vector<unsigned char> oks(world);
+        BR_CUDA_CHECK(cudaMemcpyAsync(oks.data(), flags, (size_t)world, cudaMemcpyDeviceToHost, st));
+        BR_CUDA_CHECK(cudaStreamSynchronize(st));
+        BR_CUDA_CHECK(cudaFree(flags));
+        bool all_ok = true;
+        for (unsigned char v : oks) all_ok = all_ok && v != 0;
+        if (!all_ok) {
+            for (int d = 0; d < 2; d++)
+                if (e.mapped[d]) cudaIpcCloseMemHandle(e.peer[d]);
+            // every rank has unmapped before anyone frees (same barrier as in close)
+            if (ncclAllGather(e.local + 4 * (size_t)rank, e.local, 4, ncclChar, CollectiveContext::nccl_comm, st) == ncclSuccess)
+                cudaStreamSynchronize(st);
+            cudaFree(e.local);
+            g_ends.clear();
+            br_panic("io.link.open: a rank could not map its neighbour's memory (CUDA IPC or peer access unavailable)");
         }
     }
     g_end = &g_ends[0];

@@ -67,6 +67,11 @@ class Trainer:
         self.loss_scale, self.lr = float(loss_scale), float(lr)
         self.first, self.last = rank == 0, rank == world - 1
         self.overlap = ((world > 1) if overlap is None else (bool(overlap) and world > 1)) and n_micro > 1
+        if self.overlap and not play_all_ranks and not self._links_available():
+            import sys
+            print(f"rank {rank}: one-sided links unavailable (CUDA IPC / peer access); using NCCL hand-offs and the plain schedule",
+                  file=sys.stderr)
+            self.overlap = False
         # stage boundaries in half-layer units (2 per layer); the plain schedule keeps whole layers
         unit = sum(schedule.LAYER_COST) * head_cost / sum(schedule.HEAD_COST)
         head = tuple(c * unit for c in schedule.HEAD_COST)
@@ -145,6 +150,19 @@ class Trainer:
         self.p_score = None          # built on first use
         self.step_no = 0
         self.losses = []
+
+    @staticmethod
+    def _links_available():
+        """Opens and closes a minimal set of link windows.  io.link.open fails on every rank or on none (the ranks
+        exchange their results), so all ranks reach the same answer."""
+        probe = host.Env(1)
+        try:
+            probe.execute("256 2 io.link.open io.link.close")
+            return True
+        except host.HostError:
+            return False
+        finally:
+            probe.close()
 
     def _feed(self, packed):
         e = self.env
