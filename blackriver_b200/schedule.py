@@ -23,8 +23,8 @@ from dataclasses import dataclass
 # per-family device times of the 7b1-shaped step: forward GEMMs + attention forward; input-gradient GEMMs +
 # attention backward + LayerNorm / GELU backward; weight-gradient GEMMs + column sums.  The head's forward part
 # (logits GEMM + log-softmax) is counted with its B task because it runs there.
-LAYER_COST = (0.90, 1.05, 0.80)
-HEAD_COST = (0.1, 7.3, 3.8)
+LAYER_COST = (0.816, 1.051, 0.882)
+HEAD_COST = (0.1, 6.7, 3.6)
 
 
 @dataclass(frozen=True)
@@ -216,7 +216,7 @@ def choose_partition(n_layers, world, n_micro, n_slots=None, layer_cost=LAYER_CO
 # attention) has the same shape as a layer's output, so a stage boundary may fall there too, which lets 30 layers be
 # spread over 7 ranks in pieces of 4.3 layers instead of 5 and 4.  Costs (F, B, W) in the unit of LAYER_COST, from the
 # same measured profile: A carries a third of the layer's GEMM FLOPs plus the attention kernels, M two thirds.
-UNIT_COST = {"A": (0.36, 0.545, 0.286), "M": (0.473, 0.537, 0.546)}
+UNIT_COST = {"A": (0.323, 0.491, 0.303), "M": (0.493, 0.560, 0.579)}
 
 
 def unit_kind(u):
