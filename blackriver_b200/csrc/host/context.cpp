@@ -28,6 +28,7 @@ size_t ComputingContext::workspace_size = 0;
 int ComputingContext::grad_accumulate = 0;
 float ComputingContext::loss_scale = 1.0f;
 int ComputingContext::verbose = 1;
+int ComputingContext::nccl_on_comm_stream = 0;
 bool ComputingContext::booted = false;
 static bool g_owns_compute_stream = false;
 
@@ -36,6 +37,7 @@ static void boot_common(int device, size_t workspace_bytes) {
     ComputingContext::grad_accumulate = 0;
     ComputingContext::loss_scale = 1.0f;
     ComputingContext::verbose = 1;
+    ComputingContext::nccl_on_comm_stream = 0;
     ComputingContext::cuda_device = device;
     BR_CUDA_CHECK(cudaStreamCreateWithFlags(&ComputingContext::comm_stream, cudaStreamNonBlocking));
     for (int d = 0; d < 2; d++) BR_CUDA_CHECK(cudaStreamCreateWithFlags(&ComputingContext::link_stream[d], cudaStreamNonBlocking));

@@ -36,6 +36,7 @@ struct ComputingContext {
     static float loss_scale;           // multiplies the loss gradient (fp16 gradients); Adam divides it out
 
     static int verbose;                // 1: op_loss_backward prints its "#### items loss" line like the reference
+    static int nccl_on_comm_stream;    // 1: the io.nccl.* words queue on comm_stream (between op.stream.fork and op.stream.join)
 
     static bool booted;
     static void boot(int device, size_t workspace_bytes = (size_t)256 << 20);

@@ -16,6 +16,8 @@ namespace br {
 namespace {
 
 inline cudaStream_t stream() { return ComputingContext::cuda_stream; }
+// NCCL transfers go to the transfer stream while a script has forked it (op.stream.fork ... op.stream.join)
+inline cudaStream_t nccl_stream() { return ComputingContext::nccl_on_comm_stream ? ComputingContext::comm_stream : ComputingContext::cuda_stream; }
 inline void* sptr() { return (void*)ComputingContext::cuda_stream; }
 
 template <DataType DT> constexpr int brk_dtype() { return DT == DataType::F16 ? BRK_F16 : BRK_F32; }
@@ -797,8 +799,8 @@ ComputingReturn CUDATensor<DT>::io_nccl_sendrecv(tensor_t self, tensor_t recv, i
     if (!CollectiveContext::has_comm) return OP_ATTR_ERROR;
     if (!recv || !recv->is_cuda()) return OP_OUTPUT_ERROR;
     BR_NCCL_CHECK(ncclGroupStart());
-    BR_NCCL_CHECK(ncclSend(mem_, self->bytes(), ncclChar, peer, CollectiveContext::nccl_comm, stream()));
-    BR_NCCL_CHECK(ncclRecv(recv->data(), recv->bytes(), ncclChar, peer, CollectiveContext::nccl_comm, stream()));
+    BR_NCCL_CHECK(ncclSend(mem_, self->bytes(), ncclChar, peer, CollectiveContext::nccl_comm, nccl_stream()));
+    BR_NCCL_CHECK(ncclRecv(recv->data(), recv->bytes(), ncclChar, peer, CollectiveContext::nccl_comm, nccl_stream()));
     BR_NCCL_CHECK(ncclGroupEnd());
     return OP_OK;
 }

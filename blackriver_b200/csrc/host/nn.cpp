@@ -296,6 +296,22 @@ BR_WORD(KernelStatus, {
     stack.push_number((double)code);
 })
 
+// ( -- )  the transfer stream continues from the compute stream's present position, and the io.nccl.* words that follow
+// queue on it: the transfer then runs beside whatever the compute stream is given next
+BR_WORD(StreamFork, {
+    (void)stack;
+    BR_CUDA_CHECK(cudaEventRecord(ComputingContext::compute_done, ComputingContext::cuda_stream));
+    BR_CUDA_CHECK(cudaStreamWaitEvent(ComputingContext::comm_stream, ComputingContext::compute_done, 0));
+    ComputingContext::nccl_on_comm_stream = 1;
+})
+// ( -- )  the compute stream waits for what was queued on the transfer stream since the fork
+BR_WORD(StreamJoin, {
+    (void)stack;
+    BR_CUDA_CHECK(cudaEventRecord(ComputingContext::comm_done, ComputingContext::comm_stream));
+    BR_CUDA_CHECK(cudaStreamWaitEvent(ComputingContext::cuda_stream, ComputingContext::comm_done, 0));
+    ComputingContext::nccl_on_comm_stream = 0;
+})
+
 // ---- one-sided stage hand-offs (PipeLinks) ----
 // ( bytes_per_slot slots -- )  collective over all ranks
 BR_WORD(LinkOpen, {
@@ -424,6 +440,8 @@ void load_nn_words(Enviroment& env) {
     env.insert_native_word("op.loss_backward_async", LossBackwardAsync::creator);
     env.insert_native_word("op.loss_backward_w", LossBackwardW::creator);
     env.insert_native_word("op.kernel_status", KernelStatus::creator);
+    env.insert_native_word("op.stream.fork", StreamFork::creator);
+    env.insert_native_word("op.stream.join", StreamJoin::creator);
     env.insert_native_word("io.link.open", LinkOpen::creator);
     env.insert_native_word("io.link.close", LinkClose::creator);
     env.insert_native_word("io.link.emulate", LinkEmulate::creator);

@@ -198,11 +198,17 @@ class Trainer:
             e.change(0)
             self.losses = [float(v) for v in e.read("loss_all")]
 
-    def apply_optimizer(self):
+    def apply_optimizer(self, tied_peer=None):
+        """Adam on every parameter of the stage.  With tied_peer (a rank) the tied table's gradient is first exchanged
+        with that rank, on the transfer stream, beside the Adam launches of the layers."""
         self.step_no += 1
         # gradients were summed over micro-batches and carry the loss scale: Adam divides both out
         gs = 1.0 / (self.loss_scale * self.n_micro)
-        self.env.execute(f"0 op.accumulate {self.lr} {self.step_no} {gs} optimizer_step")
+        args = f"{self.lr} {self.step_no} {gs}"
+        if tied_peer is None:
+            self.env.execute(f"0 op.accumulate {args} optimizer_step")
+        else:
+            self.env.execute(f"0 op.accumulate {tied_peer} sync_tied_start {args} optimizer_layers sync_tied_finish {args} optimizer_main")
         return float(np.mean(self.losses)) if self.losses else None
 
     def step(self, microbatches):
@@ -211,27 +217,10 @@ class Trainer:
         for i in range(len(self.tasks)):
             self.run_task(i)
         self.check_and_read_losses()
+        peer = None
         if self.world > 1 and (self.first or self.last):
             peer = self.world - 1 if self.first else 0
-            self.env.execute(f"{peer} sync_tied_grads")
-        return self.apply_optimizer()
-
-    def score(self, microbatches):
-        """Forward only (prefill scoring): runs every micro-batch through the stages and, on the rank that holds the
-        head, returns a list of (token_nll [batch, tokens] float32, mean NLL) per micro-batch -- token_nll[b, t] is the
-        NLL of ids[b, t+1] at position t, 0 where that pair is not counted.  Other ranks return an empty list."""
-        e = self.env
-        if self.p_score is None:
-            self.p_score = [e.build(f"slot_{k} stage_score") for k in range(self.n_slots)]
-        out = []
-        for k, mb in enumerate(microbatches):
-            self._feed(pack_inputs(mb))
-            e.run(self.p_score[k % self.n_slots])
-            if self.last:
-                e.change(0)
-                nll = e.read("token_nll").copy()        # synchronises the compute stream
-                out.append((nll, host.last_loss()))
-        return out
+        return self.apply_optimizer(peer)
 
     def save(self, prefix):
         """Checkpoint of this stage: fp32 master weights in the reference's per-tensor raw files plus the Adam moments

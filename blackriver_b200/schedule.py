@@ -217,6 +217,9 @@ def choose_partition(n_layers, world, n_micro, n_slots=None, layer_cost=LAYER_CO
 # spread over 7 ranks in pieces of 4.3 layers instead of 5 and 4.  Costs (F, B, W) in the unit of LAYER_COST, from the
 # same measured profile: A carries a third of the layer's GEMM FLOPs plus the attention kernels, M two thirds.
 UNIT_COST = {"A": (0.323, 0.491, 0.303), "M": (0.493, 0.560, 0.579)}
+# What the two holders of the tied 250880 x 4096 table carry besides their layers, per micro-batch: the embedding gather +
+# LayerNorm and their backward (first rank only), and a sixteenth of the table's Adam update and gradient exchange
+TABLE_COST = (0.04, 0.08, 0.45)
 
 
 def unit_kind(u):
@@ -235,6 +238,8 @@ def stage_costs_units(bounds, unit_cost=None, head_cost=HEAD_COST):
             f, b, w = f + c[0], b + c[1], w + c[2]
         if r == world - 1:
             f, b, w = f + head_cost[0], b + head_cost[1], w + head_cost[2]
+        if world > 1 and (r == 0 or r == world - 1):
+            f, b, w = f + TABLE_COST[0] * (r == 0), b + TABLE_COST[1] * (r == 0), w + TABLE_COST[2]
         out.append((max(f, 1e-3), max(b, 1e-3), max(w, 1e-3)))
     return out
 

@@ -647,15 +647,24 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         w('    0 # "loss_" !!')
         w("%end")
 
-    # ( lr step grad_scale -- )
-    w("%def optimizer_step")
-    w('    0 #  "gs_" ! "step_" ! "lr_" !')
+    # ( lr step grad_scale -- )  Adam on every parameter of the stage; optimizer_layers / optimizer_main are its two parts
     adam = '"lr_" @ 0.9 0.999 1e-08 "step_" @ "gs_" @ op.adam'
+    w("%def optimizer_layers")
+    w('    0 #  "gs_" ! "step_" ! "lr_" !')
+    for i in range(1, n_layers + 1):
+        w(f'    0 # "lr_" @ "step_" @ "gs_" @  {i} # "gs_" ! "step_" ! "lr_" !  {g("_flat", "_flat_g", "_flat.master", "_flat.m", "_flat.v")} {adam}  "gs_" !! "step_" !! "lr_" !!')
+    w('    0 #  "gs_" !! "step_" !! "lr_" !!')
+    w("%end")
+    w("%def optimizer_main")
+    w('    0 #  "gs_" ! "step_" ! "lr_" !')
     for name, _ in main_params:
         w(f'    {g(name, name + "_g", name + ".master", name + ".m", name + ".v")} {adam}')
-    for i in range(1, n_layers + 1):
-        w(f'    0 # "lr_" @ "step_" @ "gs_" @  {i} # "gs_" ! "step_" ! "lr_" !  {g("_flat", "_flat_g", "_flat.master", "_flat.m", "_flat.v")} {adam}')
-    w('    0 #  "gs_" !! "step_" !! "lr_" !!')
+    w('    "gs_" !! "step_" !! "lr_" !!')
+    w("%end")
+    w("%def optimizer_step")
+    w('    0 #  "all_gs_" ! "all_step_" ! "all_lr_" !')
+    w('    "all_lr_" @ "all_step_" @ "all_gs_" @ optimizer_main  0 # "all_lr_" @ "all_step_" @ "all_gs_" @ optimizer_layers')
+    w('    0 #  "all_gs_" !! "all_step_" !! "all_lr_" !!')
     w("%end")
 
     if overlap:
@@ -762,12 +771,20 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
         w('    0 # "ckpt_" !!')
         w("%end")
 
-    # ( peer -- )  both holders of the tied embedding / LM-head table sum their gradients
-    w("%def sync_tied_grads")
+    # ( peer -- )  both holders of the tied embedding / LM-head table sum their gradients.  sync_tied_start queues the
+    # exchange on the transfer stream, so that it runs beside what the compute stream does next (the layers' Adam);
+    # sync_tied_finish makes the compute stream wait for it and adds what arrived.
+    w("%def sync_tied_start")
     w('    0 # "peer_" !')
-    w('    "word_embeddings.weight_g" @ "tied_recv" @ "peer_" @ io.nccl.sendrecv')
-    w('    "word_embeddings.weight_g" @ "tied_recv" @ "word_embeddings.weight_g" @ op.add')
+    w('    op.stream.fork  "word_embeddings.weight_g" @ "tied_recv" @ "peer_" @ io.nccl.sendrecv')
     w('    "peer_" !!')
+    w("%end")
+    w("%def sync_tied_finish")
+    w('    0 # op.stream.join')
+    w('    "word_embeddings.weight_g" @ "tied_recv" @ "word_embeddings.weight_g" @ op.add')
+    w("%end")
+    w("%def sync_tied_grads")
+    w("    sync_tied_start sync_tied_finish")
     w("%end")
 
     return "\n".join(L) + "\n"

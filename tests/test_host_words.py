@@ -144,3 +144,23 @@ def test_reference_scripts_run_on_this_machine(env):
     assert env.tensor_info("query.weight")["shape"] == (64, 64)
     assert env.tensor_info("dense_h_to_4h.weight_g")["shape"] == (256, 64)
     assert env.tensor_info("_xinput_")["shape"] == (8192, 64)
+
+
+def test_new_words_without_a_device():
+    """The extension words exist in the words machine and fail cleanly (an error, not a crash) where they need the
+    device context; op.kernel_status answers 0 when nothing has been booted."""
+    from blackriver_b200 import host
+    env = host.Env(1)
+    try:
+        env.execute("op.kernel_status")
+        assert env.pop_number() == 0
+        for text in ("1024 2 io.link.open", "0 0 io.link.wait", "1 io.link.fence", '0 0 4 4 2 "half" io.link.window'):
+            with pytest.raises(host.HostError):
+                env.execute(text)
+            env.clear_stack()
+        # the split operators refuse host tensors like every math operator does (no CPU path)
+        env.execute('4 4 2 "cpu" "float" op.create "a" !  4 4 2 "cpu" "float" op.create "b" !  4 4 2 "cpu" "float" op.create "c" !')
+        with pytest.raises(host.HostError):
+            env.execute('"a" @ "b" @ "c" @ op.linear_backward_x')
+    finally:
+        env.close()
