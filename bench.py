@@ -713,12 +713,97 @@ def cpu_baseline_finetune():
                       "extrapolated to 30 layers + head per token, no optimizer"}
 
 
+def time_gemm_shapes(torch, ops, brk, dev):
+    """Every GEMM shape of one 7b1 layer and of the LM head for one micro-batch of 2048 tokens, in isolation: CUDA events
+    around single launches, L2 flushed before each, median of 5; both epilogues of the CTA-pair kernel."""
+    g = torch.Generator(device=dev).manual_seed(0)
+    N, H = 2048, 4096
+    shapes = {  # name: (m, n, k, trans_a, trans_b, accumulate)
+        "fwd_qkv": (N, 3 * H, H, 0, 1, 0), "fwd_dense": (N, H, H, 0, 1, 0), "fwd_h4h": (N, 4 * H, H, 0, 1, 0), "fwd_4hh": (N, H, 4 * H, 0, 1, 0),
+        "dx_qkv": (N, H, 3 * H, 0, 0, 0), "dx_h4h": (N, H, 4 * H, 0, 0, 0), "dx_4hh": (N, 4 * H, H, 0, 0, 0),
+        "dw_qkv": (3 * H, H, N, 1, 0, 1), "dw_dense": (H, H, N, 1, 0, 1), "dw_h4h": (4 * H, H, N, 1, 0, 1), "dw_4hh": (H, 4 * H, N, 1, 0, 1),
+        "head_fwd": (N, VOCAB, H, 0, 1, 0), "head_dx": (N, H, VOCAB, 0, 0, 0), "head_dw": (VOCAB, H, N, 1, 0, 1),
+    }
+    res = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for name, (m, n, k, ta, tb, acc) in shapes.items():
+        a = torch.randn((k, m) if ta else (m, k), generator=g, device=dev).half()
+        b = torch.randn((n, k) if tb else (k, n), generator=g, device=dev).half()
+        c = torch.zeros(m, n, device=dev).half()
+        for epi, tag in ((0, "tma"), (1, "registers")):
+            brk.lib().brk_gemm_f16_set_epilogue(epi)
+            ts = []
+            for _ in range(6):
+                flush.zero_()
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+                ops.gemm_f16(a, b, c, m, n, k, ta, tb, a.shape[1], b.shape[1], n, accumulate=bool(acc))
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            t = sorted(ts[1:])[2]
+            res[f"{name}/{tag}"] = {"us": round(t * 1e3, 1), "tflops": round(2 * m * n * k / t / 1e9, 1)}
+        del a, b, c
+    brk.lib().brk_gemm_f16_set_epilogue(0)
+    assert brk.lib().brk_gemm_f16_status() == 0
+    return res
+
+
+def time_attention_shapes(torch, ops, brk, dev):
+    """Fused attention forward and backward (delta + dK/dV + dQ kernels) at several shapes, head dimension 128: CUDA events
+    around 10 launches queued back to back.  FLOPs: causal half of 4 B h T^2 d forward, 2.5 x that backward."""
+    res = {}
+    d = 128
+    for B, T, heads in ((2, 1024, 32), (1, 2048, 32), (4, 1024, 32), (8, 256, 32), (16, 128, 32), (2, 1024, 8)):
+        H = heads * d
+        qkv = torch.randn(B * T, 3 * H, device=dev).half()
+        out = torch.empty(B * T, H, device=dev).half()
+        lse = torch.empty(B, heads, T, device=dev)
+        dout = torch.randn(B * T, H, device=dev).half()
+        grads = torch.empty(B * T, 3 * H, device=dev).half()
+        ws = torch.empty(brk.lib().brk_flash_attn_bwd_workspace_bytes(B, T, heads), dtype=torch.uint8, device=dev)
+        base, gb = qkv.data_ptr(), grads.data_ptr()
+
+        def fwd():
+            brk.call("brk_flash_attn_fwd", base, base + 2 * H, base + 4 * H, 3 * H, out.data_ptr(), H, lse.data_ptr(), 0, 0, B, T, heads, d,
+                     ops.stream())
+
+        def bwd():
+            brk.call("brk_flash_attn_bwd", base, base + 2 * H, base + 4 * H, 3 * H, out.data_ptr(), dout.data_ptr(), H, lse.data_ptr(),
+                     gb, gb + 2 * H, gb + 4 * H, 3 * H, 0, 0, B, T, heads, d, ws.data_ptr(), ws.numel(), ops.stream())
+        o = {"work_items": B * heads * ((T + 127) // 128)}
+        flops = 4 * B * heads * T * T * d / 2
+        for name, fn, mult in (("fwd", fwd, 1.0), ("bwd", bwd, 2.5)):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 100
+            o[name + "_us"] = round(us, 1)
+            o[name + "_tflops"] = round(mult * flops / us / 1e6, 1)
+        res[f"batch{B}_tokens{T}_heads{heads}"] = o
+    assert brk.lib().brk_flash_attn_status() == 0
+    return res
+
+
 def run_case(args):
-    """A few launches of one kernel family on a small, larger-than-L2 case (for ncu captures)."""
+    """A few launches of one kernel family on a small, larger-than-L2 case (for ncu captures), or a timing table."""
     import torch
     from blackriver_b200 import ops
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
+    if args.case in ("gemm_shapes", "attn_shapes"):
+        from blackriver_b200 import brk
+        table = time_gemm_shapes(torch, ops, brk, dev) if args.case == "gemm_shapes" else time_attention_shapes(torch, ops, brk, dev)
+        emit_line({"case": args.case, "table": table})
+        return
     g = torch.Generator(device=dev).manual_seed(SEED)
     rows = args.rows
     reps = 3
@@ -924,7 +1009,7 @@ def main():
     ap.add_argument("--no-overlap", action="store_true",
                     help="multi-GPU: the plain schedule (all forwards, all backwards, NCCL hand-offs) instead of the overlapped one")
     ap.add_argument("--skip-ops", action="store_true", help="do not run the operator microbench before the fine-tune step")
-    ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "gemm_dw", "attn"],
+    ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "gemm_dw", "attn", "gemm_shapes", "attn_shapes"],
                     help="profiling aid: run a few launches of one kernel family on a small case and exit")
     ap.add_argument("--rows", type=int, default=1024, help="rows of the --case run")
     args = ap.parse_args()

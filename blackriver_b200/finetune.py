@@ -222,6 +222,23 @@ class Trainer:
             peer = self.world - 1 if self.first else 0
         return self.apply_optimizer(peer)
 
+    def score(self, microbatches):
+        """Forward only (prefill scoring): runs every micro-batch through the stages and, on the rank that holds the
+        head, returns a list of (token_nll [batch, tokens] float32, mean NLL) per micro-batch -- token_nll[b, t] is the
+        NLL of ids[b, t+1] at position t, 0 where that pair is not counted.  Other ranks return an empty list."""
+        e = self.env
+        if self.p_score is None:
+            self.p_score = [e.build(f"slot_{k} stage_score") for k in range(self.n_slots)]
+        out = []
+        for k, mb in enumerate(microbatches):
+            self._feed(pack_inputs(mb))
+            e.run(self.p_score[k % self.n_slots])
+            if self.last:
+                e.change(0)
+                nll = e.read("token_nll").copy()        # synchronises the compute stream
+                out.append((nll, host.last_loss()))
+        return out
+
     def save(self, prefix):
         """Checkpoint of this stage: fp32 master weights in the reference's per-tensor raw files plus the Adam moments
         (the words save_model writes them); the step count goes to <prefix>step.<rank>.txt."""
