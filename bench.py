@@ -428,12 +428,13 @@ def run_finetune(args):
         box = [host.collective_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         host.collective_boot(rank, world, box[0])
+        host.collective_split(args.replicas)
     else:
         host.collective_boot_local(0, 1)
 
     tr = finetune.Trainer(cfg["hidden"], cfg["heads"], cfg["vocab"], cfg["n_layers"], cfg["batch"], cfg["tokens"], cfg["n_micro"],
                           rank=rank, world=world, seed=cfg["seed"], logits_rows=cfg["batch"] * cfg["tokens"],
-                          overlap=not args.no_overlap)
+                          overlap=not args.no_overlap, replicas=args.replicas if world > 1 else 1)
     mbs = finetune.make_microbatches(cfg["n_micro"], cfg["batch"], cfg["tokens"], cfg["vocab"], cfg["min_len"], cfg["seed"])
     tokens_per_step = cfg["n_micro"] * cfg["batch"] * cfg["tokens"]
     valid_per_step = int(sum(int(m[2].sum()) for m in mbs))
@@ -492,10 +493,10 @@ def run_finetune(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total, ms_e2e = float(t[0]), float(t[1])
         box = [loss, trace]
-        dist.broadcast_object_list(box, src=world - 1)
+        dist.broadcast_object_list(box, src=tr.world - 1)        # the head's rank (of the first replica)
         loss, trace = box
 
-    if world == 1:
+    if tr.world == 1:
         schedule_name = "forward + backward per micro-batch"
     elif tr.overlap:
         schedule_name = ("static forward / input-gradient / weight-gradient task lists per rank (greedy, simulated efficiency %.2f), "
@@ -513,7 +514,7 @@ def run_finetune(args):
         peak_tf, peak_src = load_tensor_peak()
         # rank 0's GEMM work in whole-layer equivalents (a stage may end between a layer's attention and MLP halves)
         flops = cfg["n_micro"] * finetune.gemm_flops_per_microbatch(cfg["hidden"], cfg["vocab"], tr.gemm_layers, cfg["batch"] * cfg["tokens"],
-                                                                  with_head=(world == 1))
+                                                                  with_head=(tr.world == 1)) // tr.replicas
         gemm_ms = prof.get("gemm_f16", {}).get("ms", 0.0)
         achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
         fam = {k: {"ms": round(v["ms"], 3), "calls": v["calls"]} for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"])}
@@ -525,7 +526,7 @@ def run_finetune(args):
             "data": "synthetic",
             "config": {"workload": workload_text, "layers": cfg["n_layers"], "micro_batches": cfg["n_micro"],
                        "tokens_per_step": tokens_per_step, "valid_tokens_per_step": valid_per_step,
-                       "parallelism": "pp%d" % world, "stage_layers": tr.counts, "schedule": schedule_name, "slots": tr.n_slots,
+                       "parallelism": ("pp%d" % world) if tr.replicas == 1 else ("dp%d x pp%d, gradients all-reduced over replicas" % (tr.replicas, tr.world)), "stage_layers": tr.counts, "schedule": schedule_name, "slots": tr.n_slots,
                        "l2": "inputs larger than L2: per step every kernel streams >= 14 GB of weights and activations between re-uses"},
             "clocks": clocks, "gpu_launches": launches * args.steps,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -539,6 +540,7 @@ def run_finetune(args):
                                          "(profiles/gemm_f16_pair_2048x16384x4096.md)",
                          "flops_per_step": flops, "ms_per_step": round(gemm_ms, 3)},
             "step_profile_ms": fam,
+            "in_step_hbm_kernels": in_step_hbm(prof, cfg) if world == 1 else None,
             "kernels": None if ops_line is None else ops_line.get("kernels"),
             "ops_microbench": None if ops_line is None else {"value": ops_line["value"], "unit": "tokens/s",
                                                              "roofline": ops_line["roofline"]},
@@ -653,6 +655,29 @@ def run_prefill(args):
     if world > 1:
         host.collective_shutdown()
         dist.destroy_process_group()
+
+
+def in_step_hbm(prof, cfg):
+    """The HBM-bound kernels as the step launches them (2048 rows per launch, inputs mostly still in L2 from the kernel
+    before): interval between the event records around each launch (about 3 us of event overhead included), algorithmic
+    bytes per launch and the rate against the measured HBM copy peak."""
+    n, H, es = cfg["batch"] * cfg["tokens"], cfg["hidden"], 2
+    peak, _ = load_peaks()
+    per_call = {
+        "layernorm_fwd": 2 * n * H * es + 2 * H * es + 4 * n,
+        "layernorm_bwd": 3 * n * H * es + 4 * n + 4 * H * es,
+        "gelu_bwd": 3 * n * 4 * H * es,
+        "add": 3 * n * H * es,
+        # four bias gradients per layer: dy of 4h->h, h->4h, dense and QKV, read once each
+        "colsum": (1 + 4 + 1 + 3) * n * H * es / 4,
+    }
+    out = {}
+    for k, b in per_call.items():
+        if k in prof and prof[k]["calls"]:
+            us = prof[k]["ms"] / prof[k]["calls"] * 1e3
+            gbs = b / (us * 1e-6) / 1e9
+            out[k] = {"us_per_launch": round(us, 2), "algorithmic_bytes": int(b), "gbs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / peak, 3)}
+    return out
 
 
 FT_CPU_LAYER_TOKENS = 32
@@ -1006,6 +1031,8 @@ def main():
                          "micro-batch of 4 x 512 on one GPU; prefill: forward-only scoring of 8 x 2048 tokens")
     ap.add_argument("--layers", type=int, default=0, help="fine-tune workload with fewer layers (development aid)")
     ap.add_argument("--micro", type=int, default=0, help="fine-tune workload with fewer micro-batches (development aid)")
+    ap.add_argument("--replicas", type=int, default=1,
+                    help="fine-tune workload: data-parallel replicas of a (gpus / replicas)-stage pipeline; the default is one pipeline over all GPUs")
     ap.add_argument("--no-overlap", action="store_true",
                     help="multi-GPU: the plain schedule (all forwards, all backwards, NCCL hand-offs) instead of the overlapped one")
     ap.add_argument("--skip-ops", action="store_true", help="do not run the operator microbench before the fine-tune step")

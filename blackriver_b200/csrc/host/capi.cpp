@@ -54,6 +54,7 @@ int brh_collective_boot(int rank, int world, const char id_bytes[128]) {
         CollectiveContext::boot(rank, world, id);
     });
 }
+int brh_collective_split(int replicas) { return guarded([&] { CollectiveContext::split_replicas(replicas); }); }
 int brh_collective_shutdown(void) { return guarded([] { CollectiveContext::shutdown(); }); }
 
 int brh_memory_boot(size_t total_bytes, int pinned) { return guarded([&] { MemoryContext::boot(total_bytes, pinned != 0); }); }

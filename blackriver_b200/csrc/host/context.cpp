@@ -161,6 +161,10 @@ int CollectiveContext::nccl_rank = 0;
 ncclComm_t CollectiveContext::nccl_comm = nullptr;
 ncclUniqueId CollectiveContext::nccl_id;
 bool CollectiveContext::has_comm = false;
+int CollectiveContext::dp_world = 1;
+int CollectiveContext::dp_rank = 0;
+ncclComm_t CollectiveContext::dp_comm = nullptr;
+ncclComm_t CollectiveContext::job_comm = nullptr;
 static std::chrono::steady_clock::time_point g_boot_time = std::chrono::steady_clock::now();
 
 void CollectiveContext::boot_local(int rank, int world) {
@@ -236,12 +240,37 @@ void CollectiveContext::boot_from_file(int rank, int world, const std::string& p
     if (rank == 0) ::unlink(path.c_str());
 }
 
+void CollectiveContext::split_replicas(int replicas) {
+    br_assert(job_comm == nullptr, "the job is split into replicas already");
+    br_assert(replicas >= 1 && mpi_world % replicas == 0, "the number of ranks is not a multiple of the replicas");
+    if (replicas == 1) return;
+    br_assert(has_comm, "split_replicas needs the job's communicator");
+    const int stages = mpi_world / replicas;
+    const int replica = mpi_rank / stages, stage = mpi_rank % stages;
+    ncclComm_t pipe = nullptr, dp = nullptr;
+    // every rank takes part in both splits; a pipeline of one stage needs no communicator of its own
+    BR_NCCL_CHECK(ncclCommSplit(nccl_comm, stages > 1 ? replica : NCCL_SPLIT_NOCOLOR, stage, &pipe, nullptr));
+    BR_NCCL_CHECK(ncclCommSplit(nccl_comm, stage, replica, &dp, nullptr));
+    job_comm = nccl_comm;
+    nccl_comm = pipe;
+    has_comm = pipe != nullptr;
+    nccl_rank = stage;
+    nccl_world = stages;
+    dp_comm = dp;
+    dp_rank = replica;
+    dp_world = replicas;
+}
+
 void CollectiveContext::shutdown() {
-    if (has_comm) {
-        ncclCommDestroy(nccl_comm);
-        has_comm = false;
-        nccl_comm = nullptr;
-    }
+    if (dp_comm) ncclCommDestroy(dp_comm);
+    dp_comm = nullptr;
+    dp_world = 1;
+    dp_rank = 0;
+    if (has_comm && nccl_comm) ncclCommDestroy(nccl_comm);
+    if (job_comm) ncclCommDestroy(job_comm);
+    job_comm = nullptr;
+    has_comm = false;
+    nccl_comm = nullptr;
 }
 
 int CollectiveContext::now() {

@@ -64,6 +64,14 @@ struct CollectiveContext {
     static ncclComm_t nccl_comm;
     static ncclUniqueId nccl_id;
     static bool has_comm;
+    // Data-parallel replicas (split_replicas): the job's ranks form `dp_world` replicas of a pipeline of nccl_world
+    // stages; rank r of the job is stage r % stages of replica r / stages.  nccl_comm / nccl_rank / nccl_world then
+    // describe this rank's pipeline (what every io.nccl.* hand-off and the stage links use), dp_comm joins the ranks
+    // that hold the same stage in every replica, and mpi_rank / mpi_world keep the job-wide numbers.
+    static int dp_world;
+    static int dp_rank;
+    static ncclComm_t dp_comm;
+    static ncclComm_t job_comm;     // the communicator the two above were split from (nullptr when never split)
 
     // Rank layout only (no communicator): what host-only tools and tests need.
     static void boot_local(int rank, int world);
@@ -72,6 +80,8 @@ struct CollectiveContext {
     // Rendezvous through a file: rank 0 writes the id, the others poll for it (bounded wait).
     static void boot_from_file(int rank, int world, const std::string& path, int timeout_s = 120);
     static ncclUniqueId make_unique_id();
+    // Splits the booted job into `replicas` equal pipelines (see dp_world above).  Collective over all ranks.
+    static void split_replicas(int replicas);
     static void shutdown();
     static int now();  // whole seconds since boot, as the reference's echo prints
 };

@@ -806,6 +806,16 @@ ComputingReturn CUDATensor<DT>::io_nccl_sendrecv(tensor_t self, tensor_t recv, i
 }
 
 template <DataType DT>
+ComputingReturn CUDATensor<DT>::io_nccl_allreduce(tensor_t self) {
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (CollectiveContext::dp_world <= 1) return OP_OK;
+    if (!CollectiveContext::dp_comm) return OP_ATTR_ERROR;
+    BR_NCCL_CHECK(ncclAllReduce(mem_, mem_, self->items(), DT == DataType::F16 ? ncclHalf : ncclFloat, ncclSum,
+                                CollectiveContext::dp_comm, nccl_stream()));
+    return OP_OK;
+}
+
+template <DataType DT>
 ComputingReturn CUDATensor<DT>::op_randn(tensor_t self, float mean, float std, uint64_t seed) {
     if (DT == DataType::Int) return OP_TODO_ERROR;
     return ret(brk_init_normal(mem_, (int64_t)self->items(), mean, std, seed, brk_dtype<DT>(), sptr()));

@@ -255,6 +255,16 @@ BR_WORD(IoNcclSendRecv, {
     auto t = pop_tensors<2>(stack);
     t[0]->io_nccl_sendrecv(t[0], t[1], peer);
 })
+// ( tensor -- )  the tensor becomes its sum over the data-parallel replicas
+BR_WORD(IoNcclAllReduce, {
+    tensor_t t = stack.pop_tensor();
+    t->io_nccl_allreduce(t);
+})
+// ( -- replica replicas )  this rank's place among the data-parallel replicas
+BR_WORD(IoReplica, {
+    stack.push_number(CollectiveContext::dp_rank);
+    stack.push_number(CollectiveContext::dp_world);
+})
 // ( flag -- )  1: weight / bias gradients are added to, 0: overwritten (the reference behaviour)
 BR_WORD(Accumulate, { ComputingContext::grad_accumulate = stack.pop_number() != 0.0 ? 1 : 0; })
 // ( value -- )  factor applied to the loss gradient
@@ -421,6 +431,8 @@ void load_nn_words(Enviroment& env) {
     env.insert_native_word("io.nccl.recv", IoNcclRecv::creator);
 
     env.insert_native_word("io.nccl.sendrecv", IoNcclSendRecv::creator);
+    env.insert_native_word("io.nccl.allreduce", IoNcclAllReduce::creator);
+    env.insert_native_word("io.replica", IoReplica::creator);
     env.insert_native_word("op.flash_attn", FlashAttn::creator);
     env.insert_native_word("op.flash_attn_backward", FlashAttnBackward::creator);
     env.insert_native_word("op.linear_residual", LinearResidual::creator);

@@ -100,6 +100,8 @@ struct TransformerComputing {
     // simultaneous exchange with one peer: send self, receive into `recv` (one NCCL group, so two ranks
     // that both call it towards each other cannot block one another)
     virtual ComputingReturn io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) { return OP_TODO_ERROR; }
+    // self <- sum of self over the data-parallel replicas (in place; nothing to do with one replica)
+    virtual ComputingReturn io_nccl_allreduce(tensor_t self) { return OP_TODO_ERROR; }
     // self[i] ~ N(mean, std), seeded
     virtual ComputingReturn op_randn(tensor_t self, float mean, float std, uint64_t seed) { return OP_TODO_ERROR; }
     // forward-only scoring: out[b, t] (fp32) = NLL of ids[b, t+1] given position t of self [batch, tokens, hidden], 0 where the

@@ -236,6 +236,12 @@ ComputingReturn TensorType::io_nccl_sendrecv(tensor_t self, tensor_t recv, int p
     op_check(r, "nccl_sendrecv");
 }
 
+ComputingReturn TensorType::io_nccl_allreduce(tensor_t self) {
+    SELF_CHECK();
+    auto r = impl_->io_nccl_allreduce(self);
+    op_check(r, "nccl_allreduce");
+}
+
 ComputingReturn TensorType::op_linear_backward_x(tensor_t self, tensor_t weight, tensor_t x_g) {
     SELF_CHECK();
     auto r = impl_->op_linear_backward_x(self, weight, x_g);

@@ -154,6 +154,7 @@ struct TensorType : public TransformerComputing {
     ComputingReturn op_randn(tensor_t self, float mean, float std, uint64_t seed) override;
     LossReturn op_token_nll(tensor_t self, tensor_t ids, tensor_t mask, tensor_t lm_head, tensor_t all_logits, tensor_t out) override;
     ComputingReturn io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) override;
+    ComputingReturn io_nccl_allreduce(tensor_t self) override;
     ComputingReturn op_linear_backward_x(tensor_t self, tensor_t weight, tensor_t x_g) override;
     ComputingReturn op_linear_backward_w(tensor_t self, tensor_t x, tensor_t weight_g, tensor_t bias_g) override;
     ComputingReturn op_loss_backward_async(tensor_t self, tensor_t ids, tensor_t mask, tensor_t lm_head, tensor_t all_logits, tensor_t x_g, tensor_t lm_head_g, tensor_t loss_out, int defer_weight) override;

@@ -41,6 +41,20 @@ def make_microbatches(n_micro, batch, tokens, vocab, min_len, seed, pad_id=3):
     return out
 
 
+def replica_layout(rank, world, replicas, n_micro):
+    """(replica, stage, stages, micro-batches per replica) of job rank `rank`: stage-major inside a replica, so the
+    stages of one pipeline are neighbouring ranks (and neighbouring GPUs)."""
+    if replicas < 1 or world % replicas or n_micro % replicas:
+        raise ValueError(f"{world} ranks / {n_micro} micro-batches do not divide into {replicas} replicas")
+    stages = world // replicas
+    return rank // stages, rank % stages, stages, n_micro // replicas
+
+
+def replica_share(microbatches, replica, replicas):
+    """The micro-batches of a step that replica `replica` works on: every replicas-th, starting at its own number."""
+    return list(microbatches[replica::replicas])
+
+
 def pack_inputs(mb):
     """ids [B,T], mask [B,T], lens [B] of one micro-batch as the int32 buffer the stage scripts call "inp"."""
     ids, mask, lens = mb
@@ -61,7 +75,16 @@ class Trainer:
 
     def __init__(self, hidden, heads, vocab, n_layers, batch, tokens, n_micro, rank=0, world=1, dtype="half", seed=0,
                  loss_scale=1024.0, lr=1e-4, logits_rows=None, init_std=0.02, verbose=False, head_cost=LM_HEAD_COST_IN_LAYERS,
-                 overlap=None, n_slots=None, activation_budget=56 << 30, play_all_ranks=False, split_layers=True):
+                 overlap=None, n_slots=None, activation_budget=56 << 30, play_all_ranks=False, split_layers=True, replicas=1):
+        # data-parallel replicas: the job's ranks form `replicas` pipelines of world / replicas stages; each replica
+        # takes every replicas-th micro-batch of a step and the gradients are summed over the replicas before Adam.
+        # From here on rank / world / n_micro describe this rank's pipeline and its share of the micro-batches.
+        self.job_rank, self.job_world, self.replicas = rank, world, int(replicas)
+        self.total_micro = n_micro
+        if self.replicas > 1:
+            self.replica, rank, world, n_micro = replica_layout(rank, world, self.replicas, n_micro)
+        else:
+            self.replica = 0
         self.rank, self.world, self.n_micro = rank, world, n_micro
         self.batch, self.tokens = batch, tokens
         self.loss_scale, self.lr = float(loss_scale), float(lr)
@@ -170,6 +193,8 @@ class Trainer:
         e.write_async("inp", packed)
 
     def begin_step(self, microbatches):
+        if self.replicas > 1 and len(microbatches) == self.total_micro:
+            microbatches = replica_share(microbatches, self.replica, self.replicas)
         assert len(microbatches) == self.n_micro
         self._packed = [pack_inputs(mb) for mb in microbatches]
         self.env.run(self.p_begin)
@@ -196,14 +221,15 @@ class Trainer:
         self.losses = []
         if self.last:
             e.change(0)
-            self.losses = [float(v) for v in e.read("loss_all")]
+            # with replicas "loss_all" holds sums over the replicas by now (sync_replicas)
+            self.losses = [float(v) / self.replicas for v in e.read("loss_all")]
 
     def apply_optimizer(self, tied_peer=None):
         """Adam on every parameter of the stage.  With tied_peer (a rank) the tied table's gradient is first exchanged
         with that rank, on the transfer stream, beside the Adam launches of the layers."""
         self.step_no += 1
         # gradients were summed over micro-batches and carry the loss scale: Adam divides both out
-        gs = 1.0 / (self.loss_scale * self.n_micro)
+        gs = 1.0 / (self.loss_scale * self.total_micro)
         args = f"{self.lr} {self.step_no} {gs}"
         if tied_peer is None:
             self.env.execute(f"0 op.accumulate {args} optimizer_step")
@@ -216,6 +242,8 @@ class Trainer:
         self.begin_step(microbatches)
         for i in range(len(self.tasks)):
             self.run_task(i)
+        if self.replicas > 1:
+            self.env.execute("sync_replicas")
         self.check_and_read_losses()
         peer = None
         if self.world > 1 and (self.first or self.last):
@@ -242,6 +270,9 @@ class Trainer:
     def save(self, prefix):
         """Checkpoint of this stage: fp32 master weights in the reference's per-tensor raw files plus the Adam moments
         (the words save_model writes them); the step count goes to <prefix>step.<rank>.txt."""
+        if self.replica != 0:          # the replicas hold the same weights and moments: the first one writes them
+            self.sync()
+            return
         self.env.execute(f'op.sync "{prefix}" save_model op.sync')
         with open(f"{prefix}step.{self.rank}.txt", "w") as f:
             f.write(str(self.step_no))

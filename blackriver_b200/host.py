@@ -17,6 +17,7 @@ SIGNATURES = {
     "brh_collective_boot_local": (i32, [i32, i32]),
     "brh_collective_unique_id": (i32, [C.c_char * 128]),
     "brh_collective_boot": (i32, [i32, i32, C.c_char * 128]),
+    "brh_collective_split": (i32, [i32]),
     "brh_collective_shutdown": (i32, []),
     "brh_memory_boot": (i32, [sz, i32]),
     "brh_memory_shutdown": (i32, []),
@@ -111,6 +112,11 @@ def collective_unique_id():
 def collective_boot(rank, world, id_bytes):
     buf = (C.c_char * 128)(*id_bytes)
     _check(lib().brh_collective_boot(rank, world, buf))
+
+
+def collective_split(replicas):
+    """Splits the booted job into data-parallel replicas of a pipeline (every rank calls it with the same value)."""
+    _check(lib().brh_collective_split(int(replicas)))
 
 
 def collective_shutdown():

@@ -787,4 +787,18 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w("    sync_tied_start sync_tied_finish")
     w("%end")
 
+    # ( -- )  data-parallel replicas: every gradient of the stage (and, on the head's stage, the micro-batch losses)
+    # becomes its sum over the replicas, on the transfer stream; the compute stream waits for the last one.
+    w("%def sync_replicas")
+    w("    0 # op.stream.fork")
+    for name, _ in main_params:
+        w(f'    "{name}_g" @ io.nccl.allreduce')
+    for i in range(1, n_layers + 1):
+        w(f'    {i} # "_flat_g" @ io.nccl.allreduce')
+    w("    0 #")
+    if last_stage:
+        w('    "loss_all" @ io.nccl.allreduce')
+    w("    op.stream.join")
+    w("%end")
+
     return "\n".join(L) + "\n"

@@ -32,6 +32,12 @@ BRH_API void* brh_context_stream(void);
 BRH_API int brh_collective_boot_local(int rank, int world);
 BRH_API int brh_collective_unique_id(char out[128]);
 BRH_API int brh_collective_boot(int rank, int world, const char id[128]);
+/* Data-parallel replicas of the pipeline (absent from the reference, whose one communicator is point-to-point only,
+ * blackriver/context.cpp:56-80): splits the booted job of `world` ranks into `replicas` pipelines of world / replicas
+ * stages each (rank r = stage r % stages of replica r / stages).  Afterwards the io.nccl.* hand-offs and the stage
+ * links address pipeline stages, and io.nccl.allreduce sums a tensor over the replicas.  Collective: every rank calls
+ * it with the same value; 1 is a no-op. */
+BRH_API int brh_collective_split(int replicas);
 BRH_API int brh_collective_shutdown(void);
 
 /* Host arena: blackriver/context.cpp:96-121 (MemoryContext). */

@@ -3,6 +3,7 @@
 backend nccl (GPU): trains a small model for two steps as a WORLD_SIZE-stage pipeline (overlapped schedule with
 one-sided hand-offs, or -- BR_TEST_OVERLAP=0 -- the plain order over NCCL send / receive), then rank 0 trains the same
 model on one GPU and compares losses and updated weights.
+With BR_TEST_REPLICAS = R the ranks form R data-parallel replicas of a WORLD_SIZE / R-stage pipeline.
 backend gloo (CPU): checks the host-side logic only -- stage partition, identical micro-batches and identical task
 lists on every rank, stage scripts of both kinds compile in the words machine."""
 import json
@@ -50,7 +51,7 @@ def main():
                                           next_rank=None if last else rank + 1, layer_offset=sum(counts[:rank]), overlap=overlap))
             text = ('slot_1 stage_f slot_1 "loss@1" stage_b slot_1 stage_w' if overlap else
                     'slot_1 stage_forward slot_1 stage_backward slot_1 "loss@1" stage_backward_async')
-            prog = env.build(text)     # links every word of the stage
+            prog = env.build(text + " sync_replicas")     # links every word of the stage
             env.free_program(prog)
             env.close()
         dist.barrier()
@@ -66,22 +67,30 @@ def main():
     box = [host.collective_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(box, src=0)
     host.collective_boot(rank, world, box[0])
+    replicas = int(os.environ.get("BR_TEST_REPLICAS", "1"))
+    host.collective_split(replicas)
+    stages = world // replicas
     tr = finetune.Trainer(CFG["hidden"], CFG["heads"], CFG["vocab"], CFG["n_layers"], CFG["batch"], CFG["tokens"], CFG["n_micro"],
                           rank=rank, world=world, seed=9, lr=1e-3, init_std=0.05, head_cost=head_cost,
-                          overlap=os.environ.get("BR_TEST_OVERLAP", "1") != "0")
+                          overlap=os.environ.get("BR_TEST_OVERLAP", "1") != "0", replicas=replicas)
     losses = [tr.step(mbs) for _ in range(2)]
     tr.sync()
     w_first = None
-    if tr.counts[rank] >= 1:
+    if tr.counts[tr.rank] >= 1:
         tr.env.change(1)
         w_first = tr.env.read("_flat.master").copy()          # first layer of this stage
     tr.env.change(0)
-    table = tr.env.read("word_embeddings.weight.master").copy() if (rank == 0 or rank == world - 1) else None
+    table = tr.env.read("word_embeddings.weight.master").copy() if (tr.first or tr.last) else None
     box = [losses]
-    dist.broadcast_object_list(box, src=world - 1)
+    dist.broadcast_object_list(box, src=stages - 1)           # the head's rank of the first replica
     pipe_losses = box[0]
     tables = [None] * world
     dist.all_gather_object(tables, None if table is None else float(np.abs(table).sum()))
+    # the replicas of a stage must hold the same weights bit for bit: they applied the same summed gradient
+    digests = [None] * world
+    dist.all_gather_object(digests, None if w_first is None else float(np.abs(w_first.astype(np.float64)).sum()))
+    replicas_agree = all(digests[r] == digests[r % stages] for r in range(world))
+    tables = tables[:stages]
     tr.close()
     if rank == 0:
         single = finetune.Trainer(CFG["hidden"], CFG["heads"], CFG["vocab"], CFG["n_layers"], CFG["batch"], CFG["tokens"],
@@ -98,7 +107,7 @@ def main():
             "w_err": float(np.abs(w_first - ref_w).max() / np.abs(ref_w).max()),
             "table_err": float(np.abs(table - ref_table).max() / np.abs(ref_table).max()),
             "tables_agree": abs(tables[0] - tables[-1]) <= 1e-6 * abs(tables[0]),
-            "counts": tr.counts, "overlap": tr.overlap, "n_slots": tr.n_slots,
+            "counts": tr.counts, "overlap": tr.overlap, "n_slots": tr.n_slots, "replicas": replicas, "replicas_agree": replicas_agree,
         }
         json.dump(res, open(out_path, "w"))
     dist.barrier()

@@ -11,10 +11,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "pipeline_worker.py")
 
 
-def launch(world, backend, out_path, port, head_cost=0.5, overlap=True):
+def launch(world, backend, out_path, port, head_cost=0.5, overlap=True, replicas=1):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), WORKER, backend, out_path]
-    env = dict(os.environ, OMP_NUM_THREADS="2", BR_TEST_HEAD_COST=str(head_cost), BR_TEST_OVERLAP="1" if overlap else "0")
+    env = dict(os.environ, OMP_NUM_THREADS="2", BR_TEST_HEAD_COST=str(head_cost), BR_TEST_OVERLAP="1" if overlap else "0",
+               BR_TEST_REPLICAS=str(replicas))
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return json.load(open(out_path))
@@ -66,4 +67,40 @@ def test_pipeline_with_head_only_last_stage(tmp_path, overlap):
         pytest.skip("needs three GPUs")
     res = launch(3, "nccl", str(tmp_path / "out.json"), 29535 + int(overlap), head_cost=2.5, overlap=overlap)
     assert res["counts"] == [2, 2, 0] and res["overlap"] == overlap
+    check_against_single(res)
+
+
+def test_replica_layout_and_shares():
+    from blackriver_b200.finetune import replica_layout, replica_share
+    # 8 ranks as 2 replicas of 4 stages: stages of one pipeline are neighbouring ranks
+    assert [replica_layout(r, 8, 2, 16)[:2] for r in range(8)] == [(0, 0), (0, 1), (0, 2), (0, 3), (1, 0), (1, 1), (1, 2), (1, 3)]
+    assert replica_layout(5, 8, 2, 16) == (1, 1, 4, 8) and replica_layout(3, 4, 4, 16) == (3, 0, 1, 4)
+    with pytest.raises(ValueError):
+        replica_layout(0, 6, 4, 16)
+    with pytest.raises(ValueError):
+        replica_layout(0, 4, 2, 5)
+    mbs = list(range(16))
+    shares = [replica_share(mbs, r, 4) for r in range(4)]
+    assert sorted(sum(shares, [])) == mbs and all(len(x) == 4 for x in shares) and shares[1] == [1, 5, 9, 13]
+
+
+@pytest.mark.gpu
+def test_two_replicas_match_single_gpu(tmp_path):
+    """Two data-parallel replicas of the whole model (2 GPUs): each takes half of the micro-batches, gradients are summed
+    by io.nccl.allreduce; losses and weights must match the single-GPU step over all micro-batches."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    res = launch(2, "nccl", str(tmp_path / "out.json"), 29541, replicas=2)
+    assert res["replicas"] == 2 and res["replicas_agree"] and res["counts"] == [4.0]
+    check_against_single(res)
+
+
+@pytest.mark.gpu
+def test_two_replicas_of_a_two_stage_pipeline(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    res = launch(4, "nccl", str(tmp_path / "out.json"), 29543, replicas=2)
+    assert res["replicas"] == 2 and res["replicas_agree"] and len(res["counts"]) == 2 and res["overlap"]
     check_against_single(res)
