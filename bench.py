@@ -775,6 +775,70 @@ def time_gemm_shapes(torch, ops, brk, dev):
     return res
 
 
+def time_hbm_shapes(torch, ops, brk, dev):
+    """The HBM-bound kernels at the row count the fine-tune step launches them with (one micro-batch = 2048 rows) and at the
+    microbench's 8192: CUDA events around single launches, median of 5, once with L2 flushed before each launch ("cold")
+    and once with the inputs written just before ("warm": what the step sees after the producing GEMM).  LayerNorm in both
+    kernel modes (0 = shared-memory ring, persistent CTAs; 1 = a warp per row from registers)."""
+    g = torch.Generator(device=dev).manual_seed(0)
+    H = 4096
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    peak, _ = load_peaks()
+    res = {}
+
+    def timed(fn, warm_src):
+        out = {}
+        for cond in ("cold", "warm"):
+            ts = []
+            for _ in range(6):
+                if cond == "cold":
+                    flush.zero_()
+                else:
+                    for t in warm_src:
+                        t.add_(0)            # rewrites the inputs: they sit in L2 as after their producer
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            out[cond] = sorted(ts[1:])[2]
+        return out
+
+    def put(name, t, nbytes):
+        res[name] = {c: {"us": round(v * 1e3, 2), "gbs": round(nbytes / v / 1e6, 1), "frac_of_measured_hbm": round(nbytes / v / 1e6 / peak, 3)}
+                     for c, v in t.items()}
+
+    for rows in (2048, 8192):
+        x = torch.randn(rows, H, generator=g, device=dev).half()
+        dy = torch.randn(rows, H, generator=g, device=dev).half()
+        y = torch.empty_like(x)
+        dx = torch.empty_like(x)
+        gamma = torch.ones(H, device=dev).half()
+        beta = torch.zeros(H, device=dev).half()
+        dg, db = torch.empty_like(gamma), torch.empty_like(beta)
+        ws = torch.empty(max(16, brk.lib().brk_layernorm_bwd_workspace_bytes(rows, H)), dtype=torch.uint8, device=dev)
+        _, _, var = ops.layernorm(x, gamma, beta, out=y)
+        for mode in (0, 1):
+            brk.lib().brk_layernorm_set_mode(mode)
+            put(f"layernorm_fwd/rows{rows}/mode{mode}", timed(lambda: ops.layernorm(x, gamma, beta, out=y), [x]), 2 * rows * H * 2)
+            put(f"layernorm_bwd/rows{rows}/mode{mode}",
+                timed(lambda: ops.layernorm_backward(dy, gamma, beta, var, y, dgamma=dg, dbeta=db, dx=dx, workspace=ws), [dy, y]),
+                3 * rows * H * 2)
+        brk.lib().brk_layernorm_set_mode(0)
+        put(f"add/rows{rows}", timed(lambda: ops.add(x, dy, out=dx), [x, dy]), 3 * rows * H * 2)
+        for cols in (H, 4 * H):
+            m = torch.randn(rows, cols, generator=g, device=dev).half()
+            out = torch.zeros(cols, device=dev).half()
+            cws = torch.empty(brk.lib().brk_colsum_workspace_bytes(rows, cols), dtype=torch.uint8, device=dev)
+            put(f"colsum/rows{rows}/cols{cols}",
+                timed(lambda: brk.call("brk_colsum_ws", m.data_ptr(), out.data_ptr(), rows, cols, 1, 1, cws.data_ptr(), cws.numel(), ops.stream()), [m]),
+                rows * cols * 2)
+            del m
+    return res
+
+
 def time_attention_shapes(torch, ops, brk, dev):
     """Fused attention forward and backward (delta + dK/dV + dQ kernels) at several shapes, head dimension 128: CUDA events
     around 10 launches queued back to back.  FLOPs: causal half of 4 B h T^2 d forward, 2.5 x that backward."""
@@ -824,9 +888,9 @@ def run_case(args):
     from blackriver_b200 import ops
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
-    if args.case in ("gemm_shapes", "attn_shapes"):
+    if args.case in ("gemm_shapes", "attn_shapes", "hbm_shapes"):
         from blackriver_b200 import brk
-        table = time_gemm_shapes(torch, ops, brk, dev) if args.case == "gemm_shapes" else time_attention_shapes(torch, ops, brk, dev)
+        table = {"gemm_shapes": time_gemm_shapes, "attn_shapes": time_attention_shapes, "hbm_shapes": time_hbm_shapes}[args.case](torch, ops, brk, dev)
         emit_line({"case": args.case, "table": table})
         return
     g = torch.Generator(device=dev).manual_seed(SEED)
@@ -1036,7 +1100,7 @@ def main():
     ap.add_argument("--no-overlap", action="store_true",
                     help="multi-GPU: the plain schedule (all forwards, all backwards, NCCL hand-offs) instead of the overlapped one")
     ap.add_argument("--skip-ops", action="store_true", help="do not run the operator microbench before the fine-tune step")
-    ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "gemm_dw", "attn", "gemm_shapes", "attn_shapes"],
+    ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "gemm_dw", "attn", "gemm_shapes", "attn_shapes", "hbm_shapes"],
                     help="profiling aid: run a few launches of one kernel family on a small case and exit")
     ap.add_argument("--rows", type=int, default=1024, help="rows of the --case run")
     args = ap.parse_args()

@@ -32,6 +32,7 @@ SIGNATURES = {
     "brk_layernorm_fwd": (i32, [p, p, p, p, p, p, i64, i64, f32, i32, p]),
     "brk_layernorm_bwd_workspace_bytes": (sz, [i64, i64]),
     "brk_layernorm_bwd": (i32, [p, p, p, p, p, p, p, p, i64, i64, f32, p, sz, i32, i32, p]),
+    "brk_layernorm_bwd_residual": (i32, [p, p, p, p, p, p, p, p, p, i64, i64, f32, p, sz, i32, i32, p]),
     "brk_layernorm_set_mode": (i32, [i32]),
     "brk_layernorm_bwd_static_capacity": (sz, []),
     "brk_layernorm_bwd_static": (i32, [p, p, p, p, p, p, p, p, i64, i64, f32, i32, i32, p]),

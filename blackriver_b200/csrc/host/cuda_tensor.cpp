@@ -521,6 +521,25 @@ ComputingReturn CUDATensor<DT>::op_layernorm_backward(tensor_t self, tensor_t sc
                                  ComputingContext::workspace_size, ComputingContext::grad_accumulate, brk_dtype<DT>(), sptr()));
 }
 
+template <DataType DT>
+ComputingReturn CUDATensor<DT>::op_layernorm_backward_residual(tensor_t self, tensor_t scale, tensor_t bias, tensor_t var, tensor_t y,
+                                                               tensor_t dscale, tensor_t dbias, tensor_t din, tensor_t residual,
+                                                               float eps) {
+    ProfScope prof("layernorm_bwd");
+    if (DT == DataType::Int) return OP_TODO_ERROR;
+    if (!dev_ok<DT>({scale, bias, y, residual}) || !dev_ok<DataType::Float>({var})) return OP_INPUT_ERROR;
+    if (!dev_ok<DT>({dscale, dbias, din}) || din->items() != self->items()) return OP_OUTPUT_ERROR;
+    int64_t hidden = (int64_t)self->shape().vec().back();
+    int64_t rows = (int64_t)self->items() / hidden;
+    if ((int64_t)var->items() < rows || y->items() != self->items() || residual->items() != self->items()) return OP_INPUT_ERROR;
+    size_t need = brk_layernorm_bwd_workspace_bytes(rows, hidden);
+    if (need > ComputingContext::workspace_size) return OP_ATTR_ERROR;
+    return ret(brk_layernorm_bwd_residual(mem_, scale->data(), bias->data(), (const float*)var->data(), y->data(), residual->data(),
+                                          dscale->data(), dbias->data(), din->data(), rows, hidden, eps,
+                                          ComputingContext::cuda_workspace, ComputingContext::workspace_size,
+                                          ComputingContext::grad_accumulate, brk_dtype<DT>(), sptr()));
+}
+
 // b_g = sum_n dy ; W_g = dy^T x ; x_g = dy W, all overwritten, W_g before x_g because x_g may be x
 // (blackriver/cuda_tensor.cpp:731-812; bloomz-7b/train.words:198)
 template <DataType DT>

@@ -161,6 +161,13 @@ BR_WORD(LayernormBackward, {
     t[0]->op_layernorm_backward(t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7], eps);
 })
 
+// ( dy scale bias var y dscale dbias din residual eps -- )  din = residual + the LayerNorm's input gradient
+BR_WORD(LayernormBackwardResidual, {
+    float eps = (float)stack.pop_number();
+    auto t = pop_tensors<9>(stack);
+    t[0]->op_layernorm_backward_residual(t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7], t[8], eps);
+})
+
 // ( dy x w b x_g w_g b_g -- )
 BR_WORD(LinearBackward, {
     auto t = pop_tensors<7>(stack);
@@ -481,6 +488,7 @@ void load_nn_words(Enviroment& env) {
     env.insert_native_word("op.last_logits", LastLogits::creator);
     env.insert_native_word("op.loss_backward", LossBackward::creator);
     env.insert_native_word("op.layernorm_backward", LayernormBackward::creator);
+    env.insert_native_word("op.layernorm_backward_residual", LayernormBackwardResidual::creator);
     env.insert_native_word("op.linear_backward", LinearBackward::creator);
     env.insert_native_word("op.gelu_backward", GeluBackward::creator);
     env.insert_native_word("op.attn_backward", AttnBackward::creator);

@@ -100,6 +100,12 @@ struct TransformerComputing {
     // simultaneous exchange with one peer: send self, receive into `recv` (one NCCL group, so two ranks
     // that both call it towards each other cannot block one another)
     virtual ComputingReturn io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) { return OP_TODO_ERROR; }
+    // op_layernorm_backward with the residual branch folded in: din = residual + (input gradient of the LayerNorm);
+    // residual may be din
+    virtual ComputingReturn op_layernorm_backward_residual(tensor_t self, tensor_t scale, tensor_t bias, tensor_t var, tensor_t y,
+                                                           tensor_t dscale, tensor_t dbias, tensor_t din, tensor_t residual, float eps) {
+        return OP_TODO_ERROR;
+    }
     // self <- sum of self over the data-parallel replicas (in place; nothing to do with one replica)
     virtual ComputingReturn io_nccl_allreduce(tensor_t self) { return OP_TODO_ERROR; }
     // self[i] ~ N(mean, std), seeded

@@ -157,6 +157,11 @@ ComputingReturn TensorType::op_layernorm_backward(tensor_t self, tensor_t scale,
     auto r = impl_->op_layernorm_backward(self, scale, bias, var, y, dscale, dbias, din, eps);
     op_check(r, "layernorm_backward");
 }
+ComputingReturn TensorType::op_layernorm_backward_residual(tensor_t self, tensor_t scale, tensor_t bias, tensor_t var, tensor_t y, tensor_t dscale, tensor_t dbias, tensor_t din, tensor_t residual, float eps) {
+    SELF_CHECK();
+    auto r = impl_->op_layernorm_backward_residual(self, scale, bias, var, y, dscale, dbias, din, residual, eps);
+    op_check(r, "layernorm_backward_residual");
+}
 ComputingReturn TensorType::op_linear_backward(tensor_t self, tensor_t x, tensor_t weight, tensor_t bias, tensor_t x_g, tensor_t weight_g, tensor_t bias_g) {
     SELF_CHECK();
     auto r = impl_->op_linear_backward(self, x, weight, bias, x_g, weight_g, bias_g);

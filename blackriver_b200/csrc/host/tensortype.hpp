@@ -155,6 +155,7 @@ struct TensorType : public TransformerComputing {
     LossReturn op_token_nll(tensor_t self, tensor_t ids, tensor_t mask, tensor_t lm_head, tensor_t all_logits, tensor_t out) override;
     ComputingReturn io_nccl_sendrecv(tensor_t self, tensor_t recv, int peer) override;
     ComputingReturn io_nccl_allreduce(tensor_t self) override;
+    ComputingReturn op_layernorm_backward_residual(tensor_t self, tensor_t scale, tensor_t bias, tensor_t var, tensor_t y, tensor_t dscale, tensor_t dbias, tensor_t din, tensor_t residual, float eps) override;
     ComputingReturn op_linear_backward_x(tensor_t self, tensor_t weight, tensor_t x_g) override;
     ComputingReturn op_linear_backward_w(tensor_t self, tensor_t x, tensor_t weight_g, tensor_t bias_g) override;
     ComputingReturn op_loss_backward_async(tensor_t self, tensor_t ids, tensor_t mask, tensor_t lm_head, tensor_t all_logits, tensor_t x_g, tensor_t lm_head_g, tensor_t loss_out, int defer_weight) override;

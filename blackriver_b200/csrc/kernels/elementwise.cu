@@ -183,6 +183,7 @@ colsum_partial_kernel(const T* x, float* partial, int64_t rows, int64_t cols, in
     float acc[VN];
 #pragma unroll
     for (int e = 0; e < VN; e++) acc[e] = 0.0f;
+    pdl_wait();          // launched as a programmatic dependent: x is complete from here on
     if (c0 < cols) {
         int64_t r = r0 + rl;
         for (; r + 3 * RL < r1; r += 4 * RL) {
@@ -211,17 +212,35 @@ colsum_partial_kernel(const T* x, float* partial, int64_t rows, int64_t cols, in
         const int64_t c = (int64_t)blockIdx.x * 64 + threadIdx.x;
         if (c < cols) partial[(int64_t)blockIdx.y * cols + c] = t;
     }
+    pdl_launch_dependents();
 }
 
+// Stage 2: 32 columns x 8 slice lanes per CTA; every lane adds each 8th slice (independent loads in flight) and the
+// lanes are combined in a fixed order.
+constexpr int COLSUM_FINAL_LANES = 8;
+
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(32 * COLSUM_FINAL_LANES)
 colsum_final_kernel(const float* partial, T* out, int slices, int64_t cols, int accumulate) {
-    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= cols) return;
+    __shared__ float red[COLSUM_FINAL_LANES][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t j = (int64_t)blockIdx.x * 32 + tx;
+    pdl_wait();          // the partial sums are complete from here on
     float t = 0.0f;
-    for (int s = 0; s < slices; s++) t += partial[(int64_t)s * cols + j];
-    if (accumulate) t += to_f32(out[j]);
-    out[j] = from_f32<T>(t);
+    if (j < cols) {
+#pragma unroll 4
+        for (int s = ty; s < slices; s += COLSUM_FINAL_LANES) t += partial[(int64_t)s * cols + j];
+    }
+    red[ty][tx] = t;
+    __syncthreads();
+    if (ty == 0 && j < cols) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < COLSUM_FINAL_LANES; k++) sum += red[k][tx];
+        if (accumulate) sum += to_f32(out[j]);
+        out[j] = from_f32<T>(sum);
+    }
+    pdl_launch_dependents();
 }
 
 template <typename T>
@@ -233,11 +252,27 @@ static int colsum_ws_dispatch(const void* x, void* out, int64_t rows, int64_t co
     if (slices > 64) slices = 64;
     if ((size_t)(slices * cols) * sizeof(float) > ws_bytes) return BRK_ATTR_ERROR;
     int64_t rps = (rows + slices - 1) / slices;
-    dim3 grid((unsigned)col_ctas, (unsigned)slices);
-    colsum_partial_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (float*)ws, rows, cols, rps);
-    int rc = launch_status("colsum_partial_kernel");
-    if (rc) return rc;
-    colsum_final_kernel<T><<<(unsigned)((cols + 255) / 256), 256, 0, st>>>((const float*)ws, (T*)out, (int)slices, cols, accumulate);
+    // both stages are programmatic dependents of the kernel before them in the stream: their launches overlap its tail
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)col_ctas, (unsigned)slices);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, colsum_partial_kernel<T>, (const T*)x, (float*)ws, rows, cols, rps);
+    if (le != cudaSuccess) {
+        set_cuda_error(le, "colsum_partial_kernel");
+        return BRK_CUDA_ERROR;
+    }
+    le = launch_pdl(colsum_final_kernel<T>, (int)((cols + 31) / 32), 32 * COLSUM_FINAL_LANES, 0, st, (const float*)ws, (T*)out,
+                    (int)slices, cols, accumulate);
+    if (le != cudaSuccess) {
+        set_cuda_error(le, "colsum_final_kernel");
+        return BRK_CUDA_ERROR;
+    }
     return launch_status("colsum_final_kernel");
 }
 

@@ -185,7 +185,7 @@ __device__ __forceinline__ float guard_gamma(float g, float eps) { return g >= 0
 template <typename T, int NVT>
 __global__ void __launch_bounds__(512)
 ln_bwd_kernel(const T* dy, const T* gamma, const T* beta,
-              const float* var, const T* y, T* dx,
+              const float* var, const T* y, const T* res, T* dx,
               float* partial, int64_t rows, int hidden, float eps) {
     constexpr int VN = Vec<T>::N;
     constexpr int R = LN_BWD_R;
@@ -282,6 +282,12 @@ ln_bwd_kernel(const T* dy, const T* gamma, const T* beta,
                     acc_g[i][e] += xhat * d;
                     acc_b[i][e] += d;
                 }
+                if (res) {      // res may be dx: this thread reads the packet it is about to write
+                    Vec<T> a;
+                    a.load_stream(res + row * hidden + idx * VN);
+#pragma unroll
+                    for (int e = 0; e < VN; e++) o.v[e] += a.v[e];
+                }
                 o.store_stream(dx + row * hidden + idx * VN);
             }
         }
@@ -342,7 +348,7 @@ ln_bwd_reduce_kernel(const float* partial, T* dgamma, T* dbeta, int nparts, int 
 // Generic path: one CTA per row for dx; column sums by a thread-per-column kernel.
 template <typename T>
 __global__ void __launch_bounds__(256)
-ln_bwd_dx_generic_kernel(const T* dy, const T* gamma, const T* beta, const float* var, const T* y, T* dx,
+ln_bwd_dx_generic_kernel(const T* dy, const T* gamma, const T* beta, const float* var, const T* y, const T* res, T* dx,
                          int64_t rows, int hidden, float eps) {
     __shared__ float red[64];
     const int64_t row = blockIdx.x;
@@ -364,7 +370,9 @@ ln_bwd_dx_generic_kernel(const T* dy, const T* gamma, const T* beta, const float
         float gm = to_f32(gamma[i]);
         float xhat = (to_f32(yr[i]) - to_f32(beta[i])) / guard_gamma(gm, eps);
         float g = to_f32(dyr[i]) * gm;
-        dx[row * hidden + i] = from_f32<T>((g - mg - xhat * mgx) * rstd);
+        float o = (g - mg - xhat * mgx) * rstd;
+        if (res) o += to_f32(res[row * hidden + i]);
+        dx[row * hidden + i] = from_f32<T>(o);
     }
 }
 
@@ -396,20 +404,21 @@ static int ln_bwd_grid(int64_t rows) {
 }
 
 template <typename T>
-static int ln_bwd_dispatch(const void* dy_, const void* gamma_, const void* beta_, const float* var, const void* y_,
+static int ln_bwd_dispatch(const void* dy_, const void* gamma_, const void* beta_, const float* var, const void* y_, const void* res_,
                            void* dgamma_, void* dbeta_, void* dx_, int64_t rows, int64_t hidden, float eps,
                            void* workspace, size_t workspace_bytes, int accumulate, cudaStream_t st) {
     const T* dy = (const T*)dy_;
     const T* gamma = (const T*)gamma_;
     const T* beta = (const T*)beta_;
     const T* y = (const T*)y_;
+    const T* res = (const T*)res_;
     T* dgamma = (T*)dgamma_;
     T* dbeta = (T*)dbeta_;
     T* dx = (T*)dx_;
     constexpr int VN = Vec<T>::N;
     const int64_t nvec = hidden / VN;
     bool fast = (hidden % VN == 0) && nvec <= 2048 && aligned16(dy) && aligned16(y) && aligned16(dx) &&
-                aligned16(gamma) && aligned16(beta) && aligned16(workspace);
+                aligned16(gamma) && aligned16(beta) && aligned16(workspace) && aligned16(res);
     if (fast) {
         if (workspace == nullptr || workspace_bytes < brk_layernorm_bwd_workspace_bytes(rows, hidden)) return BRK_ATTR_ERROR;
         float* partial = (float*)workspace;
@@ -423,11 +432,11 @@ static int ln_bwd_dispatch(const void* dy_, const void* gamma_, const void* beta
             int rgrid = 0;      // at most one CTA per SM: never more partial rows than the workspace was sized for
             int rc;
             if (rnvt == 1)
-                rc = launch_ln_bwd_ring<T, 1>(dy, gamma, beta, var, y, dx, partial, rows, h, eps, &rgrid, st);
+                rc = launch_ln_bwd_ring<T, 1>(dy, gamma, beta, var, y, res, dx, partial, rows, h, eps, &rgrid, st);
             else if (rnvt == 2)
-                rc = launch_ln_bwd_ring<T, 2>(dy, gamma, beta, var, y, dx, partial, rows, h, eps, &rgrid, st);
+                rc = launch_ln_bwd_ring<T, 2>(dy, gamma, beta, var, y, res, dx, partial, rows, h, eps, &rgrid, st);
             else
-                rc = launch_ln_bwd_ring<T, (Vec<T>::N == 4 ? 4 : 2)>(dy, gamma, beta, var, y, dx, partial, rows, h, eps, &rgrid, st);
+                rc = launch_ln_bwd_ring<T, (Vec<T>::N == 4 ? 4 : 2)>(dy, gamma, beta, var, y, res, dx, partial, rows, h, eps, &rgrid, st);
             if (rc) return rc;
             // programmatic dependent launch: the reduce kernel's launch overlaps the tail of the kernel above
             const float* cpartial = partial;
@@ -442,11 +451,11 @@ static int ln_bwd_dispatch(const void* dy_, const void* gamma_, const void* beta
         int nvt = nvec <= 512 ? 1 : (nvec <= 1024 ? 2 : 4);
         int threads = (int)(((nvec + nvt - 1) / nvt + 31) / 32 * 32);
         if (nvt == 1)
-            ln_bwd_kernel<T, 1><<<grid, threads, 0, st>>>(dy, gamma, beta, var, y, dx, partial, rows, h, eps);
+            ln_bwd_kernel<T, 1><<<grid, threads, 0, st>>>(dy, gamma, beta, var, y, res, dx, partial, rows, h, eps);
         else if (nvt == 2)
-            ln_bwd_kernel<T, 2><<<grid, threads, 0, st>>>(dy, gamma, beta, var, y, dx, partial, rows, h, eps);
+            ln_bwd_kernel<T, 2><<<grid, threads, 0, st>>>(dy, gamma, beta, var, y, res, dx, partial, rows, h, eps);
         else
-            ln_bwd_kernel<T, 4><<<grid, threads, 0, st>>>(dy, gamma, beta, var, y, dx, partial, rows, h, eps);
+            ln_bwd_kernel<T, 4><<<grid, threads, 0, st>>>(dy, gamma, beta, var, y, res, dx, partial, rows, h, eps);
         int rc = launch_status("ln_bwd_kernel");
         if (rc) return rc;
         ln_bwd_reduce_kernel<T><<<(2 * h + 31) / 32, 32 * LN_RED_LANES, 0, st>>>(partial, dgamma, dbeta, grid, h, accumulate);
@@ -457,7 +466,7 @@ static int ln_bwd_dispatch(const void* dy_, const void* gamma_, const void* beta
                                                                                   (int)hidden, eps, accumulate);
     int rc = launch_status("ln_bwd_cols_generic_kernel");
     if (rc) return rc;
-    ln_bwd_dx_generic_kernel<T><<<(unsigned)rows, 256, 0, st>>>(dy, gamma, beta, var, y, dx, rows, (int)hidden, eps);
+    ln_bwd_dx_generic_kernel<T><<<(unsigned)rows, 256, 0, st>>>(dy, gamma, beta, var, y, res, dx, rows, (int)hidden, eps);
     return launch_status("ln_bwd_dx_generic_kernel");
 }
 
@@ -488,21 +497,29 @@ extern "C" size_t brk_layernorm_bwd_workspace_bytes(int64_t rows, int64_t hidden
     return (size_t)(rows < cap ? rows : cap) * 2 * (size_t)hidden * sizeof(float);
 }
 
-extern "C" int brk_layernorm_bwd(const void* dy, const void* gamma, const void* beta, const float* var, const void* y,
-                                 void* dgamma, void* dbeta, void* dx, int64_t rows, int64_t hidden, float eps,
-                                 void* workspace, size_t workspace_bytes, int accumulate, int dtype, void* stream) {
+extern "C" int brk_layernorm_bwd_residual(const void* dy, const void* gamma, const void* beta, const float* var, const void* y,
+                                          const void* residual, void* dgamma, void* dbeta, void* dx, int64_t rows, int64_t hidden,
+                                          float eps, void* workspace, size_t workspace_bytes, int accumulate, int dtype,
+                                          void* stream) {
     if (!dy || !gamma || !beta || !var || !y) return BRK_INPUT_ERROR;
     if (!dgamma || !dbeta || !dx) return BRK_OUTPUT_ERROR;
     if (rows < 0 || hidden <= 0 || hidden > (1 << 30) || rows > 0x7fffffffLL) return BRK_ATTR_ERROR;
     if (rows == 0) return BRK_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == BRK_F32)
-        return brk::ln_bwd_dispatch<float>(dy, gamma, beta, var, y, dgamma, dbeta, dx, rows, hidden, eps, workspace,
+        return brk::ln_bwd_dispatch<float>(dy, gamma, beta, var, y, residual, dgamma, dbeta, dx, rows, hidden, eps, workspace,
                                            workspace_bytes, accumulate, st);
     if (dtype == BRK_F16)
-        return brk::ln_bwd_dispatch<__half>(dy, gamma, beta, var, y, dgamma, dbeta, dx, rows, hidden, eps, workspace,
+        return brk::ln_bwd_dispatch<__half>(dy, gamma, beta, var, y, residual, dgamma, dbeta, dx, rows, hidden, eps, workspace,
                                             workspace_bytes, accumulate, st);
     return BRK_ATTR_ERROR;
+}
+
+extern "C" int brk_layernorm_bwd(const void* dy, const void* gamma, const void* beta, const float* var, const void* y,
+                                 void* dgamma, void* dbeta, void* dx, int64_t rows, int64_t hidden, float eps,
+                                 void* workspace, size_t workspace_bytes, int accumulate, int dtype, void* stream) {
+    return brk_layernorm_bwd_residual(dy, gamma, beta, var, y, nullptr, dgamma, dbeta, dx, rows, hidden, eps, workspace,
+                                      workspace_bytes, accumulate, dtype, stream);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -575,8 +592,8 @@ extern "C" int brk_layernorm_bwd_static(const void* dy, const void* gamma, const
     if (rc != BRK_OK) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == BRK_F32)
-        return brk::ln_bwd_dispatch<float>(dy, gamma, beta, var, y, dgamma, dbeta, dx, rows, hidden, eps, scratch,
+        return brk::ln_bwd_dispatch<float>(dy, gamma, beta, var, y, nullptr, dgamma, dbeta, dx, rows, hidden, eps, scratch,
                                            brk::LN_BWD_STATIC_BYTES, accumulate, st);
-    return brk::ln_bwd_dispatch<__half>(dy, gamma, beta, var, y, dgamma, dbeta, dx, rows, hidden, eps, scratch,
+    return brk::ln_bwd_dispatch<__half>(dy, gamma, beta, var, y, nullptr, dgamma, dbeta, dx, rows, hidden, eps, scratch,
                                         brk::LN_BWD_STATIC_BYTES, accumulate, st);
 }

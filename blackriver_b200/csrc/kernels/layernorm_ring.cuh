@@ -307,7 +307,7 @@ struct LnrBwdRows {      // rows per stage: two while a thread's columns fit 8 f
 
 template <typename T, int NVT, int DEPTH>
 __global__ void __launch_bounds__(LNR_BWD_MAX_THREADS, 1)
-ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var, const T* y, T* dx, float* partial,
+ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var, const T* y, const T* res, T* dx, float* partial,
                    int64_t rows, int hidden, float eps) {
     constexpr int VN = Vec<T>::N;
     constexpr int R = LnrBwdRows<T, NVT>::R;
@@ -396,6 +396,8 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
 
     int phase = 0, stage = 0;
     unsigned char* dx_row = reinterpret_cast<unsigned char*>(dx) + (size_t)first_row * row_bytes;
+    // optional residual added to dx (res may be dx itself: a thread reads exactly the packets it writes, before it writes)
+    const unsigned char* res_row = res ? reinterpret_cast<const unsigned char*>(res) + (size_t)first_row * row_bytes : nullptr;
     for (; rows_left > 0; rows_left -= stride_rows, dx_row += stride_bytes, var_ptr += stride_rows, phase ^= 1) {
         const float var2 = (var_thread && rows_left - tid > 2 * stride_rows) ? __ldg(var_ptr + 2 * stride_rows) : 1.0f;
         cp_async_wait<DEPTH - 1>();      // the current group has landed (this thread's own packets)
@@ -441,6 +443,16 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
             sums[2 * r] = a;
             sums[2 * r + 1] = b;
         }
+        // the residual packets are fetched here so that their latency passes behind the block-wide sums
+        uint4 vres[R][NVT];
+        if (res_row) {
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int i = 0; i < NVT; i++)
+                    vres[r][i] = (own[i] && r < rows_left) ? __ldcs(reinterpret_cast<const uint4*>(res_row + (size_t)r * row_bytes + off[i]))
+                                                           : make_uint4(0u, 0u, 0u, 0u);
+        }
         // this thread's packets of the stage have been read and used by now: refill them with the group DEPTH ahead
         prefetch(stage);
         if (++stage == DEPTH) stage = 0;
@@ -461,9 +473,16 @@ ln_bwd_ring_kernel(const T* dy, const T* gamma, const T* beta, const float* var,
                 Vec<T> o;
 #pragma unroll
                 for (int e = 0; e < VN; e++) o.v[e] = fmaf(vdy[r][i].v[e], rstd, fmaf(vy[r][i].v[e], c2, c1));
+                if (res_row) {
+                    Vec<T> a;
+                    a.unpack(vres[r][i]);
+#pragma unroll
+                    for (int e = 0; e < VN; e++) o.v[e] += a.v[e];
+                }
                 __stcs(reinterpret_cast<uint4*>(dx_row + (size_t)r * row_bytes + off[i]), o.pack());
             }
         }
+        if (res_row) res_row += stride_bytes;
         var0 = var1;
         var1 = var2;
     }
@@ -505,7 +524,7 @@ static int lnr_bwd_grid(int64_t rows) {
 }
 
 template <typename T, int NVT, int DEPTH>
-static int launch_ln_bwd_ring_d(const T* dy, const T* gamma, const T* beta, const float* var, const T* y, T* dx, float* partial,
+static int launch_ln_bwd_ring_d(const T* dy, const T* gamma, const T* beta, const float* var, const T* y, const T* res, T* dx, float* partial,
                                 int64_t rows, int hidden, float eps, int grid, cudaStream_t st) {
     constexpr int VN = Vec<T>::N;
     constexpr int R = LnrBwdRows<T, NVT>::R;
@@ -522,7 +541,7 @@ static int launch_ln_bwd_ring_d(const T* dy, const T* gamma, const T* beta, cons
         set_cuda_error(attr_err, "ln_bwd_ring smem attribute");
         return BRK_CUDA_ERROR;
     }
-    cudaError_t le = launch_pdl(ln_bwd_ring_kernel<T, NVT, DEPTH>, grid, threads, smem, st, dy, gamma, beta, var, y, dx, partial, rows,
+    cudaError_t le = launch_pdl(ln_bwd_ring_kernel<T, NVT, DEPTH>, grid, threads, smem, st, dy, gamma, beta, var, y, res, dx, partial, rows,
                                 hidden, eps);
     if (le != cudaSuccess) {
         set_cuda_error(le, "ln_bwd_ring_kernel");
@@ -533,13 +552,13 @@ static int launch_ln_bwd_ring_d(const T* dy, const T* gamma, const T* beta, cons
 
 // Returns the number of CTAs (= partial rows written) through *grid_out.
 template <typename T, int NVT>
-static int launch_ln_bwd_ring(const T* dy, const T* gamma, const T* beta, const float* var, const T* y, T* dx, float* partial,
+static int launch_ln_bwd_ring(const T* dy, const T* gamma, const T* beta, const float* var, const T* y, const T* res, T* dx, float* partial,
                               int64_t rows, int hidden, float eps, int* grid_out, cudaStream_t st) {
     const int grid = lnr_bwd_grid<T, NVT>(rows);
     *grid_out = grid;
     if (lnr_bwd_depth<T, NVT>((size_t)hidden * sizeof(T)) == 6)
-        return launch_ln_bwd_ring_d<T, NVT, 6>(dy, gamma, beta, var, y, dx, partial, rows, hidden, eps, grid, st);
-    return launch_ln_bwd_ring_d<T, NVT, 3>(dy, gamma, beta, var, y, dx, partial, rows, hidden, eps, grid, st);
+        return launch_ln_bwd_ring_d<T, NVT, 6>(dy, gamma, beta, var, y, res, dx, partial, rows, hidden, eps, grid, st);
+    return launch_ln_bwd_ring_d<T, NVT, 3>(dy, gamma, beta, var, y, res, dx, partial, rows, hidden, eps, grid, st);
 }
 
 }  // namespace brk

@@ -48,8 +48,8 @@ def layernorm(x, gamma, beta, eps=1e-5, out=None):
 
 
 def layernorm_backward(dy, gamma, beta, var, y, eps=1e-5, dgamma=None, dbeta=None, dx=None, accumulate=False,
-                       workspace=None):
-    _chk(dy, gamma, beta, var, y, dgamma, dbeta, dx, workspace)
+                       workspace=None, residual=None):
+    _chk(dy, gamma, beta, var, y, dgamma, dbeta, dx, workspace, residual)
     h = dy.shape[-1]
     rows = dy.numel() // h
     dgamma = torch.empty_like(gamma) if dgamma is None else dgamma
@@ -58,9 +58,14 @@ def layernorm_backward(dy, gamma, beta, var, y, eps=1e-5, dgamma=None, dbeta=Non
     need = brk.lib().brk_layernorm_bwd_workspace_bytes(rows, h)
     if workspace is None:
         workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=dy.device)
-    brk.call("brk_layernorm_bwd", _ptr(dy), _ptr(gamma), _ptr(beta), _ptr(var), _ptr(y), _ptr(dgamma), _ptr(dbeta),
-             _ptr(dx), rows, h, eps, _ptr(workspace), workspace.numel() * workspace.element_size(), int(accumulate),
-             _dt(dy), stream())
+    if residual is None:
+        brk.call("brk_layernorm_bwd", _ptr(dy), _ptr(gamma), _ptr(beta), _ptr(var), _ptr(y), _ptr(dgamma), _ptr(dbeta),
+                 _ptr(dx), rows, h, eps, _ptr(workspace), workspace.numel() * workspace.element_size(), int(accumulate),
+                 _dt(dy), stream())
+    else:
+        brk.call("brk_layernorm_bwd_residual", _ptr(dy), _ptr(gamma), _ptr(beta), _ptr(var), _ptr(y), _ptr(residual), _ptr(dgamma),
+                 _ptr(dbeta), _ptr(dx), rows, h, eps, _ptr(workspace), workspace.numel() * workspace.element_size(),
+                 int(accumulate), _dt(dy), stream())
     return dgamma, dbeta, dx
 
 

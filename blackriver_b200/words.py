@@ -385,13 +385,11 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
             w(f'    {g("yout_g", "x4b", "dense_4h_to_h.weight", "dense_4h_to_h.bias", "d4", "dense_4h_to_h.weight_g", "dense_4h_to_h.bias_g")} op.linear_backward')
             w(f'    {g("d4", "x4a", "d4")} op.gelu_backward')
             w(f'    {g("d4", "xb", "dense_h_to_4h.weight", "dense_h_to_4h.bias", "dh1", "dense_h_to_4h.weight_g", "dense_h_to_4h.bias_g")} op.linear_backward')
-            w(f'    {g("dh1", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "post_ln_var", "xb", "post_attention_layernorm.weight_g", "post_attention_layernorm.bias_g", "dh2", "LN_EPS")} op.layernorm_backward')
-            w(f'    {g("yout_g", "dh2", "dh2")} op.add')
+            w(f'    {g("dh1", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "post_ln_var", "xb", "post_attention_layernorm.weight_g", "post_attention_layernorm.bias_g", "dh2", "yout_g", "LN_EPS")} op.layernorm_backward_residual')
             w(f'    {g("dh2", "attn_out", "dense.weight", "dense.bias", "dh1", "dense.weight_g", "dense.bias_g")} op.linear_backward')
             w(f'    {g("dh1", "qkv", "attn_out", "lse", "lens_", "dqkv", "HEADS_NUM")} op.flash_attn_backward')
             w(f'    {g("dqkv", "xattn_in", "query_key_value.weight", "query_key_value.bias", "dh1", "query_key_value.weight_g", "query_key_value.bias_g")} op.linear_backward')
-            w(f'    {g("dh1", "input_layernorm.weight", "input_layernorm.bias", "input_ln_var", "xattn_in", "input_layernorm.weight_g", "input_layernorm.bias_g", "dh3", "LN_EPS")} op.layernorm_backward')
-            w(f'    {g("dh3", "dh2", "xin_g")} op.add')
+            w(f'    {g("dh1", "input_layernorm.weight", "input_layernorm.bias", "input_ln_var", "xattn_in", "input_layernorm.weight_g", "input_layernorm.bias_g", "xin_g", "dh2", "LN_EPS")} op.layernorm_backward_residual')
             w("%end")
 
         # the same backward in two passes: input gradients (what the previous stage waits for), then weight gradients
@@ -400,14 +398,12 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
             w(f'    {g("yout_g", "dense_4h_to_h.weight", "d4")} op.linear_backward_x')
             w(f'    {g("d4", "x4a", "d4")} op.gelu_backward')
             w(f'    {g("d4", "dense_h_to_4h.weight", "dh1")} op.linear_backward_x')
-            w(f'    {g("dh1", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "post_ln_var", "xb", "post_attention_layernorm.weight_g", "post_attention_layernorm.bias_g", "dh2", "LN_EPS")} op.layernorm_backward')
-            w(f'    {g("yout_g", "dh2", "dh2")} op.add')
+            w(f'    {g("dh1", "post_attention_layernorm.weight", "post_attention_layernorm.bias", "post_ln_var", "xb", "post_attention_layernorm.weight_g", "post_attention_layernorm.bias_g", "dh2", "yout_g", "LN_EPS")} op.layernorm_backward_residual')
         if "A" in kind:
             w(f'    {g("dh2", "dense.weight", "dh1")} op.linear_backward_x')
             w(f'    {g("dh1", "qkv", "attn_out", "lse", "lens_", "dqkv", "HEADS_NUM")} op.flash_attn_backward')
             w(f'    {g("dqkv", "query_key_value.weight", "dh1")} op.linear_backward_x')
-            w(f'    {g("dh1", "input_layernorm.weight", "input_layernorm.bias", "input_ln_var", "xattn_in", "input_layernorm.weight_g", "input_layernorm.bias_g", "dh3", "LN_EPS")} op.layernorm_backward')
-            w(f'    {g("dh3", "dh2", "xin_g")} op.add')
+            w(f'    {g("dh1", "input_layernorm.weight", "input_layernorm.bias", "input_ln_var", "xattn_in", "input_layernorm.weight_g", "input_layernorm.bias_g", "xin_g", "dh2", "LN_EPS")} op.layernorm_backward_residual')
         w("%end")
         w(f"%def layer_backward_w_{tag}")
         if "M" in kind:

@@ -61,6 +61,14 @@ BRK_API int brk_layernorm_bwd(const void* dy, const void* gamma, const void* bet
                       void* dgamma, void* dbeta, void* dx, int64_t rows, int64_t hidden, float eps,
                       void* workspace, size_t workspace_bytes, int accumulate, int dtype, void* stream);
 
+/* The same with the residual branch of the block folded in: dx = residual + (LayerNorm input gradient), what the
+ * reference's backward kernel takes as its residual_grad input (blackriver/kernels/normalize_kernels.cu:134-221) and
+ * the words otherwise compute with a separate op_add.  residual [rows,hidden] in `dtype`, NULL = none (then identical
+ * to brk_layernorm_bwd); it may alias dx.  The sum is formed in fp32 and rounded once. */
+BRK_API int brk_layernorm_bwd_residual(const void* dy, const void* gamma, const void* beta, const float* var, const void* y,
+                      const void* residual, void* dgamma, void* dbeta, void* dx, int64_t rows, int64_t hidden, float eps,
+                      void* workspace, size_t workspace_bytes, int accumulate, int dtype, void* stream);
+
 /* Kernel selection of the LayerNorm kernels, for measurements (no counterpart in the reference).
  * Mode 0 (default): rows of 2 KiB and more are prefetched through shared memory with asynchronous
  * copies, several rows ahead; mode 1 keeps to the register-resident kernels. */

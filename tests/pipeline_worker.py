@@ -73,6 +73,10 @@ def main():
     tr = finetune.Trainer(CFG["hidden"], CFG["heads"], CFG["vocab"], CFG["n_layers"], CFG["batch"], CFG["tokens"], CFG["n_micro"],
                           rank=rank, world=world, seed=9, lr=1e-3, init_std=0.05, head_cost=head_cost,
                           overlap=os.environ.get("BR_TEST_OVERLAP", "1") != "0", replicas=replicas)
+    # forward-only scoring through the same stages (the prefill path) with the initial weights: per-token NLL from the
+    # rank that holds the head
+    scored = tr.score(mbs[:2]) if replicas == 1 else []
+    tr.sync()
     losses = [tr.step(mbs) for _ in range(2)]
     tr.sync()
     w_first = None
@@ -81,6 +85,9 @@ def main():
         w_first = tr.env.read("_flat.master").copy()          # first layer of this stage
     tr.env.change(0)
     table = tr.env.read("word_embeddings.weight.master").copy() if (tr.first or tr.last) else None
+    box = [[(nll.tolist(), mean) for nll, mean in scored]]
+    dist.broadcast_object_list(box, src=stages - 1)
+    pipe_scores = box[0]
     box = [losses]
     dist.broadcast_object_list(box, src=stages - 1)           # the head's rank of the first replica
     pipe_losses = box[0]
@@ -95,8 +102,12 @@ def main():
     if rank == 0:
         single = finetune.Trainer(CFG["hidden"], CFG["heads"], CFG["vocab"], CFG["n_layers"], CFG["batch"], CFG["tokens"],
                                   CFG["n_micro"], rank=0, world=1, seed=9, lr=1e-3, init_std=0.05)
+        ref_scores = single.score(mbs[:2])
         ref_losses = [single.step(mbs) for _ in range(2)]
         single.sync()
+        score_err = 0.0
+        for (nll, mean), (rn, rm) in zip(pipe_scores, ref_scores):
+            score_err = max(score_err, float(np.abs(np.asarray(nll, np.float32) - rn).max()), abs(mean - rm))
         single.env.change(1)
         ref_w = single.env.read("_flat.master").copy()
         single.env.change(0)
@@ -107,7 +118,7 @@ def main():
             "w_err": float(np.abs(w_first - ref_w).max() / np.abs(ref_w).max()),
             "table_err": float(np.abs(table - ref_table).max() / np.abs(ref_table).max()),
             "tables_agree": abs(tables[0] - tables[-1]) <= 1e-6 * abs(tables[0]),
-            "counts": tr.counts, "overlap": tr.overlap, "n_slots": tr.n_slots, "replicas": replicas, "replicas_agree": replicas_agree,
+            "scored": len(pipe_scores), "score_err": score_err, "counts": tr.counts, "overlap": tr.overlap, "n_slots": tr.n_slots, "replicas": replicas, "replicas_agree": replicas_agree,
         }
         json.dump(res, open(out_path, "w"))
     dist.barrier()

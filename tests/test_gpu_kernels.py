@@ -119,6 +119,38 @@ def test_layernorm_ring_and_register_kernels(ops, mode, rows, hidden, dtype):
         brk.raw("brk_layernorm_set_mode", 0)
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("rows,hidden,dtype", [(2048, 4096, "f16"), (301, 2056, "f16"), (37, 1024, "f32"), (9, 8192, "f16"), (5, 100, "f32")])
+def test_layernorm_backward_with_residual(ops, mode, rows, hidden, dtype):
+    """dx = residual + the LayerNorm's input gradient (the residual branch of the block folded into the kernel), in every
+    kernel variant; also with the residual buffer as the output."""
+    from blackriver_b200 import brk
+    rng = np.random.default_rng(rows * 3 + hidden)
+    rnd = h16 if dtype == "f16" else (lambda a: np.asarray(a, np.float32))
+    td = torch.float16 if dtype == "f16" else torch.float32
+    tol = TOL16 if dtype == "f16" else TOL32
+    x = rnd(rng.standard_normal((rows, hidden)) * 1.3 + 0.2)
+    gamma = rnd(1.0 + 0.1 * rng.standard_normal(hidden))
+    beta = rnd(0.1 * rng.standard_normal(hidden))
+    dy = rnd(rng.standard_normal((rows, hidden)))
+    res = rnd(rng.standard_normal((rows, hidden)))
+    y_ref, _, var_ref = orc.layernorm(x, gamma, beta, 1e-5)
+    yin = rnd(y_ref)
+    dg_ref, db_ref, dx_ref = orc.layernorm_backward(dy, gamma, beta, var_ref, yin, 1e-5)
+    want = dx_ref.astype(np.float32) + res.astype(np.float32)
+    assert brk.raw("brk_layernorm_set_mode", mode) == 0
+    try:
+        resd = dev(res, td)
+        dg, db, dx = ops.layernorm_backward(dev(dy, td), dev(gamma, td), dev(beta, td), dev(var_ref), dev(yin, td), 1e-5, residual=resd)
+        assert relerr(host(dx), want) <= tol
+        assert relerr(host(dg), dg_ref) <= tol and relerr(host(db), db_ref) <= tol
+        assert np.array_equal(host(resd), res)          # the residual itself is left alone
+        _, _, dx2 = ops.layernorm_backward(dev(dy, td), dev(gamma, td), dev(beta, td), dev(var_ref), dev(yin, td), 1e-5, residual=resd, dx=resd)
+        assert np.array_equal(host(dx2), host(dx))      # residual buffer as the output: same values
+    finally:
+        brk.raw("brk_layernorm_set_mode", 0)
+
+
 def test_layernorm_unaligned_views_and_inplace(ops):
     rng = np.random.default_rng(5)
     rows, hidden = 6, 256

@@ -197,6 +197,11 @@ def test_loss_backward_word(host):
         assert relerr(env.read("lm_head.weight_g"), wg_ref) <= TOL32      # accumulated onto the previous value
         assert relerr(env.read("xc"), dx_ref) <= TOL32
         assert relerr(env.read("ln_f.weight_g"), dg_ref) <= TOL32 and relerr(env.read("ln_f.bias_g"), db_ref) <= TOL32
+        # the same backward with the residual branch folded in: din = residual + input gradient
+        env.execute('"xa" @ "ln_f.weight" @ "ln_f.bias" @ "post_ln_var" @ "xb" @ "ln_f.weight_g" @ "ln_f.bias_g" @ "xc" @ "xb" @ "LN_EPS" @ '
+                    'op.layernorm_backward_residual op.sync')
+        assert relerr(env.read("xc"), dx_ref + xb_ref) <= TOL32
+        assert relerr(env.read("ln_f.weight_g"), dg_ref) <= TOL32
     finally:
         env.close()
 

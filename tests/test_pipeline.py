@@ -46,6 +46,9 @@ def check_against_single(res):
     # other way, so the bound is a few update steps relative to the largest weight
     assert res["w_err"] <= 1e-2 and res["table_err"] <= 1e-2
     assert res["tables_agree"]          # both holders of the tied table applied the same summed gradient
+    if res["replicas"] == 1:
+        # the forward-only scoring pass over the same stages (initial weights): per-token NLL and its mean
+        assert res["scored"] == 2 and res["score_err"] <= 2e-3
 
 
 @pytest.mark.gpu
