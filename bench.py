@@ -421,9 +421,12 @@ def run_finetune(args):
         ops_args = argparse.Namespace(steps=50, warmup=3)
         ops_line = run_ops(ops_args, emit=False)
 
-    # the library computes on torch's current stream so that torch events bracket its work
-    stream = torch.cuda.current_stream().cuda_stream
-    host.context_boot(local, stream, 512 << 20)
+    # the library computes on torch's current stream so that torch events bracket its work.  That has to be a stream of
+    # its own: the legacy default stream has handle 0, which the library reads as "create your own stream", and events
+    # on the default stream would not wait for that one.
+    compute_stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(compute_stream)
+    host.context_boot(local, compute_stream.cuda_stream, 512 << 20)
     if world > 1:
         box = [host.collective_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
@@ -488,7 +491,33 @@ def run_finetune(args):
     prof = host.profile_stop()
     barrier()
 
+    # ---- optional: when every task of one step ended on each rank's device (events behind the tasks), next to the
+    # schedule simulation's plan for the same lists
+    timeline = None
+    if args.timeline:
+        barrier()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(tr.tasks) + 2)]
+        evs[0].record()
+        tr.step(mbs, after_task=lambda i: evs[i + 1].record())
+        evs[-1].record()
+        torch.cuda.synchronize()
+        names = [(t.kind, t.k) for t in tr.order] if tr.order else [("F" if i % 2 == 0 else "BW", i // 2) for i in range(len(tr.tasks))]
+        mine = [[k, n, round(evs[0].elapsed_time(evs[i + 1]), 3)] for i, (k, n) in enumerate(names)]
+        mine.append(["opt", -1, round(evs[0].elapsed_time(evs[-1]), 3)])
+        timeline = [mine]
+        if world > 1:
+            gathered_tl = [None] * world
+            dist.all_gather_object(gathered_tl, mine)
+            timeline = gathered_tl
+        barrier()
+
+    # device time of every rank's kernels in the instrumented step (each interval carries ~3 us of event overhead): the
+    # rank with the largest sum paces the pipeline, the gap to the step time is what it spent waiting
+    busy = [round(sum(v["ms"] for v in prof.values()), 1)]
     if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, busy[0])
+        busy = gathered
         t = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total, ms_e2e = float(t[0]), float(t[1])
@@ -539,7 +568,7 @@ def run_finetune(args):
                                          "47.8 MB written per launch in DRAM against 151.0 + 67.1 MB algorithmic "
                                          "(profiles/gemm_f16_pair_2048x16384x4096.md)",
                          "flops_per_step": flops, "ms_per_step": round(gemm_ms, 3)},
-            "step_profile_ms": fam,
+            "step_profile_ms": fam, "rank_kernel_ms": busy, "timeline_ms": timeline,
             "in_step_hbm_kernels": in_step_hbm(prof, cfg) if world == 1 else None,
             "kernels": None if ops_line is None else ops_line.get("kernels"),
             "ops_microbench": None if ops_line is None else {"value": ops_line["value"], "unit": "tokens/s",
@@ -574,7 +603,9 @@ def run_prefill(args):
     cfg = dict(PREFILL)
     if args.layers:
         cfg["n_layers"] = args.layers
-    host.context_boot(local, torch.cuda.current_stream().cuda_stream, 512 << 20)
+    compute_stream = torch.cuda.Stream(device=dev)          # torch events and the library's work share this stream
+    torch.cuda.set_stream(compute_stream)
+    host.context_boot(local, compute_stream.cuda_stream, 512 << 20)
     if world > 1:
         box = [host.collective_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
@@ -1097,6 +1128,8 @@ def main():
     ap.add_argument("--micro", type=int, default=0, help="fine-tune workload with fewer micro-batches (development aid)")
     ap.add_argument("--replicas", type=int, default=1,
                     help="fine-tune workload: data-parallel replicas of a (gpus / replicas)-stage pipeline; the default is one pipeline over all GPUs")
+    ap.add_argument("--timeline", action="store_true",
+                    help="fine-tune workload: also report when each task of one step ended on every rank (development aid)")
     ap.add_argument("--no-overlap", action="store_true",
                     help="multi-GPU: the plain schedule (all forwards, all backwards, NCCL hand-offs) instead of the overlapped one")
     ap.add_argument("--skip-ops", action="store_true", help="do not run the operator microbench before the fine-tune step")

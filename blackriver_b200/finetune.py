@@ -237,11 +237,14 @@ class Trainer:
             self.env.execute(f"0 op.accumulate {tied_peer} sync_tied_start {args} optimizer_layers sync_tied_finish {args} optimizer_main")
         return float(np.mean(self.losses)) if self.losses else None
 
-    def step(self, microbatches):
-        """One optimizer step over the micro-batches; returns the mean loss (last stage) or None."""
+    def step(self, microbatches, after_task=None):
+        """One optimizer step over the micro-batches; returns the mean loss (last stage) or None.  after_task(i), if
+        given, is called when task i has been queued (a measurement hook: e.g. to record an event on the stream)."""
         self.begin_step(microbatches)
         for i in range(len(self.tasks)):
             self.run_task(i)
+            if after_task is not None:
+                after_task(i)
         if self.replicas > 1:
             self.env.execute("sync_replicas")
         self.check_and_read_losses()
