@@ -13,7 +13,7 @@ import numpy as np
 
 from . import host, schedule, words
 
-LM_HEAD_COST_IN_LAYERS = 3.8      # measured step time of final LayerNorm + 250880-way head + loss, in 7b1 decoder layers
+LM_HEAD_COST_IN_LAYERS = 4.3      # measured step time of final LayerNorm + 250880-way head + loss, in 7b1 decoder layers
 
 
 def partition_layers(n_layers, world, head_cost=LM_HEAD_COST_IN_LAYERS, n_micro=16):

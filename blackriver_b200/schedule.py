@@ -19,12 +19,12 @@ F(k) may only start once W(k - n_slots) has finished on that rank.
 """
 from dataclasses import dataclass
 
-# Relative costs of one decoder layer's three tasks and of the LM head + loss (same unit), from the measured
-# per-family device times of the 7b1-shaped step: forward GEMMs + attention forward; input-gradient GEMMs +
+# Costs of one decoder layer's three tasks and of the LM head + loss (milliseconds per micro-batch of 2048 tokens on a
+# B200, from the measured task durations of the 7b1-shaped step on two stages; only their ratios matter): forward GEMMs + attention forward; input-gradient GEMMs +
 # attention backward + LayerNorm / GELU backward; weight-gradient GEMMs + column sums.  The head's forward part
 # (logits GEMM + log-softmax) is counted with its B task because it runs there.
-LAYER_COST = (0.816, 1.051, 0.882)
-HEAD_COST = (0.1, 6.7, 3.6)
+LAYER_COST = (0.786, 0.924, 0.685)
+HEAD_COST = (0.5, 6.2, 3.6)
 
 
 @dataclass(frozen=True)
@@ -216,7 +216,7 @@ def choose_partition(n_layers, world, n_micro, n_slots=None, layer_cost=LAYER_CO
 # attention) has the same shape as a layer's output, so a stage boundary may fall there too, which lets 30 layers be
 # spread over 7 ranks in pieces of 4.3 layers instead of 5 and 4.  Costs (F, B, W) in the unit of LAYER_COST, from the
 # same measured profile: A carries a third of the layer's GEMM FLOPs plus the attention kernels, M two thirds.
-UNIT_COST = {"A": (0.323, 0.491, 0.303), "M": (0.493, 0.560, 0.579)}
+UNIT_COST = {"A": (0.327, 0.439, 0.250), "M": (0.459, 0.485, 0.435)}
 # What the two holders of the tied 250880 x 4096 table carry besides their layers, per micro-batch: the embedding gather +
 # LayerNorm and their backward (first rank only), and a sixteenth of the table's Adam update and gradient exchange
 TABLE_COST = (0.04, 0.08, 0.45)

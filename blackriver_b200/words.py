@@ -442,7 +442,7 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w(f'    {max(n_micro, 1)} 1 "cuda" "float" op.create "loss_all" !')
     for j in range(max(n_micro, 1)):
         w(f'    "loss_all" @ {j} 1 1 op.view "loss@{j}" !')
-    shared_scratch = [("dh1", 1), ("dh3", 1), ("gA", 1), ("gB", 1)] + ([] if overlap else [("d4", 4), ("dqkv", 3), ("dh2", 1)])
+    shared_scratch = [("dh1", 1), ("gA", 1), ("gB", 1)] + ([] if overlap else [("d4", 4), ("dqkv", 3), ("dh2", 1)])
     for name, cols in shared_scratch:
         w(f'    {batch} {tokens} {cols * hidden} 3 "cuda" "DTYPE" @ op.create "{name}" !')
     w(f'    {n} 1 "cuda" "float" op.create "ln_mean" !')
@@ -491,7 +491,7 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     for i in range(1, n_layers + 1):
         w(f"    {i} # create_layer_{tag_of(i)}")
     # bindings: scratch and inputs into every layer hash; activations chained layer to layer
-    shared = ("dh1", "dh3", "lens_", "LN_EPS", "HEADS_NUM") + (() if overlap else ("d4", "dqkv", "dh2"))
+    shared = ("dh1", "lens_", "LN_EPS", "HEADS_NUM") + (() if overlap else ("d4", "dqkv", "dh2"))
     for i in range(1, n_layers + 1):
         kind = kinds[i - 1]
         for name in shared:
