@@ -776,7 +776,7 @@ def time_gemm_shapes(torch, ops, brk, dev):
     N, H = 2048, 4096
     shapes = {  # name: (m, n, k, trans_a, trans_b, accumulate)
         "fwd_qkv": (N, 3 * H, H, 0, 1, 0), "fwd_dense": (N, H, H, 0, 1, 0), "fwd_h4h": (N, 4 * H, H, 0, 1, 0), "fwd_4hh": (N, H, 4 * H, 0, 1, 0),
-        "dx_qkv": (N, H, 3 * H, 0, 0, 0), "dx_h4h": (N, H, 4 * H, 0, 0, 0), "dx_4hh": (N, 4 * H, H, 0, 0, 0),
+        "dx_qkv": (N, H, 3 * H, 0, 0, 0), "dx_dense": (N, H, H, 0, 0, 0), "dx_h4h": (N, H, 4 * H, 0, 0, 0), "dx_4hh": (N, 4 * H, H, 0, 0, 0),
         "dw_qkv": (3 * H, H, N, 1, 0, 1), "dw_dense": (H, H, N, 1, 0, 1), "dw_h4h": (4 * H, H, N, 1, 0, 1), "dw_4hh": (H, 4 * H, N, 1, 0, 1),
         "head_fwd": (N, VOCAB, H, 0, 1, 0), "head_dx": (N, H, VOCAB, 0, 0, 0), "head_dw": (VOCAB, H, N, 1, 0, 1),
     }
@@ -786,8 +786,9 @@ def time_gemm_shapes(torch, ops, brk, dev):
         a = torch.randn((k, m) if ta else (m, k), generator=g, device=dev).half()
         b = torch.randn((n, k) if tb else (k, n), generator=g, device=dev).half()
         c = torch.zeros(m, n, device=dev).half()
-        for epi, tag in ((0, "tma"), (1, "registers")):
+        for epi, nosplit, tag in ((0, 0, "tma"), (0, 1, "tma, no split-k"), (1, 1, "registers")):
             brk.lib().brk_gemm_f16_set_epilogue(epi)
+            brk.lib().brk_gemm_f16_set_split_k(nosplit)
             ts = []
             for _ in range(6):
                 flush.zero_()
@@ -802,6 +803,7 @@ def time_gemm_shapes(torch, ops, brk, dev):
             res[f"{name}/{tag}"] = {"us": round(t * 1e3, 1), "tflops": round(2 * m * n * k / t / 1e9, 1)}
         del a, b, c
     brk.lib().brk_gemm_f16_set_epilogue(0)
+    brk.lib().brk_gemm_f16_set_split_k(0)
     assert brk.lib().brk_gemm_f16_status() == 0
     return res
 

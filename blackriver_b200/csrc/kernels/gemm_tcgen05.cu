@@ -39,6 +39,7 @@ struct TcParams {
     int m, n, k;
     int accumulate;
     int tiles_m, tiles_n;
+    int splits;      // CTA-pair kernel, staged epilogue only: each tile's k range is cut into this many work items
 };
 
 __device__ __forceinline__ float tc_gelu(float x) {
@@ -299,6 +300,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int num_tiles = p.tiles_m * p.tiles_n;         // pair tiles
     const int kblocks = (p.k + TC_BK - 1) / TC_BK;
+    // Work items: item = split * num_tiles + tile; split s of a tile covers k-blocks [kblocks * s / splits,
+    // kblocks * (s + 1) / splits) and adds its partial product into C (all splits reduce; C was cleared by the host).
+    const int num_items = num_tiles * p.splits;
+    auto kb_first = [&](int item) { return (int)((int64_t)kblocks * (item / num_tiles) / p.splits); };
+    auto kb_last = [&](int item) { return (int)((int64_t)kblocks * (item / num_tiles + 1) / p.splits); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC2_STAGES; s++) {
@@ -328,11 +334,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
+            for (int item = pair; item < num_items && ok; item += npairs) {
+                const int tile = item % num_tiles;
                 const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
                 const int row_a = tm * 256 + (int)rank * 128;
                 const int row_b = tn * BN + (int)rank * 128;
-                for (int kb = 0; kb < kblocks && ok; kb++, it++) {
+                const int kb1 = kb_last(item);
+                for (int kb = kb_first(item); kb < kb1 && ok; kb++, it++) {
                     const int s = it % TC2_STAGES;
                     ok = mbar_wait(&empty_bar[s], ((it / TC2_STAGES) & 1) ^ 1);
                     if (!ok) break;
@@ -360,13 +368,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (lane == 0 && rank == 0) {
             uint32_t it = 0, tcount = 0;
             bool ok = true;
-            for (int tile = pair; tile < num_tiles && ok; tile += npairs, tcount++) {
+            for (int item = pair; item < num_items && ok; item += npairs, tcount++) {
                 const int buf = tcount & 1;
                 ok = mbar_wait(&tmem_empty[buf], ((tcount >> 1) & 1) ^ 1);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < kblocks && ok; kb++, it++) {
+                const int kb0 = kb_first(item), kb1 = kb_last(item);
+                for (int kb = kb0; kb < kb1 && ok; kb++, it++) {
                     const int s = it % TC2_STAGES;
                     ok = mbar_wait(&full_bar[s], (it / TC2_STAGES) & 1);
                     if (!ok) break;
@@ -379,7 +388,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                                  : make_smem_desc_sw128(sa + kk * 32, 16, 1024);
                         const uint64_t db = B_MN ? make_smem_desc_sw128(sb + kk * 2048, 8192, 1024)
                                                  : make_smem_desc_sw128(sb + kk * 32, 16, 1024);
-                        umma_f16_ss_pair(d_tmem, da, db, IDESC, (kb | kk) != 0 ? 1u : 0u);
+                        umma_f16_ss_pair(d_tmem, da, db, IDESC, (kb != kb0 || kk != 0) ? 1u : 0u);
                     }
                     umma_commit_pair(&empty_bar[s], 3);      // frees the stage in both CTAs
                 }
@@ -417,7 +426,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             unsigned char* my_boxes = out_boxes + quarter * (2 * TC2_OUT_BOX_BYTES);
             const bool bias_vec = p.bias && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
             uint32_t nbox = 0;                       // boxes handed to the TMA unit so far by this warp
-            for (int tile = pair; tile < num_tiles && ok; tile += npairs, tcount++) {
+            const bool reduce = p.accumulate != 0 || p.splits > 1;
+            for (int item = pair; item < num_items && ok; item += npairs, tcount++) {
+                const int tile = item % num_tiles;
+                const bool add_bias = p.bias != nullptr && item < num_tiles;      // the first split of a tile carries the bias
                 const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
                 const int buf = tcount & 1;
                 ok = mbar_wait(&tmem_full[buf], (tcount >> 1) & 1);
@@ -448,7 +460,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         float f[8];
 #pragma unroll
                         for (int e = 0; e < 8; e++) f[e] = __uint_as_float(v[q * 8 + e]);
-                        if (p.bias) {
+                        if (add_bias) {
                             const int c = col0 + q * 8;
                             if (bias_vec && c + 8 <= p.n) {
                                 Vec<__half> b;
@@ -470,7 +482,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) {
-                        if (p.accumulate) tma_reduce_add_2d(&tmap_c, box, col0, row0);
+                        if (reduce) tma_reduce_add_2d(&tmap_c, box, col0, row0);
                         else tma_store_2d(&tmap_c, box, col0, row0);
                         bulk_commit();
                     }
@@ -557,7 +569,7 @@ static int launch_tc_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CU
         set_cuda_error(attr_err, "gemm_tc_pair smem attribute");
         return BRK_CUDA_ERROR;
     }
-    int tiles = p.tiles_m * p.tiles_n;
+    int tiles = p.tiles_m * p.tiles_n * p.splits;      // work items
     int pairs = sm_count() / 2;
     if (tiles < pairs) pairs = tiles;
     cudaLaunchConfig_t cfg = {};
@@ -593,11 +605,39 @@ static int dispatch_pair(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUte
 static int g_tc_mode = 0;
 // 0 = staged (TMA store / reduce) epilogue where it applies, 1 = always the direct register epilogue
 static int g_tc_epilogue = 0;
+// 0 = cut the k range of the tiles into several work items where that fills the last wave of CTA pairs, 1 = never
+static int g_tc_split_k = 0;
+
+// Work items per tile for the CTA-pair kernel with the staged epilogue.  `tiles` pair tiles on `pairs` CTA pairs run in
+// ceil(tiles / pairs) waves; with 128 tiles on 74 pairs the second wave is 73 % full.  Cutting every tile's k range
+// into s items (each adds its partial product into C through the TMA reduction) changes the fill of the last wave; s
+// is taken only if it raises the fill by a tenth and leaves at least 32 k-blocks per item (below that the epilogue of
+// an item is no longer hidden behind the next item's products).
+static int choose_splits(int tiles, int pairs, int kblocks) {
+    if (g_tc_split_k != 0) return 1;
+    auto fill = [&](int s) {
+        const long items = (long)tiles * s;
+        const long waves = (items + pairs - 1) / pairs;
+        return (double)items / (double)(waves * pairs);
+    };
+    int best = 1;
+    double best_fill = fill(1);
+    for (int s = 2; s <= 4; s++) {
+        if (kblocks / s < 32) break;
+        const double f = fill(s);
+        if (f > best_fill + 0.1) {
+            best = s;
+            best_fill = f;
+        }
+    }
+    return best;
+}
 
 }  // namespace brk
 
 extern "C" void brk_gemm_f16_set_mode(int mode) { brk::g_tc_mode = mode; }
 extern "C" void brk_gemm_f16_set_epilogue(int mode) { brk::g_tc_epilogue = mode; }
+extern "C" void brk_gemm_f16_set_split_k(int mode) { brk::g_tc_split_k = mode; }
 
 extern "C" int brk_gemm_f16_supported(int64_t m, int64_t n, int64_t k, int trans_a, int trans_b, int64_t lda, int64_t ldb,
                                       const void* a, const void* b) {
@@ -649,6 +689,7 @@ extern "C" int brk_gemm_f16(const void* a, const void* b, void* c, int64_t m, in
     p.accumulate = accumulate;
     p.tiles_m = (int)((m + TC_BM - 1) / TC_BM);
     p.tiles_n = (int)((n + bn - 1) / bn);
+    p.splits = 1;
     cudaStream_t st = (cudaStream_t)stream;
     if (use_pair) {
         p.tiles_m = (int)((m + 255) / 256);
@@ -657,7 +698,18 @@ extern "C" int brk_gemm_f16(const void* a, const void* b, void* c, int64_t m, in
         CUtensorMap tc;
         const bool staged = g_tc_epilogue != 1 && !residual && !gelu_out &&
                             make_tmap_2d_f16(&tc, c, (uint64_t)m, (uint64_t)n, (uint64_t)ldc, 64, 32);
-        if (staged) return dispatch_pair<true>(a_mn, b_mn, ta, tb, tc, p, st);
+        if (staged) {
+            p.splits = choose_splits(p.tiles_m * p.tiles_n, sm_count() / 2, (int)((k + TC_BK - 1) / TC_BK));
+            if (p.splits > 1 && !accumulate) {
+                // every item adds into C: clear it first (the bias rides on the first item of each tile)
+                cudaError_t e = cudaMemset2DAsync(c, (size_t)ldc * 2, 0, (size_t)n * 2, (size_t)m, st);
+                if (e != cudaSuccess) {
+                    set_cuda_error(e, "brk_gemm_f16: clearing C for the split-k items");
+                    return BRK_CUDA_ERROR;
+                }
+            }
+            return dispatch_pair<true>(a_mn, b_mn, ta, tb, tc, p, st);
+        }
         std::memset(&tc, 0, sizeof(tc));
         return dispatch_pair<false>(a_mn, b_mn, ta, tb, tc, p, st);
     }

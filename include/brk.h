@@ -228,6 +228,11 @@ BRK_API void brk_gemm_f16_set_mode(int mode);
  * tiled stores (TMA tiled reductions when accumulate != 0, so C is never read by the SMs: the sum
  * C + fp16(acc) is then rounded to fp16 at the memory side); 1 = always the register epilogue. */
 BRK_API void brk_gemm_f16_set_epilogue(int mode);
+/* Split-k of the CTA-pair kernel, for measurements: 0 (default) = where the pair tiles do not fill the last wave
+ * of CTA pairs (e.g. 128 tiles on 74 pairs) and k is long, each tile's k range is cut into 2..4 work items that add
+ * their partial products into C through the TMA reduction (C is cleared first unless accumulate != 0; partial
+ * products are rounded to fp16 before they are added); 1 = never. */
+BRK_API void brk_gemm_f16_set_split_k(int mode);
 
 /* ---- fused attention (fp16, tcgen05) ------------------------------------------------------------
  * Replaces the op_qk -> op_add(alibi) -> op_add(xmask) -> op_softmax -> op_attn chain of layer_forward

@@ -141,6 +141,23 @@ def test_model_shape_against_numpy(ops):
     run(ops, 2048, 4096, 4096, 0, 1, 11, bias=True)
 
 
+def test_split_k_items(ops):
+    """Few pair tiles and a long k: each tile's k range is cut into several work items that add their partial products
+    into C through the TMA reduction (C cleared first; the bias rides on one item; accumulate keeps the old C).  Tails in
+    both directions, every storage order, and the same calls with the splitting switched off."""
+    from blackriver_b200 import brk
+    for off in (0, 1):
+        brk.lib().brk_gemm_f16_set_split_k(off)
+        try:
+            run(ops, 520, 328, 8192, 0, 1, 41, bias=True, mode=2)
+            run(ops, 520, 328, 8192, 0, 0, 42, mode=2)
+            run(ops, 520, 328, 6208, 1, 0, 43, acc=True, mode=2)
+            run(ops, 304, 264, 8192, 1, 1, 44, bias=True, acc=True, mode=2)
+            run(ops, 2048, 4096, 12288, 0, 0, 45)        # the QKV input gradient of one micro-batch: 128 tiles, 4 items each
+        finally:
+            brk.lib().brk_gemm_f16_set_split_k(0)
+
+
 def test_rejects_unsupported_layout(ops):
     from blackriver_b200 import brk
     a = torch.zeros(64, device="cuda", dtype=torch.float16)
