@@ -69,6 +69,7 @@ SIGNATURES = {
     "brk_gemm_f16_set_mode": (None, [i32]),
     "brk_gemm_f16_set_epilogue": (None, [i32]),
     "brk_gemm_f16_set_split_k": (None, [i32]),
+    "brk_gemm_f16_split_items": (i32, [i32, i32, i32]),
     "brk_flash_attn_fwd": (i32, [p, p, p, i64, p, i64, p, p, p, i32, i32, i32, i32, p]),
     "brk_flash_attn_bwd_workspace_bytes": (sz, [i32, i32, i32]),
     "brk_flash_attn_bwd": (i32, [p, p, p, i64, p, p, i64, p, p, p, p, i64, p, p, i32, i32, i32, i32, p, sz, p]),

@@ -638,6 +638,10 @@ static int choose_splits(int tiles, int pairs, int kblocks) {
 extern "C" void brk_gemm_f16_set_mode(int mode) { brk::g_tc_mode = mode; }
 extern "C" void brk_gemm_f16_set_epilogue(int mode) { brk::g_tc_epilogue = mode; }
 extern "C" void brk_gemm_f16_set_split_k(int mode) { brk::g_tc_split_k = mode; }
+extern "C" int brk_gemm_f16_split_items(int tiles, int pairs, int kblocks) {
+    if (tiles <= 0 || pairs <= 0 || kblocks <= 0) return 1;
+    return brk::choose_splits(tiles, pairs, kblocks);
+}
 
 extern "C" int brk_gemm_f16_supported(int64_t m, int64_t n, int64_t k, int trans_a, int trans_b, int64_t lda, int64_t ldb,
                                       const void* a, const void* b) {

@@ -233,6 +233,9 @@ BRK_API void brk_gemm_f16_set_epilogue(int mode);
  * their partial products into C through the TMA reduction (C is cleared first unless accumulate != 0; partial
  * products are rounded to fp16 before they are added); 1 = never. */
 BRK_API void brk_gemm_f16_set_split_k(int mode);
+/* The rule behind it, as a pure function (no device needed): work items per tile for `tiles` pair tiles on `pairs`
+ * CTA pairs with `kblocks` 64-wide k-blocks per tile. */
+BRK_API int brk_gemm_f16_split_items(int tiles, int pairs, int kblocks);
 
 /* ---- fused attention (fp16, tcgen05) ------------------------------------------------------------
  * Replaces the op_qk -> op_add(alibi) -> op_add(xmask) -> op_softmax -> op_attn chain of layer_forward

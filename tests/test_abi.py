@@ -64,3 +64,16 @@ def test_alibi_slopes_host_helper_matches_oracle():
         sl = (C.c_double * heads)()
         brk.lib().brk_alibi_slopes(heads, sl)
         assert np.array(list(sl)).tobytes() == orc.alibi_slopes(heads).tobytes()
+
+
+def test_split_k_rule_without_gpu():
+    """Work items per tile of the CTA-pair GEMM: 128 tiles on 74 CTA pairs leave the second wave 73 % full, four items
+    per tile fill 6.9 waves; never fewer than 32 k-blocks per item, and nothing to gain when the waves are full."""
+    from blackriver_b200 import brk
+    f = brk.lib().brk_gemm_f16_split_items
+    assert f(128, 74, 192) == 4 and f(128, 74, 256) == 4 and f(128, 74, 3920) == 4      # dX of QKV, of h->4h, of the LM head
+    assert f(128, 74, 64) == 1                       # k = 4096: two items would leave the fill unchanged, more are too short
+    assert f(256, 74, 32) == 1                       # weight gradients: k = 2048 tokens is too short to cut
+    assert f(512, 74, 64) == 1 and f(7840, 74, 64) == 1
+    assert f(4, 74, 128) == 3                        # a handful of tiles with a long k
+    assert f(0, 74, 64) == 1 and f(128, 0, 64) == 1 and f(128, 74, 0) == 1
