@@ -956,6 +956,15 @@ def run_case(args):
         c = torch.empty(m, n, device=dev).half()
         for _ in range(reps * 2):
             ops.gemm_f16(a, b, c, m, n, k, 0, 1, k, k, n)
+    elif args.case == "gemm_dx":
+        # input gradient of the h -> 4h projection for one micro-batch: dX [2048, 4096] = dy [2048, 16384] x W [16384, 4096];
+        # 128 pair tiles, each cut into 4 split-k items
+        m, n, k = 2048, 4096, 16384
+        a = torch.randn(m, k, generator=g, device=dev).half()
+        b = torch.randn(k, n, generator=g, device=dev).half()
+        c = torch.empty(m, n, device=dev).half()
+        for _ in range(reps * 2):
+            ops.gemm_f16(a, b, c, m, n, k, 0, 0, k, n, n)
     elif args.case == "gemm_dw":
         # weight gradient of the h -> 4h projection for one micro-batch: W_g [16384, 4096] += dy^T [16384, 2048] x [2048, 4096]
         m, n, k = 16384, 4096, 2048
@@ -1135,7 +1144,7 @@ def main():
     ap.add_argument("--no-overlap", action="store_true",
                     help="multi-GPU: the plain schedule (all forwards, all backwards, NCCL hand-offs) instead of the overlapped one")
     ap.add_argument("--skip-ops", action="store_true", help="do not run the operator microbench before the fine-tune step")
-    ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "gemm_dw", "attn", "gemm_shapes", "attn_shapes", "hbm_shapes"],
+    ap.add_argument("--case", default=None, choices=["nll", "ln", "gelu", "gemm", "gemm_dx", "gemm_dw", "attn", "gemm_shapes", "attn_shapes", "hbm_shapes"],
                     help="profiling aid: run a few launches of one kernel family on a small case and exit")
     ap.add_argument("--rows", type=int, default=1024, help="rows of the --case run")
     args = ap.parse_args()
