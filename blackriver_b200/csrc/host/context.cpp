@@ -22,6 +22,9 @@ cudaStream_t ComputingContext::comm_stream = nullptr;
 cudaStream_t ComputingContext::link_stream[2] = {nullptr, nullptr};
 cudaEvent_t ComputingContext::compute_done = nullptr;
 cudaEvent_t ComputingContext::comm_done = nullptr;
+cudaStream_t ComputingContext::main_stream = nullptr;
+std::vector<cudaEvent_t> ComputingContext::marks;
+std::vector<char> ComputingContext::mark_set;
 void* ComputingContext::cuda_workspace = nullptr;
 void* ComputingContext::local_workspace = nullptr;
 size_t ComputingContext::workspace_size = 0;
@@ -77,6 +80,13 @@ void ComputingContext::shutdown() {
     }
     cudaFree(cuda_workspace);
     cudaFreeHost(local_workspace);
+    if (main_stream) {      // left in side mode by an interrupted script
+        cuda_stream = main_stream;
+        main_stream = nullptr;
+    }
+    for (cudaEvent_t e : marks) cudaEventDestroy(e);
+    marks.clear();
+    mark_set.clear();
     cudaEventDestroy(compute_done);
     cudaEventDestroy(comm_done);
     cudaStreamDestroy(comm_stream);
@@ -131,7 +141,10 @@ void Profiler::end() {
 
 std::string Profiler::report_json() {
     enabled = false;
-    if (ComputingContext::booted) BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::cuda_stream));
+    if (ComputingContext::booted) {
+        BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::cuda_stream));
+        BR_CUDA_CHECK(cudaStreamSynchronize(ComputingContext::comm_stream));      // operators queued in side mode
+    }
     std::map<std::string, std::pair<double, long>> agg;
     for (auto& r : g_prof) {
         float ms = 0.0f;

@@ -15,6 +15,8 @@
 #include <cstddef>
 #include <string>
 
+#include <vector>
+
 #include "common.hpp"
 
 namespace br {
@@ -26,6 +28,12 @@ struct ComputingContext {
     static cudaStream_t link_stream[2];   // stage hand-offs of PipeLinks: [0] towards the previous rank, [1] towards the next
     static cudaEvent_t compute_done;   // recorded on cuda_stream before a send reads a tensor
     static cudaEvent_t comm_done;      // recorded on comm_stream after a recv wrote a tensor
+    // Side mode (op.stream.side): cuda_stream is temporarily the transfer stream, so that every operator queued
+    // meanwhile (the optimizer) runs beside what the compute stream is given next; main_stream then holds the compute
+    // stream (nullptr outside side mode).  marks[i] are events recorded by op.event.record for op.event.wait.
+    static cudaStream_t main_stream;
+    static std::vector<cudaEvent_t> marks;
+    static std::vector<char> mark_set;
 
     static void* cuda_workspace;       // device scratch handed to kernels that need it
     static void* local_workspace;      // pinned host scratch of the same size

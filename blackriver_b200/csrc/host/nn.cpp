@@ -329,6 +329,49 @@ BR_WORD(StreamJoin, {
     ComputingContext::nccl_on_comm_stream = 0;
 })
 
+// ( flag -- )  1: from here on every operator (and io.nccl.* word) queues on the transfer stream, which first waits for
+// what the compute stream has been given so far; 0: back to the compute stream, which does NOT wait for the side work --
+// whoever needs a result of it waits for an event recorded there (op.event.record / op.event.wait) or joins
+// (op.stream.join).  Used to run the optimizer beside the next step's first forward.
+BR_WORD(StreamSide, {
+    const bool on = stack.pop_number() != 0.0;
+    if (!ComputingContext::booted) return;
+    if (on) {
+        br_assert(ComputingContext::main_stream == nullptr, "op.stream.side: already on the side stream");
+        BR_CUDA_CHECK(cudaEventRecord(ComputingContext::compute_done, ComputingContext::cuda_stream));
+        BR_CUDA_CHECK(cudaStreamWaitEvent(ComputingContext::comm_stream, ComputingContext::compute_done, 0));
+        ComputingContext::main_stream = ComputingContext::cuda_stream;
+        ComputingContext::cuda_stream = ComputingContext::comm_stream;
+    } else {
+        br_assert(ComputingContext::main_stream != nullptr, "op.stream.side: not on the side stream");
+        ComputingContext::cuda_stream = ComputingContext::main_stream;
+        ComputingContext::main_stream = nullptr;
+    }
+})
+// ( id -- )  marks the present position of the stream operators are queued on
+BR_WORD(EventRecord, {
+    const int id = (int)stack.pop_number();
+    br_assert(id >= 0 && id < 4096, "op.event.record: id out of range");
+    if (!ComputingContext::booted) return;
+    auto& marks = ComputingContext::marks;
+    while ((int)marks.size() <= id) {
+        cudaEvent_t e;
+        BR_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        marks.push_back(e);
+        ComputingContext::mark_set.push_back(0);
+    }
+    BR_CUDA_CHECK(cudaEventRecord(marks[id], ComputingContext::cuda_stream));
+    ComputingContext::mark_set[id] = 1;
+})
+// ( id -- )  the compute stream waits for mark id (nothing to wait for if it was never recorded)
+BR_WORD(EventWait, {
+    const int id = (int)stack.pop_number();
+    if (id >= 0 && id < (int)ComputingContext::marks.size() && ComputingContext::mark_set[id]) {
+        cudaStream_t compute = ComputingContext::main_stream ? ComputingContext::main_stream : ComputingContext::cuda_stream;
+        BR_CUDA_CHECK(cudaStreamWaitEvent(compute, ComputingContext::marks[id], 0));
+    }
+})
+
 // ---- one-sided stage hand-offs (PipeLinks) ----
 // ( bytes_per_slot slots -- )  collective over all ranks
 BR_WORD(LinkOpen, {
@@ -461,6 +504,9 @@ void load_nn_words(Enviroment& env) {
     env.insert_native_word("op.kernel_status", KernelStatus::creator);
     env.insert_native_word("op.stream.fork", StreamFork::creator);
     env.insert_native_word("op.stream.join", StreamJoin::creator);
+    env.insert_native_word("op.stream.side", StreamSide::creator);
+    env.insert_native_word("op.event.record", EventRecord::creator);
+    env.insert_native_word("op.event.wait", EventWait::creator);
     env.insert_native_word("io.link.open", LinkOpen::creator);
     env.insert_native_word("io.link.close", LinkClose::creator);
     env.insert_native_word("io.link.emulate", LinkEmulate::creator);

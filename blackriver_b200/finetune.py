@@ -75,7 +75,8 @@ class Trainer:
 
     def __init__(self, hidden, heads, vocab, n_layers, batch, tokens, n_micro, rank=0, world=1, dtype="half", seed=0,
                  loss_scale=1024.0, lr=1e-4, logits_rows=None, init_std=0.02, verbose=False, head_cost=LM_HEAD_COST_IN_LAYERS,
-                 overlap=None, n_slots=None, activation_budget=56 << 30, play_all_ranks=False, split_layers=True, replicas=1):
+                 overlap=None, n_slots=None, activation_budget=56 << 30, play_all_ranks=False, split_layers=True, replicas=1,
+                 async_optimizer=False):
         # data-parallel replicas: the job's ranks form `replicas` pipelines of world / replicas stages; each replica
         # takes every replicas-th micro-batch of a step and the gradients are summed over the replicas before Adam.
         # From here on rank / world / n_micro describe this rank's pipeline and its share of the micro-batches.
@@ -127,7 +128,11 @@ class Trainer:
         # play_all_ranks: this single-rank process holds the Trainers of every rank of the pipeline (a test on one GPU
         # that interleaves their task lists itself); the links then keep one block per played rank
         self.played = bool(play_all_ranks) and self.overlap
-        self.env.execute(words.fused_words(overlap=self.overlap, **kw))
+        # async_optimizer: Adam (and the tied-table exchange) are queued on the transfer stream and the next step's first
+        # forward waits, layer by layer, for the parameters it reads, so the update runs beside that forward
+        self.async_optimizer = bool(async_optimizer)
+        self._grads_clean = True          # zero_grads ran at initialisation; the asynchronous optimizer clears them itself
+        self.env.execute(words.fused_words(overlap=self.overlap, async_optimizer=self.async_optimizer, **kw))
         if self.played:
             self.env.execute(f"{world} io.link.emulate {rank} io.link.rank")
         self.env.execute("build_model init_model zero_grads")
@@ -168,6 +173,7 @@ class Trainer:
                 else:
                     self.tasks.append((prog(f"slot_{slot} stage_w"), None))
         self.p_begin = prog("zero_grads 1 op.accumulate")
+        self.p_begin_clean = prog("1 op.accumulate")
         self.p_sync = prog("op.sync")
         self.p_status = prog("op.kernel_status")
         self.p_score = None          # built on first use
@@ -197,7 +203,8 @@ class Trainer:
             microbatches = replica_share(microbatches, self.replica, self.replicas)
         assert len(microbatches) == self.n_micro
         self._packed = [pack_inputs(mb) for mb in microbatches]
-        self.env.run(self.p_begin)
+        self.env.run(self.p_begin_clean if (self.async_optimizer and self._grads_clean) else self.p_begin)
+        self._grads_clean = False
 
     def run_task(self, i):
         """Queues task i of this rank's list (step() runs them all in order; a test that emulates several ranks in one
@@ -231,7 +238,13 @@ class Trainer:
         # gradients were summed over micro-batches and carry the loss scale: Adam divides both out
         gs = 1.0 / (self.loss_scale * self.total_micro)
         args = f"{self.lr} {self.step_no} {gs}"
-        if tied_peer is None:
+        if self.async_optimizer:
+            if tied_peer is None:
+                self.env.execute(f"0 op.accumulate {args} optimizer_async")
+            else:
+                self.env.execute(f"0 op.accumulate {tied_peer} {args} optimizer_async_tied")
+            self._grads_clean = True
+        elif tied_peer is None:
             self.env.execute(f"0 op.accumulate {args} optimizer_step")
         else:
             self.env.execute(f"0 op.accumulate {tied_peer} sync_tied_start {args} optimizer_layers sync_tied_finish {args} optimizer_main")
@@ -287,6 +300,11 @@ class Trainer:
 
     def sync(self):
         self.env.run(self.p_sync)
+
+    def drain(self):
+        """Makes the compute stream wait for what is queued on the transfer stream (an asynchronous optimizer step), so
+        that an event recorded on the compute stream afterwards covers it.  Does not block the host."""
+        self.env.execute("op.stream.join")
 
     def close(self):
         # the training switches live in the process-wide computing context: hand them back at their defaults

@@ -254,7 +254,7 @@ HALF_STATS = {"A": ("input_ln_var",), "M": ("post_ln_var",)}
 
 def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps=1e-5, first_stage=True, last_stage=True,
                 logits_rows=None, init_std=0.02, seed=0, layer_offset=0, n_slots=1, prev_rank=None, next_rank=None,
-                overlap=False, n_micro=1, kinds=None):
+                overlap=False, n_micro=1, kinds=None, async_optimizer=False):
     """Script text defining the whole stage.  After executing it:
          build_model            allocates everything (call once)
          init_model             seeded random initialisation (weights N(0, init_std), biases 0, LN 1/0)
@@ -594,13 +594,21 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
 
     w("%def model_forward")
     w("    0 #")
+    # with the optimizer on the side stream (optimizer_async) every group of parameters is waited for where it is first
+    # read: mark 0 = the stage-level parameters, mark i = layer i
     if first_stage:
+        if async_optimizer:
+            w("    0 op.event.wait")
         w(f'    {g("ids_", "word_embeddings.weight", "emb_raw")} op.embed')
         w(f'    {g("emb_raw", "ln_mean", "emb_ln_var", "word_embeddings_layernorm.weight", "word_embeddings_layernorm.bias", "emb_out", "LN_EPS")} op.layernorm')
     for i in range(1, n_layers + 1):
+        if async_optimizer:
+            w(f"    {i} op.event.wait")
         w(f"    {i} # layer_forward_{tag_of(i)}")
     w("    0 #")
     if last_stage:
+        if async_optimizer and not first_stage:
+            w("    0 op.event.wait")
         w(f'    {g("stage_out", "ln_mean", "ln_f_var", "ln_f.weight", "ln_f.bias", "xf", "LN_EPS")} op.layernorm')
     w("%end")
 
@@ -662,6 +670,43 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
     w('    "all_lr_" @ "all_step_" @ "all_gs_" @ optimizer_main  0 # "all_lr_" @ "all_step_" @ "all_gs_" @ optimizer_layers')
     w('    0 #  "all_gs_" !! "all_step_" !! "all_lr_" !!')
     w("%end")
+
+    if async_optimizer:
+        # ( lr step grad_scale -- ) / ( peer lr step grad_scale -- )  the same update queued on the transfer stream, so that
+        # it runs beside the next step's first forward: every group of parameters is followed by the clearing of its
+        # gradients and by a mark that the forward waits for (model_forward), and the groups come in the order in which
+        # the forward reads them -- the stage-level parameters first on the stage that embeds, last on the others.
+        # The tied-table exchange, where there is one, is queued first so that the peer is not kept waiting.
+        def main_group():
+            for name, _ in main_params:
+                w(f'    {g(name, name + "_g", name + ".master", name + ".m", name + ".v")} {adam}  "{name}_g" @ op.zero')
+            w("    0 op.event.record")
+
+        def layer_groups():
+            for i in range(1, n_layers + 1):
+                w(f'    0 # "lr_" @ "step_" @ "gs_" @  {i} # "gs_" ! "step_" ! "lr_" !  {g("_flat", "_flat_g", "_flat.master", "_flat.m", "_flat.v")} {adam}  "_flat_g" @ op.zero  "gs_" !! "step_" !! "lr_" !!  {i} op.event.record')
+            w("    0 #")
+
+        for tied in (False, True):
+            w("%def optimizer_async_tied" if tied else "%def optimizer_async")
+            w('    0 #  "gs_" ! "step_" ! "lr_" !' + ('  "peer_" !' if tied else ""))
+            w("    1 op.stream.side")
+            if tied:
+                w('    "word_embeddings.weight_g" @ "tied_recv" @ "peer_" @ io.nccl.sendrecv')
+            add_tied = '    "word_embeddings.weight_g" @ "tied_recv" @ "word_embeddings.weight_g" @ op.add'
+            if first_stage:
+                if tied:
+                    w(add_tied)
+                main_group()
+                layer_groups()
+            else:
+                layer_groups()
+                if tied:
+                    w(add_tied)
+                main_group()
+            w("    0 op.stream.side")
+            w('    0 #  "gs_" !! "step_" !! "lr_" !!' + ('  "peer_" !!' if tied else ""))
+            w("%end")
 
     if overlap:
         # ---- the three tasks of the overlapped schedule (each runs after slot_k) ----

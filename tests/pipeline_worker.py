@@ -48,10 +48,11 @@ def main():
             env.execute(words.fused_words(hidden=CFG["hidden"], heads=CFG["heads"], vocab=CFG["vocab"], n_layers=counts[rank],
                                           batch=CFG["batch"], tokens=CFG["tokens"], first_stage=first, last_stage=last,
                                           n_slots=CFG["n_micro"], n_micro=CFG["n_micro"], prev_rank=None if first else rank - 1,
-                                          next_rank=None if last else rank + 1, layer_offset=sum(counts[:rank]), overlap=overlap))
+                                          next_rank=None if last else rank + 1, layer_offset=sum(counts[:rank]), overlap=overlap,
+                                          async_optimizer=True))
             text = ('slot_1 stage_f slot_1 "loss@1" stage_b slot_1 stage_w' if overlap else
                     'slot_1 stage_forward slot_1 stage_backward slot_1 "loss@1" stage_backward_async')
-            prog = env.build(text + " sync_replicas")     # links every word of the stage
+            prog = env.build(text + " sync_replicas 1e-3 1 1.0 optimizer_async 0 1e-3 1 1.0 optimizer_async_tied")     # links every word of the stage
             env.free_program(prog)
             env.close()
         dist.barrier()
@@ -72,7 +73,8 @@ def main():
     stages = world // replicas
     tr = finetune.Trainer(CFG["hidden"], CFG["heads"], CFG["vocab"], CFG["n_layers"], CFG["batch"], CFG["tokens"], CFG["n_micro"],
                           rank=rank, world=world, seed=9, lr=1e-3, init_std=0.05, head_cost=head_cost,
-                          overlap=os.environ.get("BR_TEST_OVERLAP", "1") != "0", replicas=replicas)
+                          overlap=os.environ.get("BR_TEST_OVERLAP", "1") != "0", replicas=replicas,
+                          async_optimizer=os.environ.get("BR_TEST_ASYNC_OPT", "0") == "1")
     # forward-only scoring through the same stages (the prefill path) with the initial weights: per-token NLL from the
     # rank that holds the head
     scored = tr.score(mbs[:2]) if replicas == 1 else []

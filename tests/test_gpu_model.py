@@ -334,6 +334,33 @@ def test_checkpoint_resume_continues_the_same_run(host, tmp_path):
     assert np.abs(ta.astype(np.float32) - tb.astype(np.float32)).max() <= 2.5e-3
 
 
+def test_async_optimizer_matches_the_blocking_one(host):
+    """Adam queued on the transfer stream, with the next step's forward waiting layer by layer for the parameters it
+    reads and the gradients cleared behind each update, must give the run of the optimizer on the compute stream."""
+    from blackriver_b200 import finetune
+    H, heads, V, L, B, T, M = 128, 2, 512, 3, 2, 64, 3
+    mbs = finetune.make_microbatches(M, B, T, V, 20, seed=4)
+    runs = []
+    for flag in (False, True):
+        tr = finetune.Trainer(H, heads, V, L, B, T, n_micro=M, seed=23, init_std=0.05, lr=1e-3, async_optimizer=flag)
+        try:
+            losses = [tr.step(mbs) for _ in range(4)]
+            scored = tr.score(mbs[:1])[0][1]          # a forward right behind the last asynchronous update
+            tr.sync()
+            tr.env.change(3); w = tr.env.read("_flat.master").copy(); g = tr.env.read("_flat_g").copy()
+            tr.env.change(0); t = tr.env.read("word_embeddings.weight.master").copy()
+            runs.append((losses, scored, w, g, t))
+        finally:
+            tr.close()
+    (la, sa, wa, ga, ta), (lb, sb, wb, gb, tb) = runs
+    for a, b in zip(la, lb):
+        assert abs(a - b) <= 1e-4 * abs(a)
+    assert abs(sa - sb) <= 1e-4 * abs(sa)
+    assert np.abs(wa - wb).max() <= 2.5e-3 and np.median(np.abs(wa - wb)) <= 1e-6
+    assert np.abs(ta - tb).max() <= 2.5e-3
+    assert not gb.any()                               # the asynchronous update leaves the gradients cleared
+
+
 def test_adam_skips_non_finite_gradients():
     """An overflowed fp16 gradient (inf under the loss scale) must not poison the weight or the moments."""
     from blackriver_b200 import brk, ops

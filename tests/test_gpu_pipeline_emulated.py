@@ -63,16 +63,17 @@ def train_single(host, mbs, n_micro, steps):
     return losses, w, table
 
 
-@pytest.mark.parametrize("world,head_cost,n_micro,n_slots,split", [(2, 0.5, 4, 4, True), (3, 2.5, 6, 3, True), (4, 0.5, 5, 2, True),
-                                                                      (3, 0.2, 4, 4, True), (2, 0.5, 4, 2, False)])
-def test_emulated_ranks_match_single_stage(host, world, head_cost, n_micro, n_slots, split):
+@pytest.mark.parametrize("world,head_cost,n_micro,n_slots,split,async_opt",
+                         [(2, 0.5, 4, 4, True, False), (3, 2.5, 6, 3, True, False), (4, 0.5, 5, 2, True, False),
+                          (3, 0.2, 4, 4, True, False), (2, 0.5, 4, 2, False, False), (3, 2.5, 6, 3, True, True), (4, 0.5, 5, 2, True, True)])
+def test_emulated_ranks_match_single_stage(host, world, head_cost, n_micro, n_slots, split, async_opt):
     from blackriver_b200 import finetune
     mbs = finetune.make_microbatches(n_micro, CFG["batch"], CFG["tokens"], CFG["vocab"], 20, seed=5)
     ref_losses, ref_w, ref_table = train_single(host, mbs, n_micro, steps=2)
 
     trs = [finetune.Trainer(CFG["hidden"], CFG["heads"], CFG["vocab"], CFG["n_layers"], CFG["batch"], CFG["tokens"], n_micro,
                             rank=r, world=world, seed=9, lr=1e-3, init_std=0.05, head_cost=head_cost, n_slots=n_slots,
-                            play_all_ranks=True, split_layers=split)
+                            play_all_ranks=True, split_layers=split, async_optimizer=async_opt)
            for r in range(world)]
     try:
         assert all(t.overlap and t.n_slots == n_slots for t in trs)

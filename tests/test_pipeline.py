@@ -11,11 +11,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "pipeline_worker.py")
 
 
-def launch(world, backend, out_path, port, head_cost=0.5, overlap=True, replicas=1):
+def launch(world, backend, out_path, port, head_cost=0.5, overlap=True, replicas=1, async_opt=False):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), WORKER, backend, out_path]
     env = dict(os.environ, OMP_NUM_THREADS="2", BR_TEST_HEAD_COST=str(head_cost), BR_TEST_OVERLAP="1" if overlap else "0",
-               BR_TEST_REPLICAS=str(replicas))
+               BR_TEST_REPLICAS=str(replicas), BR_TEST_ASYNC_OPT="1" if async_opt else "0")
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return json.load(open(out_path))
@@ -85,6 +85,17 @@ def test_replica_layout_and_shares():
     mbs = list(range(16))
     shares = [replica_share(mbs, r, 4) for r in range(4)]
     assert sorted(sum(shares, [])) == mbs and all(len(x) == 4 for x in shares) and shares[1] == [1, 5, 9, 13]
+
+
+@pytest.mark.gpu
+def test_two_stage_pipeline_with_the_optimizer_on_the_transfer_stream(tmp_path):
+    """Adam and the tied-table exchange queued on the transfer stream beside the next step's first forward."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    res = launch(2, "nccl", str(tmp_path / "out.json"), 29545, async_opt=True)
+    assert res["overlap"]
+    check_against_single(res)
 
 
 @pytest.mark.gpu
