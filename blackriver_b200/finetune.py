@@ -76,7 +76,7 @@ class Trainer:
     def __init__(self, hidden, heads, vocab, n_layers, batch, tokens, n_micro, rank=0, world=1, dtype="half", seed=0,
                  loss_scale=1024.0, lr=1e-4, logits_rows=None, init_std=0.02, verbose=False, head_cost=LM_HEAD_COST_IN_LAYERS,
                  overlap=None, n_slots=None, activation_budget=56 << 30, play_all_ranks=False, split_layers=True, replicas=1,
-                 async_optimizer=False):
+                 async_optimizer=False, early_exchange=True):
         # data-parallel replicas: the job's ranks form `replicas` pipelines of world / replicas stages; each replica
         # takes every replicas-th micro-batch of a step and the gradients are summed over the replicas before Adam.
         # From here on rank / world / n_micro describe this rank's pipeline and its share of the micro-batches.
@@ -99,8 +99,13 @@ class Trainer:
         # stage boundaries in half-layer units (2 per layer); the plain schedule keeps whole layers
         unit = sum(schedule.LAYER_COST) * head_cost / sum(schedule.HEAD_COST)
         head = tuple(c * unit for c in schedule.HEAD_COST)
+        # the early exchange of the tied table's gradient (see below) lets a rank's deferred weight-gradient tasks run in
+        # the time it would otherwise wait for the next step's first micro-batch, so the partition is then chosen for
+        # the steady-state step time of consecutive steps; every rank derives the same answer from the same arguments
+        self.early_exchange = False
+        steady = self.overlap and bool(early_exchange) and self.replicas == 1 and not async_optimizer and not play_all_ranks
         self.bounds = schedule.choose_partition_units(n_layers, world, n_micro, head_cost=head,
-                                                      whole_layers=not (self.overlap and split_layers))
+                                                      whole_layers=not (self.overlap and split_layers), steady=steady)
         self.counts = [(self.bounds[r + 1] - self.bounds[r]) / 2 for r in range(world)]      # layers per stage, halves count 0.5
         u0, u1 = self.bounds[rank], self.bounds[rank + 1]
         first_layer = u0 // 2
@@ -164,12 +169,24 @@ class Trainer:
             schedule.check(orders, n_micro, S)          # raises on a dependency or slot conflict before anything is queued
             self.order = orders[rank]
             self.simulated_efficiency = schedule.efficiency(self.simulated_step, costs, n_micro)
+            # the last rank takes the LM-head part of its weight-gradient tasks first and starts the exchange of the tied
+            # table's gradient before the layers' parts (schedule.expand_last_rank): the first rank, whose next step
+            # needs the updated table, then does not wait for this rank's deferred work
+            self.early_exchange = steady and self.last and not self.first
+            if self.early_exchange:
+                self.order = schedule.expand_last_rank(self.order)
             for t in self.order:
                 slot = t.k % S
                 if t.kind == "F":
                     self.tasks.append((prog(f"slot_{slot} stage_f"), t.k))
                 elif t.kind == "B":
                     self.tasks.append((prog(f'slot_{slot} "loss@{t.k}" stage_b'), t.k))
+                elif t.kind == "H":
+                    self.tasks.append((prog(f"slot_{slot} stage_h"), None))
+                elif t.kind == "X":
+                    self.tasks.append((prog("0 sync_tied_start"), None))
+                elif self.early_exchange:
+                    self.tasks.append((prog(f"slot_{slot} stage_wl"), None))
                 else:
                     self.tasks.append((prog(f"slot_{slot} stage_w"), None))
         self.p_begin = prog("zero_grads 1 op.accumulate")
@@ -244,6 +261,9 @@ class Trainer:
             else:
                 self.env.execute(f"0 op.accumulate {tied_peer} {args} optimizer_async_tied")
             self._grads_clean = True
+        elif tied_peer is not None and self.early_exchange:
+            # the exchange was started from the task list (X): wait for it, add, update
+            self.env.execute(f"0 op.accumulate {args} optimizer_layers sync_tied_finish {args} optimizer_main")
         elif tied_peer is None:
             self.env.execute(f"0 op.accumulate {args} optimizer_step")
         else:

@@ -174,6 +174,109 @@ def check(orders, n_micro, n_slots, costs=None, link_latency=0.02):
     return max(free_at) if costs else None
 
 
+# ---- consecutive steps -------------------------------------------------------------------------------------------------
+# A rank starts the next step as soon as its own list and its own optimizer step are done; there is no barrier between
+# steps.  A later rank therefore spends the time in which it would wait for the next step's first micro-batch on the
+# weight-gradient tasks it still has left over, so in the steady state the pipeline's fill costs nothing as long as every
+# rank has at least that much deferred work, and the step time tends to the largest per-rank work instead of work + fill.
+# The one coupling between the two ends is the tied table: the first rank's update of it needs the last rank's LM-head
+# gradient.  The last rank therefore takes the head's part of its deferred weight-gradient tasks first ("H"), starts the
+# exchange ("X") and only then works off the layers' parts ("W").
+ADAM_LAYER_COST = 1.0        # ms per decoder layer per step (28 bytes per parameter at HBM speed)
+ADAM_TABLE_COST = 3.0        # the 250880 x 4096 table
+TIED_EXCHANGE_COST = 3.0     # 2 GB each way over NVLink
+
+
+def expand_last_rank(order):
+    """The last rank's list with every W(k) cut into H(k) (LM-head weight gradient) and W(k) (its layers): pairs stay
+    together up to the last B; what is left after it runs heads first, then the exchange marker X, then the layers."""
+    last_b = max((i for i, t in enumerate(order) if t.kind == "B"), default=-1)
+    out = []
+    for t in order[:last_b + 1]:
+        if t.kind == "W":
+            out.append(Task("H", t.k))
+        out.append(t)
+    tail = [t for t in order[last_b + 1:]]
+    out += [Task("H", t.k) for t in tail if t.kind == "W"]
+    out.append(Task("X", -1))
+    out += tail
+    return out
+
+
+def steady_period(orders, costs, n_micro, n_slots, head_w=None, layers=None, link_latency=0.02, steps=3):
+    """Step time in the steady state: `steps` consecutive steps are replayed, every rank running its list in order and
+    then its optimizer step (layers' Adam; the holders of the tied table exchange its gradient once both have it and
+    update it last), and the time between the ends of the last two steps is returned.
+    head_w = the LM-head part of the last rank's W cost; layers[r] = decoder layers on rank r (for Adam's cost)."""
+    world = len(orders)
+    n_slots = max(1, min(n_slots, n_micro))
+    head_w = HEAD_COST[2] if head_w is None else head_w
+    layers = layers or [0.0] * world
+    lists = [list(o) for o in orders]
+    if world > 1:
+        lists[-1] = expand_last_rank(orders[-1])
+    dur = {"F": 0, "B": 1, "W": 2}
+
+    def cost(r, t):
+        if t.kind == "X":
+            return 0.0
+        if t.kind == "H":
+            return min(head_w, costs[r][2])
+        c = costs[r][dur[t.kind]]
+        if t.kind == "W" and world > 1 and r == world - 1:
+            c = max(c - head_w, 0.0)
+        return c
+
+    free_at = [0.0] * world
+    ends = []
+    for _ in range(steps):
+        pos = [0] * world
+        done = {}
+        table_ready = [None, None]          # first rank: after its last B; last rank: at X
+        while any(pos[r] < len(lists[r]) for r in range(world)):
+            moved = False
+            for r in range(world):
+                while pos[r] < len(lists[r]):
+                    t = lists[r][pos[r]]
+                    when = 0.0
+                    ok = True
+                    deps = [] if t.kind in "HX" else _deps(world, n_slots, r, t)
+                    if t.kind == "H":
+                        deps = [(r, Task("B", t.k))]
+                    for (dr, dt) in deps:
+                        f = done.get((dr, dt))
+                        if f is None:
+                            ok = False
+                            break
+                        when = max(when, f + (link_latency if dr != r else 0.0))
+                    if not ok:
+                        break
+                    start = max(when, free_at[r])
+                    free_at[r] = start + cost(r, t)
+                    done[(r, t)] = free_at[r]
+                    if t.kind == "X":
+                        table_ready[1] = free_at[r]
+                    if r == 0 and t.kind == "B" and t.k == n_micro - 1:
+                        pass
+                    pos[r] += 1
+                    moved = True
+            if not moved:
+                raise ValueError("deadlock in the replay of consecutive steps")
+        last_b0 = max(done[(0, Task("B", k))] for k in range(n_micro))
+        table_ready[0] = last_b0
+        if world > 1:
+            exchanged = max(table_ready[0], table_ready[1]) + TIED_EXCHANGE_COST
+        for r in range(world):
+            t_end = free_at[r] + ADAM_LAYER_COST * layers[r]
+            if world > 1 and (r == 0 or r == world - 1):
+                t_end = max(t_end, exchanged) + ADAM_TABLE_COST
+            elif world == 1:
+                t_end += ADAM_TABLE_COST
+            free_at[r] = t_end
+        ends.append(max(free_at))
+    return ends[-1] - ends[-2] if steps > 1 else ends[-1]
+
+
 def efficiency(makespan, costs, n_micro):
     """Simulated step time of one rank doing all the work, divided by (ranks x the pipeline's step time)."""
     return n_micro * sum(sum(c) for c in costs) / (len(costs) * makespan)
@@ -244,7 +347,8 @@ def stage_costs_units(bounds, unit_cost=None, head_cost=HEAD_COST):
     return out
 
 
-def choose_partition_units(n_layers, world, n_micro, n_slots=None, unit_cost=None, head_cost=HEAD_COST, whole_layers=False):
+def choose_partition_units(n_layers, world, n_micro, n_slots=None, unit_cost=None, head_cost=HEAD_COST, whole_layers=False,
+                           steady=False):
     """Stage boundaries in units (2 per layer) with the shortest simulated step.  Candidates come from an exact search
     (dynamic programme over contiguous splits) for the split that minimises the largest of
     n_micro x (work of the stage) + alpha x (forward time of everything before it), for several alpha: the second term
@@ -299,7 +403,10 @@ def choose_partition_units(n_layers, world, n_micro, n_slots=None, unit_cost=Non
             continue
         seen.add(tuple(bounds))
         costs = stage_costs_units(bounds, unit_cost, head_cost)
-        _, span = build(world, n_micro, costs, n_slots)
+        orders, span = build(world, n_micro, costs, n_slots)
+        if steady:
+            span = steady_period(orders, costs, n_micro, n_slots if n_slots else n_micro, head_w=head_cost[2],
+                                 layers=[(bounds[r + 1] - bounds[r]) / 2 for r in range(world)])
         if best is None or span < best[0] - 1e-9:
             best = (span, bounds)
     if best is None:

@@ -746,6 +746,21 @@ def fused_words(hidden, heads, vocab, n_layers, batch, tokens, dtype="half", eps
             w('    "stage_in_g" @ 0 "slot_" @ io.link.send')
         w('    "loss_" !!')
         w("%end")
+        # the LM-head part of stage_w on its own (the tied table's gradient is complete once every micro-batch's has run,
+        # so a list may take these first and start the exchange of that gradient before the layers' parts: stage_wl)
+        w("%def stage_h")
+        w("    0 #")
+        if last_stage:
+            w(f'    {g("all_logits", "xf", "word_embeddings.weight_g")} op.loss_backward_w')
+        w("%end")
+        w("%def stage_wl")
+        w("    0 #")
+        for i in range(n_layers, 0, -1):
+            w(f"    {i} # layer_backward_w_{tag_of(i)}")
+        w("    0 #")
+        if next_rank is not None:
+            w('    1 "slot_" @ io.link.release')
+        w("%end")
         w("%def stage_w")
         w("    0 #")
         if last_stage:

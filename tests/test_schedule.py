@@ -65,3 +65,46 @@ def test_slot_count_follows_the_activation_budget():
     assert S.n_slots_for(8, 16, [5, 5, 4, 4, 4, 4, 4, 0], 23 * act) == 16
     assert 2 <= S.n_slots_for(2, 16, [18, 12], 23 * act) < 16
     assert S.n_slots_for(2, 16, [18, 12], 23 * act, budget_bytes=1) == 2
+
+
+def test_last_rank_takes_head_gradients_first_and_marks_the_exchange():
+    """The last rank's list with every W cut into the LM-head part H and the layers' part W: H(k) comes before W(k) and
+    after B(k), the exchange marker X comes after the last H and after the last B, and what follows X is only layers'
+    weight gradients (work that nothing but this rank's own optimizer waits for)."""
+    for world, n_micro, slots in ((2, 4, 4), (4, 16, 16), (8, 16, 16), (3, 6, 3)):
+        costs = S.stage_costs_units(S.choose_partition_units(12, world, n_micro, slots))
+        orders, _ = S.build(world, n_micro, costs, slots)
+        ex = S.expand_last_rank(orders[-1])
+        kinds = [t.kind for t in ex]
+        assert kinds.count("X") == 1 and kinds.count("H") == n_micro and kinds.count("W") == n_micro
+        x = kinds.index("X")
+        assert all(k == "W" for k in kinds[x + 1:])
+        pos = {(t.kind, t.k): i for i, t in enumerate(ex)}
+        for k in range(n_micro):
+            assert pos[("B", k)] < pos[("H", k)] < pos[("W", k)]
+            assert pos[("H", k)] < x and pos[("B", k)] < x
+        # without the cut the list is the original one
+        assert [t for t in ex if t.kind in "FBW"] == list(orders[-1])
+
+
+def test_steady_state_period():
+    """Consecutive steps without a barrier: the step time in the steady state is at least the largest per-rank work
+    plus that rank's optimizer, never more than an isolated step plus the slowest optimizer, and the partition chosen
+    for it is no worse, by that measure, than the one chosen for an isolated step."""
+    for world, slots in ((2, 8), (4, 16), (8, 16)):
+        n_micro = 16
+        res = {}
+        for steady in (False, True):
+            b = S.choose_partition_units(30, world, n_micro, slots, steady=steady)
+            costs = S.stage_costs_units(b)
+            layers = [(b[r + 1] - b[r]) / 2 for r in range(world)]
+            orders, span = S.build(world, n_micro, costs, slots)
+            period = S.steady_period(orders, costs, n_micro, slots, layers=layers)
+            work = max(n_micro * sum(c) + S.ADAM_LAYER_COST * l for c, l in zip(costs, layers))
+            assert work - 1e-6 <= period <= span + S.ADAM_LAYER_COST * max(layers) + S.ADAM_TABLE_COST + S.TIED_EXCHANGE_COST + 1e-6
+            res[steady] = period
+        assert res[True] <= res[False] + 1e-6
+    # one rank: the period is the work of the step plus the optimizer
+    costs = S.stage_costs_units([0, 60])
+    orders, span = S.build(1, 4, costs, 1)
+    assert abs(S.steady_period(orders, costs, 4, 1, layers=[30]) - (span + 30 * S.ADAM_LAYER_COST + S.ADAM_TABLE_COST)) < 1e-6
