@@ -438,7 +438,7 @@ def run_finetune(args):
     tr = finetune.Trainer(cfg["hidden"], cfg["heads"], cfg["vocab"], cfg["n_layers"], cfg["batch"], cfg["tokens"], cfg["n_micro"],
                           rank=rank, world=world, seed=cfg["seed"], logits_rows=cfg["batch"] * cfg["tokens"],
                           overlap=not args.no_overlap, replicas=args.replicas if world > 1 else 1,
-                          async_optimizer=args.async_optimizer)
+                          async_optimizer=args.async_optimizer, early_exchange=args.early_exchange)
     mbs = finetune.make_microbatches(cfg["n_micro"], cfg["batch"], cfg["tokens"], cfg["vocab"], cfg["min_len"], cfg["seed"])
     tokens_per_step = cfg["n_micro"] * cfg["batch"] * cfg["tokens"]
     valid_per_step = int(sum(int(m[2].sum()) for m in mbs))
@@ -1144,6 +1144,9 @@ def main():
                     help="fine-tune workload: data-parallel replicas of a (gpus / replicas)-stage pipeline; the default is one pipeline over all GPUs")
     ap.add_argument("--timeline", action="store_true",
                     help="fine-tune workload: also report when each task of one step ended on every rank (development aid)")
+    ap.add_argument("--early-exchange", action="store_true",
+                    help="fine-tune workload: the last rank takes the LM-head weight gradients first and starts the tied-table "
+                         "exchange from its task list; stages chosen for the steady-state step time")
     ap.add_argument("--async-optimizer", action="store_true",
                     help="fine-tune workload: queue Adam on the transfer stream beside the next step's first forward instead of on the compute stream after the step")
     ap.add_argument("--no-overlap", action="store_true",

@@ -76,7 +76,7 @@ class Trainer:
     def __init__(self, hidden, heads, vocab, n_layers, batch, tokens, n_micro, rank=0, world=1, dtype="half", seed=0,
                  loss_scale=1024.0, lr=1e-4, logits_rows=None, init_std=0.02, verbose=False, head_cost=LM_HEAD_COST_IN_LAYERS,
                  overlap=None, n_slots=None, activation_budget=56 << 30, play_all_ranks=False, split_layers=True, replicas=1,
-                 async_optimizer=False, early_exchange=True):
+                 async_optimizer=False, early_exchange=False):
         # data-parallel replicas: the job's ranks form `replicas` pipelines of world / replicas stages; each replica
         # takes every replicas-th micro-batch of a step and the gradients are summed over the replicas before Adam.
         # From here on rank / world / n_micro describe this rank's pipeline and its share of the micro-batches.

@@ -74,7 +74,8 @@ def main():
     tr = finetune.Trainer(CFG["hidden"], CFG["heads"], CFG["vocab"], CFG["n_layers"], CFG["batch"], CFG["tokens"], CFG["n_micro"],
                           rank=rank, world=world, seed=9, lr=1e-3, init_std=0.05, head_cost=head_cost,
                           overlap=os.environ.get("BR_TEST_OVERLAP", "1") != "0", replicas=replicas,
-                          async_optimizer=os.environ.get("BR_TEST_ASYNC_OPT", "0") == "1")
+                          async_optimizer=os.environ.get("BR_TEST_ASYNC_OPT", "0") == "1",
+                          early_exchange=os.environ.get("BR_TEST_EARLY_EXCHANGE", "0") == "1")
     # forward-only scoring through the same stages (the prefill path) with the initial weights: per-token NLL from the
     # rank that holds the head
     scored = tr.score(mbs[:2]) if replicas == 1 else []
@@ -120,7 +121,8 @@ def main():
             "w_err": float(np.abs(w_first - ref_w).max() / np.abs(ref_w).max()),
             "table_err": float(np.abs(table - ref_table).max() / np.abs(ref_table).max()),
             "tables_agree": abs(tables[0] - tables[-1]) <= 1e-6 * abs(tables[0]),
-            "scored": len(pipe_scores), "score_err": score_err, "counts": tr.counts, "overlap": tr.overlap, "n_slots": tr.n_slots, "replicas": replicas, "replicas_agree": replicas_agree,
+            "scored": len(pipe_scores), "score_err": score_err, "early_exchange": os.environ.get("BR_TEST_EARLY_EXCHANGE", "0") == "1",
+            "counts": tr.counts, "overlap": tr.overlap, "n_slots": tr.n_slots, "replicas": replicas, "replicas_agree": replicas_agree,
         }
         json.dump(res, open(out_path, "w"))
     dist.barrier()

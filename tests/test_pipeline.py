@@ -11,11 +11,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "pipeline_worker.py")
 
 
-def launch(world, backend, out_path, port, head_cost=0.5, overlap=True, replicas=1, async_opt=False):
+def launch(world, backend, out_path, port, head_cost=0.5, overlap=True, replicas=1, async_opt=False, early_exchange=False):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), WORKER, backend, out_path]
     env = dict(os.environ, OMP_NUM_THREADS="2", BR_TEST_HEAD_COST=str(head_cost), BR_TEST_OVERLAP="1" if overlap else "0",
-               BR_TEST_REPLICAS=str(replicas), BR_TEST_ASYNC_OPT="1" if async_opt else "0")
+               BR_TEST_REPLICAS=str(replicas), BR_TEST_ASYNC_OPT="1" if async_opt else "0",
+               BR_TEST_EARLY_EXCHANGE="1" if early_exchange else "0")
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     return json.load(open(out_path))
@@ -95,6 +96,18 @@ def test_two_stage_pipeline_with_the_optimizer_on_the_transfer_stream(tmp_path):
         pytest.skip("needs two GPUs")
     res = launch(2, "nccl", str(tmp_path / "out.json"), 29545, async_opt=True)
     assert res["overlap"]
+    check_against_single(res)
+
+
+@pytest.mark.gpu
+def test_two_stage_pipeline_with_the_early_table_exchange(tmp_path):
+    """The last rank takes the LM-head weight gradients first and starts the exchange of the tied table's gradient from
+    its task list, before the layers' weight gradients."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    res = launch(2, "nccl", str(tmp_path / "out.json"), 29547, early_exchange=True)
+    assert res["overlap"] and res["early_exchange"]
     check_against_single(res)
 
 
