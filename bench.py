@@ -699,7 +699,7 @@ def in_step_hbm(prof, cfg):
     peak, _ = load_peaks()
     per_call = {
         "layernorm_fwd": 2 * n * H * es + 2 * H * es + 4 * n,
-        "layernorm_bwd": 3 * n * H * es + 4 * n + 4 * H * es,
+        "layernorm_bwd": 4 * n * H * es + 4 * n + 4 * H * es,      # dy, y and the residual in, dx out (the layers' launches)
         "gelu_bwd": 3 * n * 4 * H * es,
         "add": 3 * n * H * es,
         # four bias gradients per layer: dy of 4h->h, h->4h, dense and QKV, read once each
